@@ -1,0 +1,153 @@
+"""Builds the CUDA sources of this folder for sm_100a, one shared library per
+.cu file, on first use, and loads them with ctypes.
+
+A library is rebuilt when its source, `common.cuh` or the flags change (a hash
+is stored beside it).  Libraries are kept in-tree under `csrc/_build/`; if that
+folder cannot be written they go to a per-user folder under the system's
+temporary directory.  While nvcc runs, a line is printed to stderr every few
+seconds, so that a first call that has to compile does not look hung.
+"""
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+# no fast-math: the 32-bit path relies on IEEE division, sqrt and expf
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-shared"]
+
+_lock = threading.Lock()
+_loaded = {}
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def sources():
+    return sorted(f[:-3] for f in os.listdir(_HERE) if f.endswith(".cu"))
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise BuildError("nvcc not found (looked at $NVCC, PATH and /usr/local/cuda/bin): "
+                     "the CUDA kernels of this engine cannot be built")
+
+
+def _build_dir():
+    d = os.path.join(_HERE, "_build")
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".w{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return d
+    except OSError:
+        d = os.path.join(tempfile.gettempdir(), f"sglc_b200_build_{os.getuid()}")
+        os.makedirs(d, exist_ok=True)
+        return d
+
+
+def _digest(name):
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for fn in sorted(os.listdir(_HERE)):
+        if fn == name + ".cu" or fn.endswith(".cuh"):
+            with open(os.path.join(_HERE, fn), "rb") as f:
+                h.update(fn.encode())
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def lib_path(name):
+    return os.path.join(_build_dir(), f"libsglc_{name}.so")
+
+
+def build(name, verbose=False):
+    """Compile csrc/<name>.cu if its library is missing or stale; return the path."""
+    src = os.path.join(_HERE, name + ".cu")
+    if not os.path.exists(src):
+        raise BuildError(f"no CUDA source {src}")
+    out = lib_path(name)
+    stamp = out + ".hash"
+    want = _digest(name)
+    if os.path.exists(out) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == want:
+                return out
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, src]
+    t0 = time.time()
+    print(f"[sglc_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            cwd=os.path.dirname(out))
+    while True:
+        try:
+            log, _ = proc.communicate(timeout=5)
+            break
+        except subprocess.TimeoutExpired:
+            print(f"[sglc_b200] ... still compiling {name}.cu ({time.time() - t0:.0f} s)",
+                  file=sys.stderr, flush=True)
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+        raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
+    os.replace(tmp, out)
+    with open(stamp, "w") as f:
+        f.write(want)
+    print(f"[sglc_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
+          file=sys.stderr, flush=True)
+    if verbose and log.strip():
+        print(log, file=sys.stderr)
+    return out
+
+
+def build_all(names=None, jobs=None):
+    """Compile every source (or the named ones), several at a time."""
+    names = list(names) if names is not None else sources()
+    jobs = jobs or min(len(names), os.cpu_count() or 1) or 1
+    errors = []
+
+    def work(n):
+        try:
+            build(n)
+        except Exception as e:  # collected and raised below
+            errors.append(e)
+
+    threads = []
+    pending = list(names)
+    while pending or threads:
+        while pending and len(threads) < jobs:
+            t = threading.Thread(target=work, args=(pending.pop(0),))
+            t.start()
+            threads.append(t)
+        threads[0].join()
+        threads.pop(0)
+    if errors:
+        raise errors[0]
+    return [lib_path(n) for n in names]
+
+
+def load(name):
+    """The ctypes handle of csrc/<name>.cu's library, built first if needed."""
+    with _lock:
+        lib = _loaded.get(name)
+        if lib is None:
+            path = build(name)
+            try:
+                lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise BuildError(f"cannot load {path}: {e}") from None
+            lib.sglc_error_string.restype = ctypes.c_char_p
+            lib.sglc_error_string.argtypes = [ctypes.c_int]
+            _loaded[name] = lib
+        return lib

@@ -1,0 +1,96 @@
+// Shared helpers of the kernels in this folder.  Every .cu file here builds to
+// one shared library with a C interface; the bindings in ops.py load them.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#define SGLC_API extern "C" __attribute__((visibility("default")))
+
+// element types a launcher takes, as small integers across the C interface
+enum { SGLC_F32 = 0, SGLC_BF16 = 1 };
+// epilogue activations
+enum { SGLC_ACT_NONE = 0, SGLC_ACT_GELU_TANH = 1, SGLC_ACT_GELU_ERF = 2 };
+
+// codes a launcher returns besides cudaError_t values (those are > 0)
+enum { SGLC_OK = 0, SGLC_ERR_UNSUPPORTED = -2, SGLC_ERR_ARGUMENT = -3 };
+
+SGLC_API const char* sglc_error_string(int code);
+
+#define SGLC_DEFINE_ERROR_STRING()                                            \
+  SGLC_API const char* sglc_error_string(int code) {                          \
+    if (code == SGLC_ERR_UNSUPPORTED) return "size not supported by this kernel"; \
+    if (code == SGLC_ERR_ARGUMENT) return "bad argument";                     \
+    return cudaGetErrorString((cudaError_t)code);                             \
+  }
+
+static inline int sglc_launch_status() { return (int)cudaGetLastError(); }
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// tanh form: 0.5*u*(1+tanh(sqrt(2/pi)*(u+0.044715*u^3)))  (reference src/ops.c:233-241)
+__device__ __forceinline__ float gelu_tanh_f32(float u) {
+  const float k = 0.7978845608028654f;
+  float inner = k * (u + 0.044715f * u * u * u);
+  return 0.5f * u * (1.0f + tanhf(inner));
+}
+// exact form: 0.5*u*(1+erf(u/sqrt(2)))
+__device__ __forceinline__ float gelu_erf_f32(float u) {
+  return 0.5f * u * (1.0f + erff(u * 0.70710678118654752440f));
+}
+__device__ __forceinline__ float apply_act(float u, int act) {
+  if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_f32(u);
+  if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
+  return u;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; every thread gets the result.  `red` holds at least 33 floats.
+// The order of additions depends only on blockDim, so a row's result does not
+// depend on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}

@@ -1,0 +1,180 @@
+"""Python bindings of the CUDA kernels: argument checks, then a ctypes call on
+the current stream.  Every function works on CUDA tensors only and raises if
+the kernels' library is missing or the GPU is absent: there is no CPU path.
+"""
+import ctypes
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t, what):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not handled (float32 or bfloat16)") from None
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; got a CPU tensor "
+                              "(this engine has no CPU path)")
+
+
+def _check(lib, code, what):
+    if code != 0:
+        msg = lib.sglc_error_string(code).decode()
+        raise KernelError(f"{what}: {msg} (code {code})")
+
+
+def _i32(t, what):
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what} must be a contiguous int32 tensor")
+
+
+# ---------------------------------------------------------------------------
+def embed(tokens, table, out, positions=None, pos_table=None, err_flag=None):
+    """out[t,:] = table[tokens[t],:] (+ pos_table[positions[t],:]); out is float32 [T,E]."""
+    _need_cuda(tokens, table, out, positions, pos_table)
+    _i32(tokens, "tokens")
+    T, E = out.shape
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("embed: out must be contiguous float32")
+    if table.shape[1] != E or not table.is_contiguous():
+        raise KernelError(f"embed: table {tuple(table.shape)} does not match width {E}")
+    P = 0
+    if pos_table is not None:
+        _i32(positions, "positions")
+        if pos_table.dtype != table.dtype or pos_table.shape[1] != E or not pos_table.is_contiguous():
+            raise KernelError("embed: position table must have the token table's dtype and width")
+        P = pos_table.shape[0]
+    lib = build.load("embed")
+    code = lib.sglc_embed(_ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table), _ptr(out),
+                          T, E, table.shape[0], P, _dt(table, "embed table"), _ptr(err_flag), _stream())
+    _check(lib, code, "embed")
+
+
+def add_rows(x, idx, table):
+    """x[t,:] += table[idx[t],:] (x float32)."""
+    _need_cuda(x, idx, table)
+    _i32(idx, "idx")
+    T, E = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or table.shape[1] != E:
+        raise KernelError("add_rows: x must be contiguous float32 of the table's width")
+    lib = build.load("embed")
+    code = lib.sglc_add_rows(_ptr(x), _ptr(idx), _ptr(table), T, E, table.shape[0],
+                             _dt(table, "table"), _stream())
+    _check(lib, code, "add_rows")
+
+
+def layernorm(x, gamma, beta, eps, out, rows=None):
+    """out[r,:] = LayerNorm(x[rows[r] or r,:]); x float32 [*,E]; out float32 or bfloat16."""
+    _need_cuda(x, gamma, beta, out, rows)
+    E = x.shape[-1]
+    n = out.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("layernorm: x must be contiguous float32 and out contiguous")
+    if gamma.dtype != torch.float32 or beta.dtype != torch.float32 or gamma.numel() != E or beta.numel() != E:
+        raise KernelError("layernorm: gain and bias must be float32 vectors of the row width")
+    if rows is not None:
+        _i32(rows, "rows")
+        if rows.numel() < n:
+            raise KernelError("layernorm: fewer row indices than output rows")
+    elif x.shape[0] < n:
+        raise KernelError("layernorm: fewer input rows than output rows")
+    lib = build.load("layernorm")
+    code = lib.sglc_layernorm(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), n, E,
+                              ctypes.c_float(eps), _dt(out, "layernorm out"), _stream())
+    _check(lib, code, f"layernorm (width {E})")
+
+
+def gemm_simt(a, w, bias, out=None, residual=None, act=None):
+    """out = act(a·wᵀ + bias), or residual += a·wᵀ + bias.  a [M,K] (row stride free),
+    w [N,K] contiguous; plain FFMA with 32-bit accumulation."""
+    _need_cuda(a, w, bias, out, residual)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or a.stride(1) != 1 or a.dtype != w.dtype:
+        raise KernelError(f"gemm: a {tuple(a.shape)}/{a.dtype} and w {tuple(w.shape)}/{w.dtype} do not match")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm: bias must be a float32 vector of N")
+    dst = residual if residual is not None else out
+    if dst is None or dst.shape[0] < M or dst.shape[1] != N or dst.stride(1) != 1:
+        raise KernelError("gemm: output does not match [M,N]")
+    if residual is not None and residual.dtype != torch.float32:
+        raise KernelError("gemm: the residual stream is float32")
+    lib = build.load("gemm_simt")
+    code = lib.sglc_gemm_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
+                              a.stride(0), dst.stride(0), _dt(a, "gemm input"),
+                              _dt(dst, "gemm output"), ACT[act], _stream())
+    _check(lib, code, f"gemm_simt M={M} N={N} K={K}")
+
+
+def kv_write(k_src, v_src, cache, slots, n_kv_heads, head_dim):
+    """Scatter keys and values of T tokens into one layer's pages.
+    k_src, v_src: [T, n_kv_heads*head_dim] views (row stride free); cache:
+    [n_pages, 2, n_kv_heads, page_size, head_dim]; slots int32 [T]."""
+    _need_cuda(k_src, v_src, cache, slots)
+    _i32(slots, "slots")
+    T = k_src.shape[0]
+    n_pages, two, H, page_size, D = cache.shape
+    if two != 2 or H != n_kv_heads or D != head_dim or not cache.is_contiguous():
+        raise KernelError(f"kv_write: cache {tuple(cache.shape)} does not match heads {n_kv_heads} x {head_dim}")
+    if k_src.shape[1] != H * D or k_src.stride(1) != 1 or v_src.stride(1) != 1 \
+            or k_src.stride(0) != v_src.stride(0) or k_src.dtype != cache.dtype:
+        raise KernelError("kv_write: key/value rows do not match the cache")
+    lib = build.load("kv_cache")
+    code = lib.sglc_kv_write(_ptr(k_src), _ptr(v_src), k_src.stride(0), _ptr(cache), _ptr(slots), T,
+                             H, D, page_size, n_pages, _dt(k_src, "kv source"), _dt(cache, "cache"),
+                             _stream())
+    _check(lib, code, "kv_write")
+
+
+def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
+                   max_keys):
+    """Causal attention of T tokens over the paged cache, 32-bit arithmetic.
+    q: [T, n_heads*head_dim] view; out likewise; block_table int32 [R, max_blocks]."""
+    _need_cuda(q, cache, block_table, token_req, positions, out)
+    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, nm)
+    T = q.shape[0]
+    n_pages, two, Hkv, page_size, D = cache.shape
+    if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != out.dtype:
+        raise KernelError("attention: query/output rows do not match heads x head_dim")
+    if q.dtype != cache.dtype:
+        raise KernelError("attention: queries and cache must have one dtype")
+    lib = build.load("attention_simt")
+    code = lib.sglc_attention_simt(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                   block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
+                                   out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
+                                   int(window or 0), int(max_keys), _dt(q, "attention q"),
+                                   _dt(cache, "cache"), _stream())
+    _check(lib, code, f"attention_simt (head_dim {D}, up to {max_keys} keys)")
+
+
+# ---------------------------------------------------------------------------
+# tensor-core GEMM (bfloat16): filled in by gemm_tc.cu's bindings
+def gemm_tc_supported(a, w):
+    return False
+
+
+def gemm_tc(a, w, bias, out=None, residual=None, act=None):
+    raise KernelError("the tensor-core GEMM is not built")

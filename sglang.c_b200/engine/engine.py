@@ -1,0 +1,208 @@
+"""The engine core: model, cache and the one step function.
+
+`Engine.step(entries)` takes a batch of (request, its next tokens, wanted
+places): portions of prompts beside single decoded tokens, cut anywhere.  It
+runs only the tokens it is given, as one batch, against what earlier steps left
+in the cache, and returns the logits at the wanted places.
+"""
+import torch
+
+from ..cache import CacheManager
+from ..config.registry import load_config
+from .model import Model
+from .runtime import Runtime
+from .step import GroupStep, StepBuffers, StepContext, StepEntry, Workspace
+
+
+class StepError(ValueError):
+    """A step that cannot run as asked (bad ids, unknown request, too many tokens)."""
+
+
+class OutOfPages(RuntimeError):
+    """The step needs more pages than are free.  Nothing was run or changed."""
+
+
+class Engine:
+    def __init__(self, plan, runtime, page_size=16, n_pages=None, max_tokens=None, max_requests=64,
+                 max_step_tokens=2048, model_dir=None):
+        self.rt = runtime
+        self.plan = plan
+        self.model = Model(plan, runtime)
+        if model_dir is not None:
+            self.model.load(model_dir)
+        if n_pages is None:
+            if max_tokens is None:
+                raise ValueError("give n_pages or max_tokens to size the cache")
+            n_pages = (int(max_tokens) + page_size - 1) // page_size
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.max_step_tokens = int(max_step_tokens)
+        needs, cache_of = self.model.cache_needs()
+        self.cache = CacheManager(needs, cache_of, self.page_size, n_pages, self.max_requests,
+                                  make_tensor=runtime.make_tensor, cache_dtype=runtime.cache_dtype_name)
+        self.b_cap = (plan.max_positions + self.page_size - 1) // self.page_size
+        self._paged = self.cache.paged_groups()
+        self.bufs = StepBuffers(runtime.device, self.max_step_tokens, self.max_requests, self.b_cap,
+                                len(self.cache.groups))
+        self.err_flag = torch.zeros(1, dtype=torch.int32, device=runtime.device)
+        self.ws = Workspace(runtime.device, self._workspace_bytes())
+        self.logits = None
+        self.steps_run = 0
+
+    # -- construction ---------------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir, dtype="bfloat16", device="cuda:0", **kw):
+        arch, cfg = load_config(model_dir)
+        plan = arch.build_plan(cfg)
+        eng = cls(plan, Runtime(dtype, device), model_dir=model_dir, **kw)
+        eng.config = cfg
+        eng.architecture = arch
+        return eng
+
+    def _workspace_bytes(self):
+        widths = [self.plan.hidden_size]
+        for lp in self.plan.layers:
+            for spec in (lp.mixer, lp.ffn):
+                p = spec.params
+                widths.append(int(p.get("inner_size", 0)))
+                if "n_heads" in p:
+                    widths.append((p["n_heads"] + 2 * p.get("n_kv_heads", p["n_heads"])) * p["head_dim"])
+        per_token = 4 * (3 * self.plan.hidden_size + 2 * max(widths) + 2 * sum(sorted(widths)[-2:]))
+        return per_token * self.max_step_tokens + (8 << 20)
+
+    def _logits_buffer(self, n):
+        if self.logits is None or self.logits.shape[0] < n:
+            cap = max(n, min(self.max_step_tokens, 64))
+            self.logits = torch.empty((cap, self.plan.vocab_size), dtype=torch.float32,
+                                      device=self.rt.device)
+        return self.logits
+
+    # -- requests ---------------------------------------------------------------
+    def add_request(self, req):
+        slot = self.cache.add_request(req)
+        if slot is None:
+            raise StepError(f"all {self.max_requests} request slots are taken")
+        return slot
+
+    def end_request(self, req):
+        self.cache.free_request(req)
+
+    def has_request(self, req):
+        return self.cache.has_request(req)
+
+    def length(self, req):
+        return self.cache.length(req)
+
+    # -- the step ---------------------------------------------------------------
+    def _validate(self, entries):
+        seen = set()
+        T = 0
+        V, P = self.plan.vocab_size, self.plan.max_positions
+        for e in entries:
+            if e.req in seen:
+                raise StepError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            if not self.cache.has_request(e.req):
+                raise StepError(f"request {e.req!r} is not live (add_request first)")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.req!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"request {e.req!r}: token id {t} is outside the vocabulary of {V}")
+            if self.cache.length(e.req) + n > P:
+                raise StepError(f"request {e.req!r} would reach {self.cache.length(e.req) + n} positions; "
+                                f"the model has {P}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.req!r}: wanted place {w} is outside its {n} tokens")
+            T += n
+        if T > self.max_step_tokens:
+            raise StepError(f"step of {T} tokens exceeds max_step_tokens={self.max_step_tokens}")
+        if len(entries) > self.max_requests:
+            raise StepError(f"step of {len(entries)} requests exceeds max_requests={self.max_requests}")
+        return T
+
+    def pages_available_for(self, wants):
+        return self.cache.can_extend_all(wants)
+
+    def step(self, entries):
+        """entries: list of StepEntry (or (req, tokens, want) tuples).  Returns a
+        float32 device tensor [n_wanted, vocab]: the logits at the wanted
+        places, in the order of the entries and of each `want`.  The tensor is
+        a view of a buffer that the next step overwrites."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        V = self.plan.vocab_size
+        if not entries:
+            return torch.empty((0, V), dtype=torch.float32, device=self.rt.device)
+        T = self._validate(entries)
+        wants = [(e.req, self.cache.length(e.req) + len(e.tokens)) for e in entries]
+        if not self.cache.can_extend_all(wants):
+            raise OutOfPages(f"step needs more pages than the {self.cache.n_free_pages()} free ones")
+        old_len = [self.cache.length(e.req) for e in entries]
+        for (req, new_len) in wants:
+            ok = self.cache.extend(req, new_len)
+            assert ok, "extend failed after can_extend_all"
+
+        b = self.bufs
+        b.wait_host_free()
+        R = len(entries)
+        tok, pos, trq, wr = b.hview("tokens"), b.hview("positions"), b.hview("token_req"), b.hview("want_rows")
+        qs, kl, ss = b.hview("q_start"), b.hview("kv_len"), b.hview("state_slots")
+        ctx = StepContext(self.rt, self.ws)
+        t0 = 0
+        nw = 0
+        max_keys = 0
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            tok[t0:t0 + n] = torch.tensor(e.tokens, dtype=torch.int32)
+            pos[t0:t0 + n] = torch.arange(old_len[r], old_len[r] + n, dtype=torch.int32)
+            trq[t0:t0 + n] = r
+            qs[r] = t0
+            kl[r] = old_len[r] + n
+            ss[r] = self.cache.slot(e.req)
+            for w in e.want:
+                wr[nw] = t0 + int(w)
+                nw += 1
+            for gi in self._paged:
+                table = self.cache.block_table(gi, e.req)
+                sl = b.hview(f"slots{gi}")
+                bt = b.hview(f"bt{gi}")
+                tt = torch.tensor(table, dtype=torch.int32)
+                bt[r * self.b_cap: r * self.b_cap + len(table)] = tt
+                p = torch.arange(old_len[r], old_len[r] + n, dtype=torch.int64)
+                sl[t0:t0 + n] = (tt[p // self.page_size].to(torch.int64) * self.page_size
+                                 + p % self.page_size).to(torch.int32)
+            ctx.h_q_len.append(n)
+            ctx.h_kv_len.append(old_len[r] + n)
+            ctx.h_fresh.append(old_len[r] == 0)
+            ctx.h_reqs.append(e.req)
+            max_keys = max(max_keys, old_len[r] + n)
+            ctx.max_q_len = max(ctx.max_q_len, n)
+            t0 += n
+        qs[R] = t0
+        b.upload()
+
+        ctx.T, ctx.R, ctx.n_want, ctx.max_keys = T, R, nw, max_keys
+        ctx.tokens, ctx.positions = b.dview("tokens", T), b.dview("positions", T)
+        ctx.token_req, ctx.want_rows = b.dview("token_req", T), b.dview("want_rows", max(nw, 1))
+        ctx.q_start, ctx.kv_len = b.dview("q_start", R + 1), b.dview("kv_len", R)
+        ctx.state_slots = b.dview("state_slots", R)
+        ctx.err_flag = self.err_flag
+        ctx.groups = []
+        for gi in range(len(self.cache.groups)):
+            if gi in self._paged:
+                ctx.groups.append(GroupStep(b.dview(f"bt{gi}").view(self.max_requests, self.b_cap),
+                                            b.dview(f"slots{gi}", T), self.page_size))
+            else:
+                ctx.groups.append(None)
+        self.ws.reset()
+        logits = self.model.forward(ctx, self.cache, self._logits_buffer(nw))
+        self.steps_run += 1
+        return logits
+
+    def check_device_errors(self):
+        """Raise if a kernel flagged corrupted step data (synchronises)."""
+        if int(self.err_flag.item()) != 0:
+            self.err_flag.zero_()
+            raise RuntimeError("a kernel met an out-of-range token or position id")

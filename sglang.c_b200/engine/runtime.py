@@ -1,0 +1,50 @@
+"""The runtime: device, precision, and the choice of kernel for each operation.
+
+"float32": weights, activations and cache in 32-bit, every product by plain
+FFMA kernels (no tensor-core mode).  "bfloat16": matrices, activations and
+cache in bfloat16 with 32-bit accumulation; the residual stream, norms' and
+softmax statistics stay 32-bit in both.
+"""
+import torch
+
+from ..csrc import ops
+
+_NAMES = {"float32": "float32", "fp32": "float32", "f32": "float32",
+          "bfloat16": "bfloat16", "bf16": "bfloat16"}
+
+
+class Runtime:
+    def __init__(self, dtype="bfloat16", device="cuda:0"):
+        if dtype not in _NAMES:
+            raise ValueError(f"dtype '{dtype}' is not handled; choose float32 or bfloat16")
+        self.dtype = _NAMES[dtype]
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("this engine runs on a CUDA device only (no CPU path)")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; this engine has no CPU path")
+        t = torch.float32 if self.dtype == "float32" else torch.bfloat16
+        self.matrix_dtype = t
+        self.act_dtype = t
+        self.cache_dtype = t
+
+    @property
+    def cache_dtype_name(self):
+        return self.dtype
+
+    def make_tensor(self, shape, dtype_name):
+        dt = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}[dtype_name]
+        return torch.zeros(shape, dtype=dt, device=self.device)
+
+    # -- kernel choice --------------------------------------------------------
+    def gemm(self, a, w, bias, out=None, residual=None, act=None):
+        if self.dtype == "bfloat16" and ops.gemm_tc_supported(a, w):
+            return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act)
+        return ops.gemm_simt(a, w, bias, out=out, residual=residual, act=act)
+
+    def kv_write(self, k, v, cache, slots, n_kv_heads, head_dim):
+        ops.kv_write(k, v, cache, slots, n_kv_heads, head_dim)
+
+    def attention(self, ctx, q, cache, grp, out, n_heads, scale, window):
+        ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
+                           scale, window, ctx.max_keys)

@@ -1,0 +1,56 @@
+"""Attention mixers."""
+from ..cache.needs import CacheNeed
+from .base import Part
+from .linear import Linear, declare_linear
+from .registry import register_part
+
+
+@register_part("mixer", "causal_attention")
+class CausalAttention(Part):
+    """Causal multi-head attention over a paged cache:
+    qkv = h·W + b, split q|k|v along the last axis, heads side by side; new keys
+    and values go to the cache; each query attends to the keys at positions up to
+    its own (within `window` if set); the heads' outputs, side by side, go
+    through the output projection into the residual
+    (reference src/gpt2.c:222-278).
+    params: size, n_heads, n_kv_heads, head_dim, scale (the multiplier of q·k),
+    window (None or a count of keys), bias, weight_layout."""
+
+    @classmethod
+    def declare_weights(cls, params):
+        lay, bias = params.get("weight_layout", "linear"), params.get("bias", True)
+        qkv_out = (params["n_heads"] + 2 * params["n_kv_heads"]) * params["head_dim"]
+        qkv = declare_linear(params["size"], qkv_out, lay, bias)
+        out = declare_linear(params["n_heads"] * params["head_dim"], params["size"], lay, bias,
+                             init="residual_matrix")
+        d = {"qkv_" + k: v for k, v in qkv.items()}
+        d.update({"out_" + k: v for k, v in out.items()})
+        return d
+
+    def load(self, tensors, store):
+        lay = self.params.get("weight_layout", "linear")
+        self.qkv = Linear.from_refs(store, tensors["qkv_weight"], tensors.get("qkv_bias"), lay)
+        self.out = Linear.from_refs(store, tensors["out_weight"], tensors.get("out_bias"), lay)
+
+    def cache_need(self):
+        p = self.params
+        return CacheNeed.paged_kv(p["n_kv_heads"], p["head_dim"], p.get("window"))
+
+    def forward(self, ctx, h, residual, cache, position=None):
+        p = self.params
+        H, Hkv, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]
+        T = h.shape[0]
+        qkv = ctx.alloc((T, (H + 2 * Hkv) * D), self.rt.act_dtype)
+        self.qkv.forward(ctx, h, out=qkv)
+        q = qkv[:, :H * D]
+        k = qkv[:, H * D:(H + Hkv) * D]
+        v = qkv[:, (H + Hkv) * D:]
+        if position is not None:
+            position.rotate(ctx, q, k)
+        grp = ctx.group(cache.group)
+        if cache.write:
+            ctx.rt.kv_write(k, v, cache.tensor, grp.slots, Hkv, D)
+        o = ctx.alloc((T, H * D), self.rt.act_dtype)
+        ctx.rt.attention(ctx, q, cache.tensor, grp, o, H, float(p["scale"]), p.get("window"))
+        self.out.forward(ctx, o, residual=residual)
+        return residual

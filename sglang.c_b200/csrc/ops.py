@@ -178,3 +178,21 @@ def gemm_tc_supported(a, w):
 
 def gemm_tc(a, w, bias, out=None, residual=None, act=None):
     raise KernelError("the tensor-core GEMM is not built")
+
+
+def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
+    """One token per row of `logits` ([n, V] float32, row stride free; penalties
+    change the rows in place).  `params`: int32 tensor [n, 10] holding the packed
+    per-row records (see sampling.cu); hist_tok/hist_cnt: int32 (token, count)
+    pairs of the rows' histories."""
+    _need_cuda(logits, params, hist_tok, hist_cnt, out_tok, out_logprob)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 rows")
+    if params.dtype != torch.int32 or params.shape != (n, 10) or not params.is_contiguous():
+        raise KernelError("sample: params must be a contiguous int32 [n,10] tensor")
+    _i32(out_tok, "out_tok")
+    lib = build.load("sampling")
+    code = lib.sglc_sample(_ptr(logits), logits.stride(0), V, n, _ptr(params), _ptr(hist_tok),
+                           _ptr(hist_cnt), _ptr(out_tok), _ptr(out_logprob), _stream())
+    _check(lib, code, "sample")

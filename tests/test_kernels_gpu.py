@@ -1,0 +1,303 @@
+"""Each kernel alone against a plain PyTorch reference of the same operation,
+at sizes other than the engine's test models: widths and vocabularies that are
+no power of two, head sizes in steps of 16, odd numbers of heads and groups."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from sglang_c_b200.csrc import ops
+    return ops
+
+
+def _rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,E,V,P", [(1, 48, 11, 5), (37, 1600, 1000, 300), (5, 100, 50257, 64)])
+def test_embed(T, E, V, P, dtype):
+    ops = _ops()
+    wte, wpe = _rand(V, E, dtype=dtype, seed=1), _rand(P, E, dtype=dtype, seed=2)
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    pos = torch.randint(0, P, (T,), generator=g, dtype=torch.int32).to(DEV)
+    out = torch.empty(T, E, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed(tok, wte, out, positions=pos, pos_table=wpe, err_flag=err)
+    ref = wte.float()[tok.long()] + wpe.float()[pos.long()]
+    assert torch.equal(out, ref) and int(err.item()) == 0
+    out2 = torch.empty(T, E, device=DEV)
+    ops.embed(tok, wte, out2)
+    ops.add_rows(out2, pos, wpe)
+    assert torch.equal(out2, ref)
+    # an id outside the table is flagged, not read
+    tok[0] = V
+    ops.embed(tok, wte, out, positions=pos, pos_table=wpe, err_flag=err)
+    assert int(err.item()) == 1 and float(out[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,E,eps", [(1, 16, 1e-5), (33, 96, 1e-6), (7, 1600, 1e-5), (3, 50, 1e-3), (2, 4099, 1e-5)])
+def test_layernorm(n, E, eps, out_dtype):
+    ops = _ops()
+    x = _rand(n, E, seed=4, scale=3.0) + 1.5
+    gamma, beta = _rand(E, seed=5) + 1.0, _rand(E, seed=6)
+    out = torch.empty(n, E, dtype=out_dtype, device=DEV)
+    ops.layernorm(x, gamma, beta, eps, out)
+    xd = x.double()
+    ref = (xd - xd.mean(-1, keepdim=True)) / torch.sqrt(xd.var(-1, unbiased=False, keepdim=True) + eps)
+    ref = ref * gamma.double() + beta.double()
+    tol = 2e-5 if out_dtype == torch.float32 else 4e-2
+    assert float((out.double() - ref).abs().max()) < tol
+    # gathered rows
+    rows = torch.tensor(list(range(n - 1, -1, -1)), dtype=torch.int32, device=DEV)
+    out2 = torch.empty(n, E, dtype=out_dtype, device=DEV)
+    ops.layernorm(x, gamma, beta, eps, out2, rows=rows)
+    assert torch.equal(out2, out.flip(0))
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (65, 129, 100), (130, 50257 // 16, 96), (3, 320, 1600)])
+def test_gemm_simt(M, N, K, in_dtype):
+    ops = _ops()
+    a, w, bias = _rand(M, K, dtype=in_dtype, seed=7), _rand(N, K, dtype=in_dtype, seed=8, scale=0.1), _rand(N, seed=9)
+    ref = a.double() @ w.double().t() + bias.double()
+    tol = 1e-5 * math.sqrt(K) if in_dtype == torch.float32 else 1e-4 * math.sqrt(K)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_simt(a, w, bias, out=out)
+    assert float((out.double() - ref).abs().max()) < tol
+    for act, fn in (("gelu_tanh", lambda u: torch.nn.functional.gelu(u, approximate="tanh")),
+                    ("gelu_erf", torch.nn.functional.gelu)):
+        ops.gemm_simt(a, w, bias, out=out, act=act)
+        assert float((out.double() - fn(ref)).abs().max()) < tol
+    res = _rand(M, N, seed=10)
+    res0 = res.clone()
+    ops.gemm_simt(a, w, bias, residual=res)
+    assert float((res.double() - (res0.double() + ref)).abs().max()) < tol
+    # a row's result does not depend on the rows beside it
+    if M > 1:
+        one = torch.empty(1, N, device=DEV)
+        ops.gemm_simt(a[M - 1:M], w, bias, out=one)
+        ops.gemm_simt(a, w, bias, out=out)
+        assert torch.equal(one[0], out[M - 1])
+    # strided input rows (a column slice of a wider buffer)
+    wide = _rand(M, K + 24, dtype=in_dtype, seed=11)
+    ops.gemm_simt(wide[:, 8:8 + K], w, None, out=out)
+    assert float((out.double() - wide[:, 8:8 + K].double() @ w.double().t()).abs().max()) < tol
+
+
+def _paged_case(lens, q_lens, H, Hkv, D, page_size, dtype, seed, n_pages_extra=3, far_key=None):
+    """Random requests laid out in shuffled pages.  Returns the kernel inputs and
+    per-request dense K, V, and queries for the reference."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    n_blocks = [(n + page_size - 1) // page_size for n in lens]
+    n_pages = sum(n_blocks) + n_pages_extra
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    maxb = max(n_blocks) + 1
+    bt = torch.full((R, maxb), -1, dtype=torch.int32)
+    cache = torch.randn(n_pages, 2, Hkv, page_size, D, generator=g).to(dtype)   # garbage where unused
+    Ks, Vs, Qs = [], [], []
+    token_req, positions = [], []
+    pi = 0
+    for r, n in enumerate(lens):
+        K = torch.randn(n, Hkv, D, generator=g)
+        V = torch.randn(n, Hkv, D, generator=g)
+        Q = torch.randn(q_lens[r], H, D, generator=g)
+        if far_key is not None and n > far_key:
+            # one far key stands out for the last query: the score at that key dominates
+            K[far_key] = K[far_key] * 0 + Q[-1, ::H // Hkv][:Hkv] * 4.0
+        K, V, Q = K.to(dtype), V.to(dtype), Q.to(dtype)
+        for b in range(n_blocks[r]):
+            page = perm[pi]
+            pi += 1
+            bt[r, b] = page
+            lo, hi = b * page_size, min(n, (b + 1) * page_size)
+            cache[page, 0, :, :hi - lo] = K[lo:hi].transpose(0, 1)
+            cache[page, 1, :, :hi - lo] = V[lo:hi].transpose(0, 1)
+        Ks.append(K)
+        Vs.append(V)
+        Qs.append(Q)
+        for j in range(q_lens[r]):
+            token_req.append(r)
+            positions.append(n - q_lens[r] + j)
+    q = torch.cat([x.reshape(x.shape[0], H * D) for x in Qs])
+    return dict(q=q.to(DEV), cache=cache.to(DEV), bt=bt.to(DEV),
+                token_req=torch.tensor(token_req, dtype=torch.int32, device=DEV),
+                positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                Ks=Ks, Vs=Vs, Qs=Qs, lens=lens, q_lens=q_lens)
+
+
+def _attention_reference(case, H, Hkv, D, scale, window):
+    outs = []
+    for K, V, Q, n, ql in zip(case["Ks"], case["Vs"], case["Qs"], case["lens"], case["q_lens"]):
+        K, V, Q = K.double(), V.double(), Q.double()
+        o = torch.zeros(ql, H, D, dtype=torch.float64)
+        for j in range(ql):
+            pos = n - ql + j
+            lo = 0 if not window else max(0, pos - window + 1)
+            for h in range(H):
+                hk = h // (H // Hkv)
+                s = (K[lo:pos + 1, hk] @ Q[j, h]) * scale
+                w = torch.softmax(s, 0)
+                o[j, h] = w @ V[lo:pos + 1, hk]
+        outs.append(o.reshape(ql, H * D))
+    return torch.cat(outs)
+
+
+ATTN_CASES = [
+    # lens, q_lens, H, Hkv, D, page_size, window
+    ([1], [1], 1, 1, 16, 16, None),
+    ([37, 5, 64], [37, 1, 3], 4, 4, 16, 16, None),
+    ([100, 33], [2, 33], 3, 3, 32, 8, None),
+    ([70, 129, 16], [1, 1, 1], 6, 2, 48, 16, None),        # grouped heads, head size 48
+    ([65, 40], [65, 7], 5, 1, 80, 4, None),                # one key/value head for five query heads
+    ([90, 50, 17], [30, 50, 1], 2, 2, 64, 16, 24),         # a window: its edge falls inside a page
+    ([200], [200], 2, 1, 128, 32, 33),
+    ([300, 9], [1, 9], 25, 25, 64, 16, None),              # 25 heads
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case_id", range(len(ATTN_CASES)))
+def test_attention_simt_and_kv_write(case_id, dtype):
+    ops = _ops()
+    lens, q_lens, H, Hkv, D, ps, window = ATTN_CASES[case_id]
+    c = _paged_case(lens, q_lens, H, Hkv, D, ps, dtype, seed=case_id)
+    scale = 0.7 / math.sqrt(D)
+    T = c["q"].shape[0]
+    out = torch.empty(T, H * D, dtype=dtype, device=DEV)
+    ops.attention_simt(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, scale,
+                       window, max(lens))
+    ref = _attention_reference(c, H, Hkv, D, scale, window)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert float((out.double().cpu() - ref).abs().max()) < tol
+    # kv_write puts the step's own keys and values where attention reads them
+    cache2 = torch.zeros_like(c["cache"])
+    for r, (K, V, n) in enumerate(zip(c["Ks"], c["Vs"], lens)):
+        k_src = K.reshape(n, Hkv * D).to(DEV)
+        v_src = V.reshape(n, Hkv * D).to(DEV)
+        p = torch.arange(n)
+        slots = (c["bt"][r].cpu()[p // ps].long() * ps + p % ps).to(torch.int32).to(DEV)
+        ops.kv_write(k_src, v_src, cache2, slots, Hkv, D)
+    out2 = torch.empty_like(out)
+    ops.attention_simt(c["q"], cache2, c["bt"], c["token_req"], c["positions"], out2, H, scale,
+                       window, max(lens))
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(dtype):
+    """One key hundreds of positions back carries nearly all the weight: a kernel
+    that loses it (a page's edge, a wrong block) is far off."""
+    ops = _ops()
+    H, Hkv, D, ps = 2, 2, 64, 16
+    for far in (0, 15, 16, 255, 256, 300):
+        c = _paged_case([700], [1], H, Hkv, D, ps, dtype, seed=far, far_key=far)
+        out = torch.empty(1, H * D, dtype=dtype, device=DEV)
+        ops.attention_simt(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, 1.0, None, 700)
+        ref = _attention_reference(c, H, Hkv, D, 1.0, None)
+        v_far = c["Vs"][0][far].double().reshape(-1)
+        assert float((ref[0] - v_far).abs().max()) < 0.05        # the case is what it claims
+        assert float((out.double().cpu() - ref).abs().max()) < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def _sampling_reference(row, p, u):
+    """The kept set by thresholds (ties kept) and the draw in index order, float64."""
+    l = row.astype(np.float64)
+    if p["temperature"] <= 0:
+        return int(np.argmax(l)), None
+    w = np.exp((l - l.max()) / p["temperature"])
+    S = w.sum()
+    keep = np.ones_like(w, dtype=bool)
+    if 0 < p["min_p"] < 1:
+        keep &= w >= p["min_p"]
+    if 0 < p["top_k"] < len(w):
+        kept = np.sort(w[keep])[::-1]
+        if len(kept) >= p["top_k"]:
+            keep &= w >= kept[p["top_k"] - 1]
+    if 0 < p["top_p"] < 1:
+        order = np.argsort(-np.where(keep, w, -1), kind="stable")
+        cum = np.cumsum(np.where(keep[order], w[order], 0.0))
+        idx = np.searchsorted(cum, p["top_p"] * S, side="left")
+        if idx < keep.sum():
+            keep &= w >= w[order[idx]]
+    cdf = np.cumsum(np.where(keep, w, 0.0))
+    cdf /= cdf[-1]
+    return keep, cdf
+
+
+@pytest.mark.parametrize("V", [50, 1000, 50257])
+def test_sampling(V):
+    from sglang_c_b200.sampling import Sampler, SamplingParams
+    g = torch.Generator().manual_seed(V)
+    n = 12
+    logits = (torch.randn(n, V, generator=g) * 2.0)
+    logits[0, 7] = logits[0].max() + 1.0
+    logits[0, 3] = logits[0, 7]                  # equal maxima: the lowest index wins
+    params = [SamplingParams(),                               # greedy
+              SamplingParams(temperature=0.0, top_k=5),
+              SamplingParams(temperature=0.8),
+              SamplingParams(temperature=1.3),
+              SamplingParams(temperature=0.8, top_k=5),
+              SamplingParams(temperature=1.0, top_k=1),
+              SamplingParams(temperature=1.0, top_p=0.5),
+              SamplingParams(temperature=0.7, top_p=0.9, top_k=20),
+              SamplingParams(temperature=1.0, min_p=0.2),
+              SamplingParams(temperature=0.8, top_k=50, top_p=0.95),   # the command line's defaults
+              SamplingParams(temperature=1.0, top_k=10, top_p=0.3, min_p=0.05),
+              SamplingParams(temperature=2.0, top_p=0.99)]
+    s = Sampler(DEV, 16)
+    rng = np.random.default_rng(V)
+    for trial in range(6):
+        us = [float(u) for u in rng.random(n)]
+        if trial == 0:
+            us = [0.0] * n
+        if trial == 1:
+            us = [0.9999999] * n
+        dev = logits.clone().to(DEV)
+        toks = s.sample(dev, params, us)
+        for i in range(n):
+            p = dict(temperature=params[i].temperature, top_k=params[i].top_k, top_p=params[i].top_p,
+                     min_p=params[i].min_p)
+            keep, cdf = _sampling_reference(logits[i].numpy(), p, us[i])
+            if cdf is None:
+                assert toks[i] == keep
+                continue
+            t = toks[i]
+            assert keep[t], f"row {i}: token {t} is outside the kept set"
+            lo = cdf[t - 1] if t > 0 else 0.0
+            assert lo - 1e-4 <= us[i] <= cdf[t] + 1e-4, f"row {i}: u={us[i]} not in [{lo},{cdf[t]}]"
+    assert toks[0] == 3
+
+
+def test_sampling_penalties_and_logprob():
+    from sglang_c_b200.sampling import Sampler, SamplingParams
+    V = 300
+    g = torch.Generator().manual_seed(1)
+    logits = torch.randn(3, V, generator=g)
+    top = int(logits[0].argmax())
+    second = int(logits[0].topk(2).indices[1])
+    logits[0, top] = abs(float(logits[0, top])) + 1.0
+    s = Sampler(DEV, 8)
+    params = [SamplingParams(repetition_penalty=100.0), SamplingParams(frequency_penalty=2.0, presence_penalty=0.5),
+              SamplingParams()]
+    hist = [[top, top], [int(logits[1].argmax())] * 3, [1, 2, 3]]
+    dev = logits.clone().to(DEV)
+    toks, lps = s.sample(dev, params, [0.0] * 3, histories=hist, want_logprobs=True)
+    assert toks[0] == second
+    l1 = logits[1].clone().double()
+    l1[hist[1][0]] -= 2.0 * 3 + 0.5
+    assert toks[1] == int(l1.argmax())
+    assert abs(lps[1] - float(torch.log_softmax(l1, 0)[toks[1]])) < 1e-4
+    assert toks[2] == int(logits[2].argmax())
+    assert abs(lps[2] - float(torch.log_softmax(logits[2].double(), 0)[toks[2]])) < 1e-4

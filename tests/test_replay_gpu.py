@@ -1,0 +1,186 @@
+"""Replay through the engine's step function, cut in every way, against the
+plain implementation, in 32-bit and in bfloat16."""
+import io
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_gpt2
+import traces
+from conftest import PAGE_SIZE, ROOT, TINY
+
+pytestmark = pytest.mark.gpu
+
+# Fixed before the first run.  32-bit: the engine and the float64 oracle differ by
+# float32 rounding only (logits are below 1 in size).  bfloat16: activations and
+# products are rounded to 8 bits of mantissa; a fault of the cache or of a kernel
+# moves logits by several 1e-2 at least.
+TOL = {"float32": 2e-5, "bfloat16": 1e-2}
+STORE = {"float32": "float32", "bfloat16": "bfloat16"}
+
+LENGTHS = {"A": [5, 17, 32, 100, 128], "B": [1, 9, 40, 63, 100, 201]}
+
+
+def requests_for(name):
+    V = TINY[name]["vocab_size"]
+    return {f"r{i}": traces.random_tokens(10 * i + ord(name), n, V) for i, n in enumerate(LENGTHS[name])}
+
+
+_ref_cache = {}
+
+
+def reference(model_dir, requests):
+    out = {}
+    for rid, toks in requests.items():
+        key = (model_dir, tuple(toks))
+        if key not in _ref_cache:
+            _ref_cache[key] = plain_gpt2.forward_dir(model_dir, toks)
+        out[rid] = _ref_cache[key]
+    return out
+
+
+def run_trace(model_dir, dtype, name, steps, tmp_path, n_pages=None, max_tokens=None, max_step_tokens=256):
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.engine.replay import replay
+    ps = PAGE_SIZE[name]
+    if n_pages is None:
+        n_pages = (max_tokens or traces.peak_tokens(steps)) // ps
+    eng = Engine.from_dir(model_dir, dtype=dtype, page_size=ps, n_pages=n_pages, max_requests=8,
+                          max_step_tokens=max_step_tokens)
+    out = str(tmp_path / "out")
+    done = []
+    replay(eng, traces.to_lines(steps), out, emit=done.append)
+    assert done == [f"done {st['step']}" for st in steps]
+    eng.cache.check()
+    assert eng.cache.n_free_pages() == n_pages, "pages were not all given back"
+    return traces.collect(steps, out, TINY[name]["vocab_size"]), eng
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions"])
+def test_each_request_alone(model_dirs, tmp_path, name, dtype, mode):
+    d = model_dirs(name, STORE[dtype])
+    reqs = requests_for(name)
+    steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions}[mode](reqs)
+    got, _ = run_trace(d, dtype, name, steps, tmp_path)
+    err, where = traces.max_error(got, reference(d, reqs))
+    assert err < TOL[dtype], f"{mode}: max error {err} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_batches_with_pages_used_again(model_dirs, tmp_path, name, dtype):
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    P = TINY[name]["n_positions"]
+    lens = [37, 64, 90, 21, 128, 55, 70, 33, 101, 48] if name == "A" else [50, 1, 130, 77, 200, 9, 64, 150, 31, 99]
+    lens = [min(n, P) for n in lens]
+    reqs = {f"m{i}": traces.random_tokens(1000 + i, n, V) for i, n in enumerate(lens)}
+    prompt_len = {rid: max(1, len(t) - 20 - 3 * i) for i, (rid, t) in enumerate(reqs.items())}
+    steps = traces.mixed(reqs, prompt_len, seed=3)
+    peak = traces.peak_tokens(steps)
+    total = sum((n + 63) // 64 * 64 for n in lens)
+    assert peak < total, "the pool must be smaller than all requests together"
+    got, eng = run_trace(d, dtype, name, steps, tmp_path, max_tokens=peak)
+    err, where = traces.max_error(got, reference(d, reqs))
+    assert err < TOL[dtype], f"mixed: max error {err} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_results_equal_alone_results(model_dirs, tmp_path, dtype):
+    """What else is in the batch and which pages are used changes a position's
+    logits by rounding at most; in 32-bit, where one kernel serves every cut,
+    not at all."""
+    name = "B"
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    reqs = {f"q{i}": traces.random_tokens(500 + i, n, V) for i, n in enumerate([60, 90, 33, 120, 75])}
+    alone, _ = run_trace(d, dtype, name, traces.whole(reqs), tmp_path / "alone")
+    prompt_len = {rid: len(t) - 16 for rid, t in reqs.items()}
+    steps = traces.mixed(reqs, prompt_len, seed=9)
+    mix, _ = run_trace(d, dtype, name, steps, tmp_path / "mix", max_tokens=traces.peak_tokens(steps))
+    worst = 0.0
+    for rid in reqs:
+        for p in range(len(reqs[rid])):
+            worst = max(worst, float(np.abs(mix[rid][p] - alone[rid][p]).max()))
+    assert worst <= (0.0 if dtype == "float32" else TOL[dtype]), worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_dirs, tmp_path, dtype):
+    """A short prompt, then hundreds of tokens one by one, to the last position
+    the model has."""
+    name = "C"
+    d = model_dirs(name, STORE[dtype])
+    P, V = TINY[name]["n_positions"], TINY[name]["vocab_size"]
+    toks = traces.random_tokens(77, P, V)
+    reqs = {"long": toks}
+    steps = traces.tail_decoded(reqs, n_tail=P - 24)
+    got, _ = run_trace(d, dtype, name, steps, tmp_path, max_step_tokens=64)
+    err, where = traces.max_error(got, reference(d, reqs))
+    assert err < TOL[dtype], f"long decoding: max error {err} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_dirs, tmp_path, name, dtype):
+    """Position 0 alone, then position 1, 2, ...: the shortest contexts."""
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    reqs = {"s": traces.random_tokens(5, 6, V), "t": traces.random_tokens(6, 2, V)}
+    steps = traces.tail_decoded(reqs, n_tail=64)
+    got, _ = run_trace(d, dtype, name, steps, tmp_path)
+    err, where = traces.max_error(got, reference(d, reqs))
+    assert err < TOL[dtype], f"first tokens: max error {err} at {where}"
+
+
+def test_want_subset_and_empty_want(model_dirs, tmp_path):
+    """Logits only where asked: a subset of places, and steps that want nothing."""
+    name, dtype = "A", "float32"
+    d = model_dirs(name)
+    V = TINY[name]["vocab_size"]
+    toks = traces.random_tokens(3, 40, V)
+    steps = [
+        {"step": 0, "entries": [{"id": "x", "tokens": toks[:20], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "x", "tokens": toks[20:], "want": [19, 0, 7]}], "end": ["x"]},
+    ]
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.engine.replay import replay
+    eng = Engine.from_dir(d, dtype=dtype, page_size=16, n_pages=4, max_requests=4, max_step_tokens=64)
+    out = str(tmp_path / "o")
+    replay(eng, traces.to_lines(steps), out)
+    assert not os.path.exists(os.path.join(out, "0.f32"))
+    rows = np.fromfile(os.path.join(out, "1.f32"), dtype="<f4").reshape(3, V)
+    ref = plain_gpt2.forward_dir(d, toks)
+    for r, p in zip(rows, [39, 20, 27]):
+        assert np.abs(r - ref[p]).max() < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, tmp_path, dtype):
+    """The program itself, as a child process fed line by line."""
+    name = "B"
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    reqs = {f"p{i}": traces.random_tokens(40 + i, n, V) for i, n in enumerate([45, 70, 12, 100, 64, 30])}
+    prompt_len = {rid: max(2, len(t) - 10) for rid, t in reqs.items()}
+    steps = traces.mixed(reqs, prompt_len, seed=1)
+    out = str(tmp_path / "out")
+    # page size 8 of tiny B divides 64
+    proc = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+                             "--out", out, "--max-tokens", str(traces.peak_tokens(steps)),
+                             "--page-size", str(PAGE_SIZE[name])],
+                            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+    for st, line in zip(steps, traces.to_lines(steps)):
+        proc.stdin.write(line + "\n")
+        proc.stdin.flush()
+        assert proc.stdout.readline().strip() == f"done {st['step']}"
+    proc.stdin.close()
+    assert proc.wait(timeout=120) == 0
+    got = traces.collect(steps, out, V)
+    err, where = traces.max_error(got, reference(d, reqs))
+    assert err < TOL[dtype], f"trace_run: max error {err} at {where}"

@@ -1,0 +1,314 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of GPT-2 small (n_layer 12, n_embd 768,
+n_head 12, n_inner 3072, vocab 50257, positions 1024) with random weights in
+bfloat16, a batch of 8 requests decoding at a context of 512 tokens, pages of
+16.  A "step" is one decode step of the whole batch.  One JSON line is printed:
+`value` is decoded tokens a second with the step timed on the device (CUDA
+events around every step, L2 flushed between steps); `e2e` is the same through
+the Python entry point (scheduler, host token ids in and out); `prefill` is one
+step of 2,048 prompt tokens (2 x 1,024); `roofline` is the decode step's bytes
+(every weight once, the cache of the live requests) over its time, against the
+measured copy bandwidth; `points` has decode at batch 1 and 64.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMALL = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=12, n_embd=768, n_head=12,
+             n_inner=3072, vocab_size=50257, n_positions=1024, layer_norm_epsilon=1e-5,
+             activation_function="gelu_new")
+CONTEXT = 512
+BATCH = 8
+PAGE = 16
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_bytes_flops(cfg, batch, context, elem=2):
+    """Bytes a decode step has to read (every weight it uses once, the cache of
+    the live requests) and the flops of a prefill of T tokens as n prompts."""
+    E, I, L, V, H = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"], cfg["vocab_size"], cfg["n_head"]
+    mats = L * (E * 3 * E + E * E + E * I + I * E)
+    vecs = L * (3 * E + E + I + E + 4 * E) + 2 * E
+    weights = (mats + V * E) * elem + vecs * 4 + batch * E * elem      # + the position rows used
+    kv = batch * context * L * 2 * E * elem
+    return weights + kv
+
+
+def prefill_flops(cfg, n_prompts, prompt_len):
+    E, I, L, V = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"], cfg["vocab_size"]
+    T = n_prompts * prompt_len
+    gemm = 2 * T * L * (E * 3 * E + E * E + 2 * E * I)
+    attn = n_prompts * L * 4 * E * (prompt_len * (prompt_len + 1) // 2)
+    head = 2 * n_prompts * V * E
+    return gemm + attn + head
+
+
+def make_model(tmp, cfg_d, n_layer=None):
+    from sglang_c_b200.config import resolve_architecture
+    from sglang_c_b200.weights import write_random_model
+    d = dict(cfg_d)
+    if n_layer is not None:
+        d["n_layer"] = n_layer
+    arch = resolve_architecture(d)
+    cfg = arch.config_class.from_dict(d)
+    return write_random_model(os.path.join(tmp, "model"), arch, cfg, 1234, scheme="standard",
+                              store_dtype="bfloat16")
+
+
+def time_decode(eng, batch, context, steps, warmup, flush):
+    """Device time of `steps` decode steps of `batch` requests that hold `context`
+    tokens each; returns (ms per step list, launches per step)."""
+    import numpy as np
+    import torch
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.engine import StepEntry
+    from sglang_c_b200.sampling import Sampler, SamplingParams
+    V = eng.plan.vocab_size
+    rng = np.random.default_rng(batch)
+    reqs = [f"b{batch}_{i}" for i in range(batch)]
+    for r in reqs:
+        eng.add_request(r)
+    # fill the context in portions
+    todo = {r: [int(t) for t in rng.integers(0, V, size=context)] for r in reqs}
+    done = 0
+    while done < context:
+        n = min(eng.max_step_tokens // batch, context - done)
+        eng.step([StepEntry(r, todo[r][done:done + n], []) for r in reqs])
+        done += n
+    sampler = Sampler(eng.rt.device, max(batch, 1))
+    sp = [SamplingParams(temperature=0.0)] * batch
+    toks = [int(t) for t in rng.integers(0, V, size=batch)]
+    times = []
+    launches = 0
+    for it in range(warmup + steps):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ops.LAUNCHES
+        e0.record()
+        logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(reqs, toks)])
+        ops.sample(logits, sampler.d_params[:batch], sampler.d_hist_tok, sampler.d_hist_cnt,
+                   sampler.d_out[:batch])
+        e1.record()
+        torch.cuda.synchronize()
+        toks = sampler.d_out[:batch].tolist()
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1))
+            launches += ops.LAUNCHES - l0
+    for r in reqs:
+        eng.end_request(r)
+    return times, launches
+
+
+def time_prefill(eng, n_prompts, prompt_len, reps, warmup, flush):
+    import numpy as np
+    import torch
+    from sglang_c_b200.engine import StepEntry
+    V = eng.plan.vocab_size
+    rng = np.random.default_rng(99)
+    times = []
+    for it in range(warmup + reps):
+        reqs = [f"p{it}_{i}" for i in range(n_prompts)]
+        for r in reqs:
+            eng.add_request(r)
+        entries = [StepEntry(r, [int(t) for t in rng.integers(0, V, size=prompt_len)], [prompt_len - 1])
+                   for r in reqs]
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step(entries)
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1))
+        for r in reqs:
+            eng.end_request(r)
+    return times
+
+
+def time_e2e(model_dir, batch, context, steps, warmup):
+    """The same decode through the Python entry point: token ids on the host in,
+    token ids on the host out, every step."""
+    import numpy as np
+    import torch
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    s = sched_new(model_dir, seed=0, dtype="bfloat16", page_size=PAGE,
+                  max_tokens=batch * (context + steps + warmup + 64), max_requests=max(batch, 1),
+                  max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
+    V = s.engine.plan.vocab_size
+    rng = np.random.default_rng(5)
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+    for _ in range(batch):
+        s.submit_ids([int(t) for t in rng.integers(0, V, size=context)], warmup + steps + 32, sp)
+    while any(r.n_pending != 1 or r.n_computed == 0 for r in s.running) or s.waiting:
+        s.step()                                   # prompts done; every request decodes from here
+    for _ in range(warmup):
+        s.step()
+    torch.cuda.synchronize()
+    n0 = s.stats.decode_tokens
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        s.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = s.engine.bufs.total * 4 + batch * 40      # the packed step data and the sampling records
+    d2h = batch * 4                                 # the sampled token ids
+    return (s.stats.decode_tokens - n0) / dt, h2d, d2h
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "integemjack/sglang.c is a C/CMake project without a Python package: "
+                          "pip install of /root/reference finds no setup.py or pyproject.toml"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.engine import Engine
+    pk = peaks()
+    n_layer = args.layers or SMALL["n_layer"]
+    cfg_d = dict(SMALL, n_layer=n_layer)
+    tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+    model_dir = make_model(tmp, SMALL, n_layer)
+    eng = Engine.from_dir(model_dir, dtype="bfloat16", page_size=PAGE,
+                          max_tokens=64 * (CONTEXT + 256), max_requests=64, max_step_tokens=PREFILL_TOKENS)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")     # larger than the 126 MB L2
+
+    # warm every path once (compiles on a fresh checkout) before the clocks are watched
+    time_decode(eng, BATCH, 32, 2, 3, None)
+    clocks = ClockSampler()
+    clocks.start()
+    times, launches = time_decode(eng, BATCH, CONTEXT, steps, warmup, flush)
+    clk = clocks.stop()
+    ms = sum(times) / len(times)
+    value = BATCH / (ms / 1e3)
+    nbytes = model_bytes_flops(cfg_d, BATCH, CONTEXT + steps // 2)
+    achieved = nbytes / (ms / 1e3) / 1e9
+
+    pt = time_prefill(eng, 2, PREFILL_TOKENS // 2, 5, 3, flush)
+    pms = sum(pt) / len(pt)
+    pflops = prefill_flops(cfg_d, 2, PREFILL_TOKENS // 2)
+    prefill = {"value": PREFILL_TOKENS / (pms / 1e3), "tokens": PREFILL_TOKENS, "ms": pms,
+               "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"]}
+
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            t, _ = time_decode(eng, b, CONTEXT, min(steps, 32), warmup, flush)
+            points[f"decode_b{b}"] = b / (sum(t) / len(t) / 1e3)
+    del eng
+    torch.cuda.empty_cache()
+    e2e_value, h2d, d2h = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
+
+    out = {
+        "metric": "decode tok/s at batch 8, context 512 (GPT-2 small layer sizes, random weights)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+        "config": {"model": "gpt2-small layer sizes, random weights", "n_layer": n_layer,
+                   "n_layer_full": SMALL["n_layer"], "n_embd": SMALL["n_embd"], "n_head": SMALL["n_head"],
+                   "n_inner": SMALL["n_inner"], "vocab_size": SMALL["vocab_size"],
+                   "n_positions": SMALL["n_positions"], "global_batch": BATCH, "seq_len": CONTEXT,
+                   "page_size": PAGE, "parallelism": "none (1 GPU)", "prefill_tokens": PREFILL_TOKENS,
+                   "prefill_shape": "2 prompts x 1024", "l2": "flushed between timed steps",
+                   "timing": "CUDA events per step, mean", "cuda_graph": "decode step replays a graph",
+                   "peaks": pk["source"]},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "of": pk["source"], "bytes_per_step": nbytes},
+        "points": points,
+        "clocks": clk,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

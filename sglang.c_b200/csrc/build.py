@@ -22,7 +22,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 
-_lock = threading.Lock()
+_lock = threading.RLock()
 _loaded = {}
 
 
@@ -42,19 +42,26 @@ def _nvcc():
                      "the CUDA kernels of this engine cannot be built")
 
 
+_dir = None
+
+
 def _build_dir():
-    d = os.path.join(_HERE, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"sglc_b200_build_{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    """csrc/_build if it can be written, else a per-user folder under the
+    temporary directory; decided once per process."""
+    global _dir
+    with _lock:
+        if _dir is None:
+            d = os.path.join(_HERE, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(dir=d)
+                os.close(fd)
+                os.remove(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"sglc_b200_build_{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _dir = d
+        return _dir
 
 
 def _digest(name):
@@ -84,7 +91,7 @@ def build(name, verbose=False):
         with open(stamp) as f:
             if f.read().strip() == want:
                 return out
-    tmp = out + f".tmp{os.getpid()}"
+    tmp = out + f".tmp{os.getpid()}_{threading.get_ident()}"
     cmd = [_nvcc()] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, src]
     t0 = time.time()
     print(f"[sglc_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)

@@ -13,6 +13,10 @@ ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 
+# how many kernels of this package were launched (bench and tests read it)
+LAUNCHES = 0
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -39,7 +43,9 @@ def _need_cuda(*tensors):
                               "(this engine has no CPU path)")
 
 
-def _check(lib, code, what):
+def _check(lib, code, what, n_kernels=1):
+    global LAUNCHES
+    LAUNCHES += n_kernels
     if code != 0:
         msg = lib.sglc_error_string(code).decode()
         raise KernelError(f"{what}: {msg} (code {code})")

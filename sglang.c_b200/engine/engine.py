@@ -24,7 +24,7 @@ class OutOfPages(RuntimeError):
 
 class Engine:
     def __init__(self, plan, runtime, page_size=16, n_pages=None, max_tokens=None, max_requests=64,
-                 max_step_tokens=2048, model_dir=None):
+                 max_step_tokens=2048, model_dir=None, use_graphs=True):
         self.rt = runtime
         self.plan = plan
         self.model = Model(plan, runtime)
@@ -48,6 +48,12 @@ class Engine:
         self.ws = Workspace(runtime.device, self._workspace_bytes())
         self.logits = None
         self.steps_run = 0
+        # decode-only steps (one token per request, every row wanted) replay a CUDA graph
+        # captured per batch size; the first such step of a size runs eagerly as warm-up
+        self.use_graphs = bool(use_graphs)
+        self._graphs = {}
+        self._graph_seen = set()
+        self.graph_replays = 0
 
     # -- construction ---------------------------------------------------------
     @classmethod
@@ -196,10 +202,44 @@ class Engine:
                                             b.dview(f"slots{gi}", T), self.page_size))
             else:
                 ctx.groups.append(None)
-        self.ws.reset()
-        logits = self.model.forward(ctx, self.cache, self._logits_buffer(nw))
+        out = self._logits_buffer(nw)
+        decode_only = (T == R and nw == R and all(e.want == [0] for e in entries))
+        if self.use_graphs and decode_only:
+            logits = self._forward_graphed(ctx, out)
+        else:
+            self.ws.reset()
+            logits = self.model.forward(ctx, self.cache, out)
         self.steps_run += 1
         return logits
+
+    def _forward_graphed(self, ctx, out):
+        from ..csrc import ops
+        # shared memory of the attention kernels is sized for the longest context the model has
+        ctx.max_keys = self.plan.max_positions
+        key = ctx.R
+        if key in self._graphs:
+            graph, n_launches = self._graphs[key]
+            graph.replay()
+            ops.LAUNCHES += n_launches
+            self.graph_replays += 1
+            return out[:ctx.n_want]
+        if key not in self._graph_seen:
+            self._graph_seen.add(key)
+            self.ws.reset()
+            return self.model.forward(ctx, self.cache, out)
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        before = ops.LAUNCHES
+        with torch.cuda.graph(graph):
+            self.ws.reset()
+            self.model.forward(ctx, self.cache, out)
+        n_launches = ops.LAUNCHES - before
+        ops.LAUNCHES = before
+        self._graphs[key] = (graph, n_launches)
+        graph.replay()
+        ops.LAUNCHES += n_launches
+        self.graph_replays += 1
+        return out[:ctx.n_want]
 
     def check_device_errors(self):
         """Raise if a kernel flagged corrupted step data (synchronises)."""

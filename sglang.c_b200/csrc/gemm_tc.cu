@@ -1,0 +1,443 @@
+// bfloat16 GEMM on the 5th-generation tensor cores:
+//   C[M,N] = A[M,K] · W[N,K]^T (+ bias[N]) with an optional GELU, stored as bfloat16 or float,
+//   or added into the 32-bit residual stream in place.
+// Operands arrive in shared memory by TMA (128-byte swizzle, K-major), one elected thread
+// issues tcgen05.mma with float accumulators in tensor memory, and four warps read the
+// accumulators back with tcgen05.ld for the fused epilogue.  The reference reaches the
+// tensor cores only through cuBLAS (gemm_nt_cublas, src/cuda_backend.cu:2843-2903) and adds
+// bias, GELU and the residual with separate kernels (k_fill_bias :2642, k_gelu :527,
+// k_residual :2405); its small-M products are one-block-per-output GEMVs (:333-349,412-427).
+//
+// One kernel serves both regimes through the choice of which matrix is the MMA's 128-row
+// operand ("P") and which its N operand ("Q", tile of BN rows):
+//   many tokens  (prefill): P = A (128 tokens per tile),  Q = W (BN output features per tile)
+//   few tokens   (decode):  P = W (128 features per tile), Q = A (all tokens, padded to BN),
+//                           with the K range split across blocks so that every SM streams
+//                           weights.  The blocks of one tile leave float partial sums in a
+//                           workspace; the block that arrives last adds them in split order
+//                           (a fixed order: the result does not depend on timing) and runs
+//                           the epilogue.
+// Sizes: K a multiple of 8 and 16-byte aligned rows (TMA's rule); M, N anything (edges are
+// zero-filled on load and masked on store).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+namespace {
+using namespace tc;
+
+constexpr int BM = 128;   // rows of P per tile = MMA M = TMEM lanes
+constexpr int BK = 64;    // K per stage: 128 bytes of bfloat16, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr int MAX_STAGES = 8;
+
+struct GemmArgs {
+  int M, N, K;             // logical sizes
+  int P_rows, Q_rows;      // rows of the two operands as mapped (P: 128-row operand)
+  int swap;                // 0: P = A (tokens), Q = W (features); 1: P = W, Q = A
+  int kb_total;            // K blocks of 64
+  int kb_per_split;        // K blocks per split (grid.z splits)
+  int splits;
+  int stages;
+  const float* bias;       // [N] or null
+  void* out;               // [M][ldo], bfloat16 or float
+  float* residual;         // float [M][ldo], updated in place (then `out` is unused)
+  int ldo;
+  int out_f32;             // out is float
+  int act;
+  float* ws;               // split-K partial sums: [tile][split][BN][128] floats
+  int* counters;           // one per tile, zero between launches
+  int* err;                // set to 1 if a bounded wait ran out
+};
+
+struct SharedCtl {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t accum;
+  uint32_t tmem_base;
+  int abort_flag;
+  int is_last;
+};
+
+template <int BN>
+__device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, int q0, const float* v,
+                                               int nq) {
+  // v[j]: value at (p_glob, q0 + j), already reduced over K; applies bias, activation, store.
+  if (a.swap) {
+    int n = p_glob;
+    if (n >= a.N) return;
+    float b = a.bias ? a.bias[n] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < nq; j++) {
+      int m = q0 + j;
+      if (m >= a.M) break;
+      float x = apply_act(v[j] + b, a.act);
+      size_t o = (size_t)m * a.ldo + n;
+      if (a.residual) a.residual[o] += x;
+      else if (a.out_f32) ((float*)a.out)[o] = x;
+      else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(x);
+    }
+  } else {
+    int m = p_glob;
+    if (m >= a.M) return;
+    size_t row = (size_t)m * a.ldo;
+    bool vec_ok = (q0 + nq <= a.N);
+    if (a.residual) {
+      float* dst = a.residual + row + q0;
+      if (vec_ok && ((uintptr_t)dst & 15) == 0 && nq % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < nq; j += 4) {
+          float4 r = *reinterpret_cast<float4*>(dst + j);
+          r.x += v[j] + (a.bias ? a.bias[q0 + j] : 0.0f);
+          r.y += v[j + 1] + (a.bias ? a.bias[q0 + j + 1] : 0.0f);
+          r.z += v[j + 2] + (a.bias ? a.bias[q0 + j + 2] : 0.0f);
+          r.w += v[j + 3] + (a.bias ? a.bias[q0 + j + 3] : 0.0f);
+          *reinterpret_cast<float4*>(dst + j) = r;
+        }
+      } else {
+        for (int j = 0; j < nq && q0 + j < a.N; j++)
+          dst[j] += v[j] + (a.bias ? a.bias[q0 + j] : 0.0f);
+      }
+    } else if (a.out_f32) {
+      float* dst = (float*)a.out + row + q0;
+      for (int j = 0; j < nq && q0 + j < a.N; j++)
+        dst[j] = apply_act(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act);
+    } else {
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + row + q0;
+      if (vec_ok && ((uintptr_t)dst & 15) == 0 && nq % 8 == 0) {
+#pragma unroll
+        for (int j = 0; j < nq; j += 8) {
+          __align__(16) __nv_bfloat162 h[4];
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            float x0 = apply_act(v[j + 2 * t] + (a.bias ? a.bias[q0 + j + 2 * t] : 0.0f), a.act);
+            float x1 =
+                apply_act(v[j + 2 * t + 1] + (a.bias ? a.bias[q0 + j + 2 * t + 1] : 0.0f), a.act);
+            h[t] = __floats2bfloat162_rn(x0, x1);
+          }
+          *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(h);
+        }
+      } else {
+        for (int j = 0; j < nq && q0 + j < a.N; j++)
+          dst[j] = __float2bfloat16_rn(apply_act(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act));
+      }
+    }
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // stage buffers need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int P_BYTES = BM * BK * 2;
+  constexpr int Q_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  __shared__ SharedCtl ctl;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pt = blockIdx.x, qt = blockIdx.y, split = blockIdx.z;
+  const int kb0 = split * a.kb_per_split;
+  const int kb1 = min(a.kb_total, kb0 + a.kb_per_split);
+  const int n_kb = kb1 - kb0;
+  const int stages = a.stages;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; s++) {
+      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.empty[s], 1);
+    }
+    mbar_init(&ctl.accum, 1);
+    ctl.abort_flag = 0;
+    ctl.is_last = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_p);
+    tma_prefetch_desc(&map_q);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (elect_one()) {
+      int issued = 0;
+      for (int i = 0; i < n_kb; i++) {
+        int s = i % stages;
+        if (i >= stages && !mbar_wait(&ctl.empty[s], ((i / stages) - 1) & 1, abort_flag)) break;
+        uint8_t* sp = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&ctl.full[s], STAGE_BYTES);
+        tma_load_2d(sp, &map_p, &ctl.full[s], (kb0 + i) * BK, pt * BM);
+        tma_load_2d(sp + P_BYTES, &map_q, &ctl.full[s], (kb0 + i) * BK, qt * BN);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // wait, with a limit, for the copies still in flight before the block may exit
+        for (int i = max(0, issued - stages); i < issued; i++)
+          mbar_wait(&ctl.full[i % stages], (i / stages) & 1, abort_flag);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < n_kb && ok; i++) {
+        int s = i % stages;
+        ok = mbar_wait(&ctl.full[s], (i / stages) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        uint64_t dp = smem_desc_k_sw128(sp);
+        uint64_t dq = smem_desc_k_sw128(sp + P_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; k++) {
+          // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+          mma_bf16(tmem_base, dp + 2 * k, dq + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&ctl.empty[s]);    // the stage is free once these MMAs have read it
+      }
+      if (ok) mma_commit(&ctl.accum);   // accumulator complete
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+    const int lane_base = (warp & 3) * 32;
+    const int p_glob = pt * BM + lane_base + lane;
+    bool ok = n_kb > 0 ? mbar_wait(&ctl.accum, 0, abort_flag) : true;
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16);
+    constexpr int CH = BN < 32 ? 16 : 32;
+    if (ok && a.splits == 1) {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CH) {
+        float v[CH];
+        if (n_kb > 0) {
+          if constexpr (CH == 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; j++) v[j] = 0.0f;
+        }
+        epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
+      }
+    } else if (ok) {
+      // split-K: leave this block's partial sums, then the last block of the tile reduces
+      const int tile = qt * gridDim.x + pt;
+      float* wsp = a.ws + ((size_t)tile * a.splits + split) * (size_t)(BN * BM);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CH) {
+        uint32_t r[CH];
+        if (n_kb > 0) {
+          if constexpr (CH == 32) tmem_ld_32x32(taddr + c, (uint32_t(&)[32])r);
+          else tmem_ld_32x16(taddr + c, (uint32_t(&)[16])r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; j++) r[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < CH; j++)
+          wsp[(size_t)(c + j) * BM + lane_base + lane] = __uint_as_float(r[j]);
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        int old = atomicAdd(&a.counters[tile], 1);
+        ctl.is_last = (old == a.splits - 1);
+        if (old == a.splits - 1) a.counters[tile] = 0;   // ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ctl.is_last) {
+        __threadfence();
+        const float* base = a.ws + (size_t)tile * a.splits * (size_t)(BN * BM);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CH) {
+          float v[CH];
+#pragma unroll
+          for (int j = 0; j < CH; j++) v[j] = 0.0f;
+          for (int s = 0; s < a.splits; s++) {
+            const float* sp = base + (size_t)s * (BN * BM) + lane_base + lane;
+#pragma unroll
+            for (int j = 0; j < CH; j++) v[j] += __ldcg(sp + (size_t)(c + j) * BM);
+          }
+          epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.base;
+    h = h * 1315423911u + k.rows;
+    h = h * 1315423911u + k.cols;
+    h = h * 1315423911u + k.ld;
+    h = h * 1315423911u + k.box_rows;
+    return h;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+             uint32_t box_rows) {
+  MapKey key{base, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return true;
+  }
+  CUtensorMap m;
+  if (!make_map_bf16_2d(&m, base, rows, cols, ld, box_rows)) return false;
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return true;
+}
+
+template <int BN>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3 grid,
+           cudaStream_t stream) {
+  size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2) + 1024;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(mp, mq, a);
+  return sglc_launch_status();
+}
+}  // namespace
+
+// Split-K scratch a call may need, in floats and counters, for the plan the launcher would
+// choose; lets the caller size one workspace for all its GEMMs.
+static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split,
+                 int* tiles_p, int* tiles_q) {
+  int kb_total = (K + BK - 1) / BK;
+  if (M <= 128) {
+    *swap = 1;
+    *bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+    *tiles_p = (N + BM - 1) / BM;
+    *tiles_q = 1;
+    int want = (2 * 148) / (*tiles_p);
+    if (want < 1) want = 1;
+    if (want > kb_total) want = kb_total;
+    int per = (kb_total + want - 1) / want;
+    *kb_per_split = per;
+    *splits = (kb_total + per - 1) / per;
+  } else {
+    *swap = 0;
+    int tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    *bn = (tiles128 >= 148 || N <= 64) ? 128 : 64;
+    *tiles_p = (M + BM - 1) / BM;
+    *tiles_q = (N + *bn - 1) / *bn;
+    *splits = 1;
+    *kb_per_split = kb_total;
+  }
+}
+
+// Floats of workspace and number of counters the call (M,N,K) needs (0,0 without split-K).
+SGLC_API int sglc_gemm_tc_scratch(int M, int N, int K, long long* ws_floats, int* n_counters) {
+  int swap, bn, splits, per, tp, tq;
+  plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
+  *ws_floats = splits > 1 ? (long long)tp * tq * splits * bn * BM : 0;
+  *n_counters = splits > 1 ? tp * tq : 0;
+  return SGLC_OK;
+}
+
+// A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
+// null; out [M,N] rows ldo apart (bfloat16, or float if out_f32), or residual (float, in place).
+// ws / counters: scratch of at least sglc_gemm_tc_scratch's sizes (counters zeroed once; the
+// kernel leaves them zero).  err: device int, set to 1 if a wait ran out.
+SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void* out,
+                          float* residual, int M, int N, int K, int lda, int ldo, int out_f32,
+                          int act, float* ws, int* counters, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return SGLC_OK;
+  if (K <= 0) return SGLC_ERR_ARGUMENT;
+  if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+    return SGLC_ERR_UNSUPPORTED;
+  int swap, bn, splits, per, tp, tq;
+  plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
+  if (splits > 1 && (!ws || !counters)) return SGLC_ERR_ARGUMENT;
+  GemmArgs a;
+  a.M = M; a.N = N; a.K = K;
+  a.swap = swap;
+  a.kb_total = (K + BK - 1) / BK;
+  a.kb_per_split = per;
+  a.splits = splits;
+  a.bias = bias; a.out = out; a.residual = residual; a.ldo = ldo; a.out_f32 = out_f32; a.act = act;
+  a.ws = ws; a.counters = counters; a.err = err;
+  CUtensorMap mp, mq;
+  bool ok;
+  if (swap) {
+    a.P_rows = N; a.Q_rows = M;
+    ok = get_map(&mp, W, N, K, K, BM) && get_map(&mq, A, M, K, lda, bn);
+  } else {
+    a.P_rows = M; a.Q_rows = N;
+    ok = get_map(&mp, A, M, K, lda, BM) && get_map(&mq, W, N, K, K, bn);
+  }
+  if (!ok) return SGLC_ERR_UNSUPPORTED;
+  int stage_bytes = BM * BK * 2 + bn * BK * 2;
+  int budget = swap ? 96 * 1024 : (bn == 128 ? 100 * 1024 : 100 * 1024);
+  int stages = budget / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  if (stages > per) stages = per;
+  if (stages < 1) stages = 1;
+  a.stages = stages;
+  dim3 grid(tp, tq, splits);
+  switch (bn) {
+    case 16: return launch<16>(mp, mq, a, grid, stream);
+    case 32: return launch<32>(mp, mq, a, grid, stream);
+    case 64: return launch<64>(mp, mq, a, grid, stream);
+    case 128: return launch<128>(mp, mq, a, grid, stream);
+  }
+  return SGLC_ERR_ARGUMENT;
+}

@@ -177,28 +177,66 @@ def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, sc
 
 
 # ---------------------------------------------------------------------------
-# tensor-core GEMM (bfloat16): filled in by gemm_tc.cu's bindings
+# tensor-core GEMM (bfloat16, tcgen05 + TMA)
+_tc_scratch = {}
+TC_WS_FLOATS = 8 << 20          # 32 MB of split-K partial sums
+TC_COUNTERS = 8192
+
+
+def _tc_buffers(device):
+    """Split-K workspace, tile counters (zero between launches) and the error word of the
+    tensor-core kernels, one set per device, allocated at first use."""
+    b = _tc_scratch.get(device)
+    if b is None:
+        b = (torch.empty(TC_WS_FLOATS, dtype=torch.float32, device=device),
+             torch.zeros(TC_COUNTERS, dtype=torch.int32, device=device),
+             torch.zeros(1, dtype=torch.int32, device=device))
+        _tc_scratch[device] = b
+    return b
+
+
+def tc_error_flag(device):
+    return _tc_buffers(device)[2]
+
+
 def gemm_tc_supported(a, w):
-    return False
+    """TMA needs 16-byte aligned rows: K and the row stride multiples of 8 elements."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2
+            and a.shape[1] % 8 == 0 and a.stride(1) == 1 and a.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
 
 def gemm_tc(a, w, bias, out=None, residual=None, act=None):
-    raise KernelError("the tensor-core GEMM is not built")
-
-
-def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
-    """One token per row of `logits` ([n, V] float32, row stride free; penalties
-    change the rows in place).  `params`: int32 tensor [n, 10] holding the packed
-    per-row records (see sampling.cu); hist_tok/hist_cnt: int32 (token, count)
-    pairs of the rows' histories."""
-    _need_cuda(logits, params, hist_tok, hist_cnt, out_tok, out_logprob)
-    n, V = logits.shape
-    if logits.dtype != torch.float32 or logits.stride(1) != 1:
-        raise KernelError("sample: logits must be float32 rows")
-    if params.dtype != torch.int32 or params.shape != (n, 10) or not params.is_contiguous():
-        raise KernelError("sample: params must be a contiguous int32 [n,10] tensor")
-    _i32(out_tok, "out_tok")
-    lib = build.load("sampling")
-    code = lib.sglc_sample(_ptr(logits), logits.stride(0), V, n, _ptr(params), _ptr(hist_tok),
-                           _ptr(hist_cnt), _ptr(out_tok), _ptr(out_logprob), _stream())
-    _check(lib, code, "sample")
+    """out = act(a·wᵀ + bias) (bfloat16 or float32), or residual += a·wᵀ + bias, on the
+    tensor cores.  a [M,K] bfloat16 (row stride free), w [N,K] bfloat16 contiguous."""
+    _need_cuda(a, w, bias, out, residual)
+    if not gemm_tc_supported(a, w):
+        raise KernelError(f"gemm_tc: operands a {tuple(a.shape)} stride {a.stride()} / w {tuple(w.shape)} "
+                          "do not meet the 16-byte row rule of TMA (K and row stride multiples of 8)")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_tc: a {tuple(a.shape)} and w {tuple(w.shape)} do not match")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_tc: bias must be a float32 vector of N")
+    dst = residual if residual is not None else out
+    if dst is None or dst.shape[0] < M or dst.shape[1] != N or dst.stride(1) != 1:
+        raise KernelError("gemm_tc: output does not match [M,N]")
+    if residual is not None:
+        if residual.dtype != torch.float32:
+            raise KernelError("gemm_tc: the residual stream is float32")
+        if act not in (None, "none"):
+            raise KernelError("gemm_tc: no activation when adding into the residual stream")
+    elif dst.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_tc: output must be float32 or bfloat16")
+    lib = build.load("gemm_tc")
+    ws, counters, err = _tc_buffers(a.device)
+    need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
+    lib.sglc_gemm_tc_scratch(M, N, K, ctypes.byref(need_ws), ctypes.byref(need_c))
+    if need_ws.value > ws.numel() or need_c.value > counters.numel():
+        raise KernelError(f"gemm_tc M={M} N={N} K={K}: split-K scratch of {need_ws.value} floats exceeds "
+                          f"the {ws.numel()} reserved")
+    code = lib.sglc_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
+                            a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
+                            ACT[act], _ptr(ws), _ptr(counters), _ptr(err), _stream())
+    _check(lib, code, f"gemm_tc M={M} N={N} K={K}")

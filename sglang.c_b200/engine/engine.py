@@ -246,3 +246,9 @@ class Engine:
         if int(self.err_flag.item()) != 0:
             self.err_flag.zero_()
             raise RuntimeError("a kernel met an out-of-range token or position id")
+        if self.rt.dtype == "bfloat16":
+            from ..csrc import ops
+            flag = ops.tc_error_flag(self.rt.device)
+            if int(flag.item()) != 0:
+                flag.zero_()
+                raise RuntimeError("a tensor-core kernel gave up on a bounded wait; its output is invalid")

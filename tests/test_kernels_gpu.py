@@ -301,3 +301,56 @@ def test_sampling_penalties_and_logprob():
     assert abs(lps[1] - float(torch.log_softmax(l1, 0)[toks[1]])) < 1e-4
     assert toks[2] == int(logits[2].argmax())
     assert abs(lps[2] - float(torch.log_softmax(logits[2].double(), 0)[toks[2]])) < 1e-4
+
+
+GEMM_TC_SHAPES = [
+    # M, N, K: few tokens (weights on the MMA's 128-row side, split-K) and many tokens
+    (1, 768, 768), (8, 2304, 768), (8, 768, 3072), (16, 3072, 768), (17, 100, 64), (64, 768, 768),
+    (33, 1000, 96), (100, 320, 96), (128, 50257, 64), (3, 96, 320), (5, 777, 128), (128, 128, 128),
+    (129, 768, 768), (300, 2304, 768), (2048, 768, 3072), (1000, 1000, 200), (257, 96, 320),
+    (512, 50257 // 8, 96), (130, 72, 8), (2, 8, 8),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_TC_SHAPES)
+def test_gemm_tc(M, N, K):
+    """The tcgen05 GEMM against a float64 product of the same bfloat16 operands."""
+    ops = _ops()
+    a, w, bias = _rand(M, K, dtype=torch.bfloat16, seed=20), _rand(N, K, dtype=torch.bfloat16, seed=21, scale=0.1), _rand(N, seed=22)
+    assert ops.gemm_tc_supported(a, w)
+    ref = a.double() @ w.double().t() + bias.double()
+    tol32 = 2e-5 * math.sqrt(K) + 1e-5
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_tc(a, w, bias, out=out)
+    assert float((out.double() - ref).abs().max()) < tol32
+    outb = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(a, w, bias, out=outb, act="gelu_tanh")
+    want = torch.nn.functional.gelu(ref, approximate="tanh")
+    assert float((outb.double() - want).abs().max()) < tol32 + 8e-3 * float(want.abs().max())
+    ops.gemm_tc(a, w, None, out=outb, act="gelu_erf")
+    want = torch.nn.functional.gelu(ref - bias.double())
+    assert float((outb.double() - want).abs().max()) < tol32 + 8e-3 * float(want.abs().max())
+    res = _rand(M, N, seed=23)
+    res0 = res.clone()
+    ops.gemm_tc(a, w, bias, residual=res)
+    assert float((res.double() - (res0.double() + ref)).abs().max()) < tol32
+    # the same call twice gives the same bits (the split-K sum has a fixed order)
+    out2 = torch.empty(M, N, device=DEV)
+    ops.gemm_tc(a, w, bias, out=out2)
+    assert torch.equal(out, out2)
+    # strided input rows and a wider output buffer
+    wide = _rand(M, K + 16, dtype=torch.bfloat16, seed=24)
+    big = torch.zeros(M, N + 5, device=DEV)
+    if (K + 16) % 8 == 0:
+        ops.gemm_tc(wide[:, 8:8 + K], w, None, out=big[:, :N])
+        assert float((big[:, :N].double() - wide[:, 8:8 + K].double() @ w.double().t()).abs().max()) < tol32
+        assert float(big[:, N:].abs().max()) == 0.0
+    assert int(ops.tc_error_flag(a.device).item()) == 0
+
+
+def test_gemm_tc_refuses_rows_that_tma_cannot_load():
+    ops = _ops()
+    a, w = _rand(4, 100, dtype=torch.bfloat16), _rand(6, 100, dtype=torch.bfloat16)
+    assert not ops.gemm_tc_supported(a, w)            # K = 100 is not a multiple of 8
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc(a, w, None, out=torch.empty(4, 6, device=DEV))

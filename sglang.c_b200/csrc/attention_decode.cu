@@ -1,0 +1,228 @@
+// Attention for single decoded tokens over the paged bfloat16 cache, with the keys of one
+// query split across blocks (each block: one (token, head, key range)).
+//   s[p] = (q·K_p)*scale; per range: m = max s, e = exp(s-m), l = sum e, o = sum e*V_p;
+//   ranges are merged as  M = max m_i,  o = sum_i o_i*exp(m_i-M) / sum_i l_i*exp(m_i-M)
+// always in range order by the block that finishes last, so the result does not depend on
+// timing.  All arithmetic is 32-bit.  Lengths, positions and block tables are read from
+// device arrays, so the launch has a fixed shape and can be replayed from a CUDA graph.
+// The reference's closest kernels: k_attn_batch (src/cuda_backend.cu:3172-3223, decode over
+// a contiguous cache, scores in shared memory) and k_attn_q_split_partial/_merge
+// (:2056-2185, split keys over a paged, quantised pool with a separate merge launch).
+#include "common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+namespace {
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
+                        const __nv_bfloat16* __restrict__ cache,
+                        const int* __restrict__ block_table, int bt_stride,
+                        const int* __restrict__ token_req, const int* __restrict__ positions,
+                        __nv_bfloat16* __restrict__ out, int o_stride, int T, int H, int Hkv, int D,
+                        int page_size, float scale, int window, int n_splits, int chunk_cap,
+                        float* __restrict__ ws, int* __restrict__ counters) {
+  extern __shared__ float smem[];
+  __shared__ float red[33];
+  __shared__ int s_last;
+  const int t = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
+  float* sq = smem;                     // D
+  float* part = sq + D;                 // WARPS * D
+  float* sc = part + WARPS * D;         // chunk_cap scores
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = token_req[t];
+  const int pos = positions[t];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n = pos - lo + 1;
+  int chunk = (n + n_splits - 1) / n_splits;
+  if (chunk > chunk_cap) chunk = chunk_cap;          // cannot happen when the host sized chunk_cap
+  const int k0 = lo + sp * chunk;
+  int k1 = k0 + chunk;
+  if (k1 > pos + 1) k1 = pos + 1;
+  const int nk = k1 > k0 ? k1 - k0 : 0;
+  const int hk = h / (H / Hkv);
+  const int* bt = block_table + (size_t)r * bt_stride;
+  const size_t page_elems = (size_t)2 * Hkv * page_size * D;
+  const size_t head_off = (size_t)hk * page_size * D;
+  const size_t v_off = (size_t)Hkv * page_size * D;
+
+  const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * D;
+  for (int d = tid; d < D; d += THREADS) sq[d] = __bfloat162float(qp[d]) * scale;
+  __syncthreads();
+
+  // scores: one key per thread, the row read as 16-byte vectors
+  float lmax = -INFINITY;
+  for (int i = tid; i < nk; i += THREADS) {
+    int p = k0 + i;
+    int page = bt[p / page_size];
+    const uint4* kp = reinterpret_cast<const uint4*>(cache + (size_t)page * page_elems + head_off +
+                                                     (size_t)(p % page_size) * D);
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int d8 = 0; d8 < D / 8; d8++) {
+      uint4 u = __ldg(kp + d8);
+      float f[8];
+      bf16x8_to_f32(u, f);
+      const float* qq = sq + d8 * 8;
+      s0 = fmaf(qq[0], f[0], s0); s1 = fmaf(qq[1], f[1], s1);
+      s0 = fmaf(qq[2], f[2], s0); s1 = fmaf(qq[3], f[3], s1);
+      s0 = fmaf(qq[4], f[4], s0); s1 = fmaf(qq[5], f[5], s1);
+      s0 = fmaf(qq[6], f[6], s0); s1 = fmaf(qq[7], f[7], s1);
+    }
+    float s = s0 + s1;
+    sc[i] = s;
+    lmax = fmaxf(lmax, s);
+  }
+  const float m = block_max(lmax, red);
+  float lsum = 0.0f;
+  for (int i = tid; i < nk; i += THREADS) {
+    float e = expf(sc[i] - m);
+    sc[i] = e;
+    lsum += e;
+  }
+  const float l = block_sum(lsum, red);     // also orders the writes of sc before the reads below
+
+  // values: warp w takes keys w, w+WARPS, ...; a lane owns element pairs lane, lane+32, ...
+  float acc[4][2];
+#pragma unroll
+  for (int j = 0; j < 4; j++) acc[j][0] = acc[j][1] = 0.0f;
+  const int D2 = D / 2;
+  for (int i = warp; i < nk; i += WARPS) {
+    int p = k0 + i;
+    int page = bt[p / page_size];
+    const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(
+        cache + (size_t)page * page_elems + v_off + head_off + (size_t)(p % page_size) * D);
+    float w = sc[i];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      int d2 = lane + 32 * j;
+      if (d2 < D2) {
+        float2 v = __bfloat1622float2(vp[d2]);
+        acc[j][0] = fmaf(w, v.x, acc[j][0]);
+        acc[j][1] = fmaf(w, v.y, acc[j][1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    int d2 = lane + 32 * j;
+    if (d2 < D2) {
+      part[warp * D + 2 * d2] = acc[j][0];
+      part[warp * D + 2 * d2 + 1] = acc[j][1];
+    }
+  }
+  __syncthreads();
+
+  __nv_bfloat16* op = out + (size_t)t * o_stride + (size_t)h * D;
+  if (n_splits == 1) {
+    float inv = 1.0f / l;
+    for (int d = tid; d < D; d += THREADS) {
+      float o = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WARPS; w++) o += part[w * D + d];
+      op[d] = __float2bfloat16_rn(o * inv);
+    }
+    return;
+  }
+  // leave (m, l, o) of this range, then the block that arrives last merges all ranges
+  const int rec = D + 2;
+  float* mine = ws + ((size_t)(t * H + h) * n_splits + sp) * rec;
+  for (int d = tid; d < D; d += THREADS) {
+    float o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) o += part[w * D + d];
+    mine[2 + d] = o;
+  }
+  if (tid == 0) {
+    mine[0] = m;
+    mine[1] = l;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int old = atomicAdd(&counters[t * H + h], 1);
+    s_last = (old == n_splits - 1);
+    if (old == n_splits - 1) counters[t * H + h] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* all = ws + (size_t)(t * H + h) * n_splits * rec;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; s++) M = fmaxf(M, __ldcg(all + (size_t)s * rec));
+  float L = 0.0f;
+  for (int s = 0; s < n_splits; s++) {
+    float ms = __ldcg(all + (size_t)s * rec), ls = __ldcg(all + (size_t)s * rec + 1);
+    L += ls > 0.0f ? ls * expf(ms - M) : 0.0f;
+  }
+  float inv = 1.0f / L;
+  for (int d = tid; d < D; d += THREADS) {
+    float o = 0.0f;
+    for (int s = 0; s < n_splits; s++) {
+      float ms = __ldcg(all + (size_t)s * rec), ls = __ldcg(all + (size_t)s * rec + 1);
+      if (ls > 0.0f) o += __ldcg(all + (size_t)s * rec + 2 + d) * expf(ms - M);
+    }
+    op[d] = __float2bfloat16_rn(o * inv);
+  }
+}
+}  // namespace
+
+// Scratch the launch needs: floats of workspace and counters (zero between launches).
+SGLC_API int sglc_attention_decode_scratch(int T, int H, int D, int n_splits, long long* ws_floats,
+                                           int* n_counters) {
+  *ws_floats = n_splits > 1 ? (long long)T * H * n_splits * (D + 2) : 0;
+  *n_counters = n_splits > 1 ? T * H : 0;
+  return SGLC_OK;
+}
+
+// How many key ranges the launcher would use for T tokens of H heads with up to max_keys keys.
+SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
+  long long blocks = (long long)T * H;
+  int want = (int)((2 * 148 + blocks - 1) / blocks);
+  int most = (max_keys + 63) / 64;
+  if (want > most) want = most;
+  if (want > 32) want = 32;
+  if (want < 1) want = 1;
+  return want;
+}
+
+// q, out: bfloat16 rows ([T][q_stride], [T][o_stride]), heads side by side; cache: one layer's
+// bfloat16 pages [n_pages][2][Hkv][page_size][D]; positions[t]: the token's own position (the
+// last key it sees); max_keys: the most keys any token sees (sizes shared memory).
+SGLC_API int sglc_attention_decode(const void* q, int q_stride, const void* cache,
+                                   const int* block_table, int bt_stride, const int* token_req,
+                                   const int* positions, void* out, int o_stride, int T, int H,
+                                   int Hkv, int D, int page_size, float scale, int window,
+                                   int max_keys, int n_splits, float* ws, int* counters,
+                                   cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1)
+    return SGLC_ERR_ARGUMENT;
+  if (D % 8 != 0 || D > 256 || H > 65535 || n_splits > 65535) return SGLC_ERR_UNSUPPORTED;
+  if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return SGLC_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (!ws || !counters)) return SGLC_ERR_ARGUMENT;
+  int eff = window > 0 && window < max_keys ? window : max_keys;
+  int chunk_cap = (eff + n_splits - 1) / n_splits;
+  size_t smem = ((size_t)D + (size_t)WARPS * D + (size_t)chunk_cap) * sizeof(float);
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+  dim3 grid(T, H, n_splits);
+  attention_decode_kernel<<<grid, THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, block_table, bt_stride,
+      token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window,
+      n_splits, chunk_cap, ws, counters);
+  return sglc_launch_status();
+}

@@ -282,10 +282,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           float v[CH];
 #pragma unroll
           for (int j = 0; j < CH; j++) v[j] = 0.0f;
+          // loads of different splits are independent; the additions keep split order
+#pragma unroll 4
           for (int s = 0; s < a.splits; s++) {
             const float* sp = base + (size_t)s * (BN * BM) + lane_base + lane;
+            float t[CH];
 #pragma unroll
-            for (int j = 0; j < CH; j++) v[j] += __ldcg(sp + (size_t)(c + j) * BM);
+            for (int j = 0; j < CH; j++) t[j] = __ldcg(sp + (size_t)(c + j) * BM);
+#pragma unroll
+            for (int j = 0; j < CH; j++) v[j] += t[j];
           }
           epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
         }
@@ -367,7 +372,10 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
     *bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     *tiles_p = (N + BM - 1) / BM;
     *tiles_q = 1;
+    // enough blocks to put most SMs on the weights, but few enough partial sums that the
+    // last block's reduction stays short
     int want = (2 * 148) / (*tiles_p);
+    if (want > 8) want = 8;
     if (want < 1) want = 1;
     if (want > kb_total) want = kb_total;
     int per = (kb_total + want - 1) / want;

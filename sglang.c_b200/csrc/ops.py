@@ -240,3 +240,51 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
                             a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
                             ACT[act], _ptr(ws), _ptr(counters), _ptr(err), _stream())
     _check(lib, code, f"gemm_tc M={M} N={N} K={K}")
+
+
+# ---------------------------------------------------------------------------
+def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
+                     max_keys):
+    """Attention of single decoded tokens (one query per request) over the paged bfloat16
+    cache, keys split across blocks and merged in a fixed order."""
+    _need_cuda(q, cache, block_table, token_req, positions, out)
+    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
+        _i32(t, nm)
+    T = q.shape[0]
+    n_pages, two, Hkv, page_size, D = cache.shape
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_decode: bfloat16 queries, cache and output only")
+    if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_decode: query/output rows do not match heads x head_dim")
+    lib = build.load("attention_decode")
+    ws, counters, _ = _tc_buffers(q.device)
+    splits = lib.sglc_attention_decode_splits(T, n_heads, int(max_keys))
+    need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
+    lib.sglc_attention_decode_scratch(T, n_heads, D, splits, ctypes.byref(need_ws), ctypes.byref(need_c))
+    if need_ws.value > ws.numel() or need_c.value > counters.numel():
+        splits = 1
+    code = lib.sglc_attention_decode(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                     block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
+                                     out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
+                                     int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
+                                     _stream())
+    _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
+
+
+# ---------------------------------------------------------------------------
+def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
+    """One token per row of `logits` ([n, V] float32, row stride free; penalties
+    change the rows in place).  `params`: int32 tensor [n, 10] holding the packed
+    per-row records (see sampling.cu); hist_tok/hist_cnt: int32 (token, count)
+    pairs of the rows' histories."""
+    _need_cuda(logits, params, hist_tok, hist_cnt, out_tok, out_logprob)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 rows")
+    if params.dtype != torch.int32 or params.shape != (n, 10) or not params.is_contiguous():
+        raise KernelError("sample: params must be a contiguous int32 [n,10] tensor")
+    _i32(out_tok, "out_tok")
+    lib = build.load("sampling")
+    code = lib.sglc_sample(_ptr(logits), logits.stride(0), V, n, _ptr(params), _ptr(hist_tok),
+                           _ptr(hist_cnt), _ptr(out_tok), _ptr(out_logprob), _stream())
+    _check(lib, code, "sample")

@@ -47,6 +47,7 @@ class Engine:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=runtime.device)
         self.ws = Workspace(runtime.device, self._workspace_bytes())
         self.logits = None
+        self.decode_logits = None      # fixed: the captured decode graphs write here
         self.steps_run = 0
         # decode-only steps (one token per request, every row wanted) replay a CUDA graph
         # captured per batch size; the first such step of a size runs eagerly as warm-up
@@ -202,13 +203,15 @@ class Engine:
                                             b.dview(f"slots{gi}", T), self.page_size))
             else:
                 ctx.groups.append(None)
-        out = self._logits_buffer(nw)
         decode_only = (T == R and nw == R and all(e.want == [0] for e in entries))
         if self.use_graphs and decode_only:
-            logits = self._forward_graphed(ctx, out)
+            if self.decode_logits is None:
+                self.decode_logits = torch.empty((self.max_requests, self.plan.vocab_size),
+                                                 dtype=torch.float32, device=self.rt.device)
+            logits = self._forward_graphed(ctx, self.decode_logits)
         else:
             self.ws.reset()
-            logits = self.model.forward(ctx, self.cache, out)
+            logits = self.model.forward(ctx, self.cache, self._logits_buffer(nw))
         self.steps_run += 1
         return logits
 

@@ -46,5 +46,10 @@ class Runtime:
         ops.kv_write(k, v, cache, slots, n_kv_heads, head_dim)
 
     def attention(self, ctx, q, cache, grp, out, n_heads, scale, window):
+        if self.dtype == "bfloat16" and ctx.max_q_len == 1 and cache.shape[-1] % 8 == 0 \
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+            # every request brings one token: keys split across blocks
+            return ops.attention_decode(q, cache, grp.block_table, ctx.token_req, ctx.positions, out,
+                                        n_heads, scale, window, ctx.max_keys)
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys)

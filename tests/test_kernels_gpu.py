@@ -354,3 +354,38 @@ def test_gemm_tc_refuses_rows_that_tma_cannot_load():
     assert not ops.gemm_tc_supported(a, w)            # K = 100 is not a multiple of 8
     with pytest.raises(ops.KernelError):
         ops.gemm_tc(a, w, None, out=torch.empty(4, 6, device=DEV))
+
+
+@pytest.mark.parametrize("case_id", range(len(ATTN_CASES)))
+@pytest.mark.parametrize("tokens", ["last", "all"])
+def test_attention_decode(case_id, tokens):
+    """The split-key decode kernel: one query per request ("last"), and the same kernel given
+    every token of a portion ("all": each token is an independent query)."""
+    ops = _ops()
+    lens, q_lens, H, Hkv, D, ps, window = ATTN_CASES[case_id]
+    if tokens == "last":
+        q_lens = [1] * len(lens)
+    c = _paged_case(lens, q_lens, H, Hkv, D, ps, torch.bfloat16, seed=100 + case_id)
+    scale = 0.9 / math.sqrt(D)
+    T = c["q"].shape[0]
+    ref = _attention_reference(c, H, Hkv, D, scale, window)
+    for max_keys in (max(lens), 1024):          # 1024: as under a captured graph
+        out = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, scale,
+                             window, max_keys)
+        assert float((out.double().cpu() - ref).abs().max()) < 2e-2
+        out2 = torch.empty_like(out)
+        ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out2, H, scale,
+                             window, max_keys)
+        assert torch.equal(out, out2)             # fixed merge order
+
+
+def test_attention_decode_finds_a_far_key():
+    ops = _ops()
+    H, Hkv, D, ps = 2, 2, 64, 16
+    for far in (0, 15, 16, 63, 64, 255, 256, 300, 699):
+        c = _paged_case([700], [1], H, Hkv, D, ps, torch.bfloat16, seed=far, far_key=far)
+        out = torch.empty(1, H * D, dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, 1.0, None, 700)
+        ref = _attention_reference(c, H, Hkv, D, 1.0, None)
+        assert float((out.double().cpu() - ref).abs().max()) < 2e-2, far

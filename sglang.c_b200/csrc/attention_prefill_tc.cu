@@ -1,0 +1,362 @@
+// Causal attention of prompt portions over the paged bfloat16 cache on the tensor cores.
+// One block per (request, head, tile of 128 queries).  For every tile of 128 keys that the
+// queries may see:  S = Q·K^T (tcgen05.mma into tensor memory), then the softmax warps (one
+// thread per query row) read S, apply the scale, the causal bound and the window, keep the
+// running maximum and sum of an online softmax in 32-bit, write P = exp(S - max) as bfloat16
+// to shared memory, O_tile = P·V (second MMA, V taken as it lies in the cache: keys by rows),
+// and the threads fold O_tile into their row's output with the usual rescaling.  Keys and
+// values come page by page through the block table (16-byte cp.async into the 128-byte
+// swizzle the MMA expects).  Lengths, positions and block tables are read on the device.
+// The reference's prefill attention for this architecture is k_attn (scores of a whole row in
+// shared memory, src/cuda_backend.cu:1600-1651); its tiled form for other architectures is
+// k_attn_flash (:1838-1960, CUDA cores, warp-shuffle online softmax).
+// Head sizes: 64 and 128 here (other sizes run on the plain kernel of attention_simt.cu).
+#include "common.cuh"
+#include "tc_common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+namespace {
+using namespace tc;
+
+constexpr int BQ = 128;          // queries per block = MMA M = TMEM lanes
+constexpr int BKV = 128;         // keys per tile = MMA N of S
+constexpr int THREADS = 256;     // warps 0-3 softmax, warp 4 MMA + TMEM, warps 5-7 loaders
+constexpr int N_LOADERS = 96;
+constexpr int KV_STAGES = 2;
+
+struct Ctl {
+  uint64_t q_full, s_full, p_ready, o_full;
+  uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct Args {
+  const __nv_bfloat16* q;
+  int q_stride;
+  const __nv_bfloat16* cache;
+  const int* block_table;
+  int bt_stride;
+  const int* q_start;     // [R+1] first token of each request in this step
+  const int* kv_len;      // [R] length of each request after this step
+  __nv_bfloat16* out;
+  int o_stride;
+  int H, Hkv, page_size;
+  float scale_log2;       // scale * log2(e)
+  int window;
+  int* err;
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  int n = valid ? 16 : 0;     // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// byte offset of 16-byte chunk `c` (0..7) of row `r` in a [rows][128 B] tile with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_kernel(const Args a) {
+  constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
+  constexpr int TILE_BYTES = BKV * 128 * DB;       // one K (or V, or Q) tile: [DB][128 rows][128 B]
+  constexpr int P_BYTES = BQ * 128 * (BKV / 64);   // P: [2][128 rows][128 B]
+  constexpr int TMEM_COLS = 256;                   // S: columns 0..127, O_tile: 128..128+D
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sP = sQ + TILE_BYTES;
+  uint8_t* sK = sP + P_BYTES;                      // KV_STAGES tiles
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;       // KV_STAGES tiles
+  __shared__ Ctl ctl;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  const int t0 = a.q_start[r];
+  const int q_len = a.q_start[r + 1] - t0;
+  if (qt * BQ >= q_len) return;                    // uniform for the block: nothing allocated yet
+  const int kv_len = a.kv_len[r];
+  const int pos0 = kv_len - q_len + qt * BQ;       // position of the tile's first query
+  const int rows = min(BQ, q_len - qt * BQ);
+  const int last_pos = pos0 + rows - 1;
+  int first_key = 0;
+  if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
+  const int kt0 = first_key / BKV;
+  const int kt1 = last_pos / BKV;                  // inclusive
+  const int n_tiles = kt1 - kt0 + 1;
+  const int hk = h / (a.H / a.Hkv);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl.q_full, N_LOADERS);
+    mbar_init(&ctl.s_full, 1);
+    mbar_init(&ctl.p_ready, 128);
+    mbar_init(&ctl.o_full, 1);
+    for (int s = 0; s < KV_STAGES; s++) {
+      mbar_init(&ctl.kv_full[s], N_LOADERS);
+      mbar_init(&ctl.kv_empty[s], 1);
+    }
+    ctl.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(&ctl.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+
+  if (warp >= 5) {
+    // ---- loaders: Q once, then K and V tiles through the block table ----
+    const int lt = threadIdx.x - 160;
+    {
+      const __nv_bfloat16* qbase = a.q + (size_t)(t0 + qt * BQ) * a.q_stride + (size_t)h * D;
+      const uint32_t dst = smem_u32(sQ);
+      for (int c = lt; c < BQ * (D / 8); c += N_LOADERS) {
+        int row = c / (D / 8), ch = c % (D / 8);
+        bool valid = row < rows;
+        const void* src = valid ? (const void*)(qbase + (size_t)row * a.q_stride + ch * 8) : (const void*)a.q;
+        cp_async16(dst + (ch / 8) * (BQ * 128) + sw128(row, ch % 8), src, valid);
+      }
+      cp_async_commit();
+    }
+    const int* bt = a.block_table + (size_t)r * a.bt_stride;
+    const size_t page_elems = (size_t)2 * a.Hkv * a.page_size * D;
+    const size_t head_off = (size_t)hk * a.page_size * D;
+    const size_t v_off = (size_t)a.Hkv * a.page_size * D;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; j++) {
+      const int s = j % KV_STAGES;
+      if (j >= KV_STAGES) ok = mbar_wait(&ctl.kv_empty[s], ((j / KV_STAGES) - 1) & 1, abort_flag);
+      if (!ok) break;
+      const int key0 = (kt0 + j) * BKV;
+      const uint32_t dk = smem_u32(sK + s * TILE_BYTES), dv = smem_u32(sV + s * TILE_BYTES);
+      for (int c = lt; c < BKV * (D / 8); c += N_LOADERS) {
+        int row = c / (D / 8), ch = c % (D / 8);
+        int key = key0 + row;
+        // keys before the window may lie in pages that were given back: never touched
+        bool valid = key <= last_pos && key >= first_key;
+        const __nv_bfloat16* src = a.cache;
+        if (valid) {
+          int page = bt[key / a.page_size];
+          src = a.cache + (size_t)page * page_elems + head_off + (size_t)(key % a.page_size) * D + ch * 8;
+        }
+        uint32_t off = (ch / 8) * (BKV * 128) + sw128(row, ch % 8);
+        cp_async16(dk + off, src, valid);
+        cp_async16(dv + off, valid ? src + v_off : src, valid);
+      }
+      cp_async_commit();
+      if (j == 0) {
+        cp_async_wait<1>();           // Q has landed
+        fence_async_proxy();
+        mbar_arrive(&ctl.q_full);
+      }
+      if (j >= 1) {
+        cp_async_wait<1>();           // tile j-1 has landed
+        fence_async_proxy();
+        mbar_arrive(&ctl.kv_full[(j - 1) % KV_STAGES]);
+      }
+    }
+    cp_async_wait<0>();
+    fence_async_proxy();
+    if (ok) mbar_arrive(&ctl.kv_full[(n_tiles - 1) % KV_STAGES]);
+  } else if (warp == 4) {
+    // ---- MMA issuer ----
+    if (elect_one()) {
+      constexpr uint32_t idesc_s = idesc_bf16_f32(BQ, BKV, 0, 0);       // Q, K both K-major
+      constexpr uint32_t idesc_o = idesc_bf16_f32(BQ, D, 0, 1);         // P K-major, V MN-major
+      const uint32_t tS = tmem_base, tO = tmem_base + 128;
+      auto issue_s = [&](int s) {
+        const uint32_t q0 = smem_u32(sQ), k0 = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; k++) {
+          uint32_t off = (k / 4) * (BQ * 128) + (k % 4) * 32;
+          mma_bf16(tS, smem_desc_k_sw128(q0 + off), smem_desc_k_sw128(k0 + off), idesc_s, k > 0 ? 1u : 0u);
+        }
+        mma_commit(&ctl.s_full);
+      };
+      bool ok = mbar_wait(&ctl.q_full, 0, abort_flag) && mbar_wait(&ctl.kv_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; j++) {
+        const int s = j % KV_STAGES;
+        ok = mbar_wait(&ctl.p_ready, j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t p0 = smem_u32(sP), v0 = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; k++) {
+          uint64_t dp = smem_desc_k_sw128(p0 + (k / 4) * (BQ * 128) + (k % 4) * 32);
+          // V: 16 keys = 16 rows of 128 bytes further; blocks of 64 head elements BKV*128 bytes apart
+          uint64_t dv = smem_desc_mn_sw128(v0 + k * 2048, BKV * 128, 1024);
+          mma_bf16(tO, dp, dv, idesc_o, k > 0 ? 1u : 0u);
+        }
+        mma_commit(&ctl.o_full);
+        mma_commit(&ctl.kv_empty[s]);
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(&ctl.kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s((j + 1) % KV_STAGES);
+        }
+      }
+    }
+  } else {
+    // ---- softmax and output: thread = query row ----
+    const int row = warp * 32 + lane;
+    const bool row_valid = row < rows;
+    const int pos = pos0 + row;
+    const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const uint32_t tS = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tO = tS + 128;
+    float m = -INFINITY, l = 0.0f;
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; d++) o[d] = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; j++) {
+      ok = mbar_wait(&ctl.s_full, j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int key0 = (kt0 + j) * BKV;
+      // pass 1: the row's maximum over the keys it may see
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; x++) {
+          int key = key0 + c + x;
+          if (row_valid && key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[x]));
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a row with no key yet
+      const float alpha = exp2f((m - m_use) * a.scale_log2);     // m = -inf gives 0
+      // pass 2: p = exp(s - max) as bfloat16 into shared memory, and the row sum
+      float sum = 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c, v);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int x = 0; x < 32; x += 2) {
+          int key = key0 + c + x;
+          float p0 = 0.0f, p1 = 0.0f;
+          if (row_valid && key <= pos && key >= lo)
+            p0 = exp2f((__uint_as_float(v[x]) - m_use) * a.scale_log2);
+          if (row_valid && key + 1 <= pos && key + 1 >= lo)
+            p1 = exp2f((__uint_as_float(v[x + 1]) - m_use) * a.scale_log2);
+          sum += p0 + p1;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+          packed[x / 2] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        // 32 keys = 4 chunks of 16 bytes: key block (c/64), chunks (c%64)/8 ..
+#pragma unroll
+        for (int q4 = 0; q4 < 4; q4++) {
+          int ch = (c % 64) / 8 + q4;
+          uint4 val = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(sP + (c / 64) * (BQ * 128) + sw128(row, ch)) = val;
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      tc_fence_before_sync();       // the loads of S are done before the next S may be written
+      fence_async_proxy();          // P is visible to the tensor core
+      mbar_arrive(&ctl.p_ready);
+      ok = mbar_wait(&ctl.o_full, j & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tO + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int x = 0; x < 32; x++) o[c + x] = o[c + x] * alpha + __uint_as_float(v[x]);
+      }
+      tc_fence_before_sync();
+    }
+    if (ok && row_valid) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row) * a.o_stride + (size_t)h * D;
+#pragma unroll
+      for (int d = 0; d < D; d += 8) {
+        __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+        for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(o[d + 2 * x] * inv, o[d + 2 * x + 1] * inv);
+        *reinterpret_cast<uint4*>(op + d) = *reinterpret_cast<uint4*>(hh);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int D>
+int launch(const Args& a, int R, int max_q_len, cudaStream_t stream) {
+  constexpr int DB = D / 64;
+  size_t smem = (size_t)BQ * 128 * DB + (size_t)BQ * 128 * 2 + (size_t)2 * KV_STAGES * BKV * 128 * DB + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((max_q_len + BQ - 1) / BQ, a.H, R);
+  attention_prefill_kernel<D><<<grid, THREADS, smem, stream>>>(a);
+  return sglc_launch_status();
+}
+}  // namespace
+
+// Head sizes this kernel takes.
+SGLC_API int sglc_attention_prefill_tc_supports(int D) { return D == 64 || D == 128; }
+
+// q, out: bfloat16 [T][stride], heads side by side, tokens of request r at q_start[r]..q_start[r+1];
+// cache: one layer's pages [n_pages][2][Hkv][page_size][D]; kv_len[r]: the request's length after
+// this step (its last query sits at kv_len-1); max_q_len: the longest portion (sizes the grid).
+SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* cache,
+                                       const int* block_table, int bt_stride, const int* q_start,
+                                       const int* kv_len, void* out, int o_stride, int R,
+                                       int max_q_len, int H, int Hkv, int D, int page_size,
+                                       float scale, int window, int* err, cudaStream_t stream) {
+  if (R <= 0 || max_q_len <= 0) return SGLC_OK;
+  if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
+  if (!(D == 64 || D == 128) || H > 65535 || R > 65535 || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
+  if (q_stride % 8 != 0 || o_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)cache & 15))
+    return SGLC_ERR_UNSUPPORTED;
+  Args a;
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.cache = (const __nv_bfloat16*)cache;
+  a.block_table = block_table; a.bt_stride = bt_stride;
+  a.q_start = q_start; a.kv_len = kv_len;
+  a.out = (__nv_bfloat16*)out; a.o_stride = o_stride;
+  a.H = H; a.Hkv = Hkv; a.page_size = page_size;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.window = window;
+  a.err = err;
+  if (D == 64) return launch<64>(a, R, max_q_len, stream);
+  return launch<128>(a, R, max_q_len, stream);
+}

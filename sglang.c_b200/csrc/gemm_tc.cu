@@ -12,11 +12,13 @@
 // operand ("P") and which its N operand ("Q", tile of BN rows):
 //   many tokens  (prefill): P = A (128 tokens per tile),  Q = W (BN output features per tile)
 //   few tokens   (decode):  P = W (128 features per tile), Q = A (all tokens, padded to BN),
-//                           with the K range split across blocks so that every SM streams
-//                           weights.  The blocks of one tile leave float partial sums in a
-//                           workspace; the block that arrives last adds them in split order
-//                           (a fixed order: the result does not depend on timing) and runs
-//                           the epilogue.
+//                           with the K range split across the blocks of a thread-block
+//                           cluster so that many SMs stream weights.  Each block leaves its
+//                           float partial sums in its own shared memory; after a cluster
+//                           barrier every block sums a slice of the tile's rows over all
+//                           blocks through distributed shared memory, in split order (a
+//                           fixed order: the result does not depend on timing), and runs the
+//                           epilogue for that slice.
 // Sizes: K a multiple of 8 and 16-byte aligned rows (TMA's rule); M, N anything (edges are
 // zero-filled on load and masked on store).
 #include <mutex>
@@ -50,8 +52,6 @@ struct GemmArgs {
   int ldo;
   int out_f32;             // out is float
   int act;
-  float* ws;               // split-K partial sums: [tile][split][BN][128] floats
-  int* counters;           // one per tile, zero between launches
   int* err;                // set to 1 if a bounded wait ran out
 };
 
@@ -61,8 +61,18 @@ struct SharedCtl {
   uint64_t accum;
   uint32_t tmem_base;
   int abort_flag;
-  int is_last;
 };
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t cta_rank) {
+  uint32_t laddr = tc::smem_u32(local), raddr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+  return v;
+}
 
 template <int BN>
 __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, int q0, const float* v,
@@ -157,7 +167,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
     mbar_init(&ctl.accum, 1);
     ctl.abort_flag = 0;
-    ctl.is_last = 0;
     mbar_fence_init();
   }
   if (warp == 0 && lane == 0) {
@@ -248,9 +257,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
       }
     } else if (ok) {
-      // split-K: leave this block's partial sums, then the last block of the tile reduces
-      const int tile = qt * gridDim.x + pt;
-      float* wsp = a.ws + ((size_t)tile * a.splits + split) * (size_t)(BN * BM);
+      // split-K: this block's partial sums into its own shared memory, [column][row] floats
+      // (the stage buffers are free: every MMA that read them has completed)
+      float* mine = reinterpret_cast<float*>(smem);
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
         uint32_t r[CH];
@@ -263,39 +272,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           for (int j = 0; j < CH; j++) r[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < CH; j++)
-          wsp[(size_t)(c + j) * BM + lane_base + lane] = __uint_as_float(r[j]);
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (threadIdx.x == 64) {
-        int old = atomicAdd(&a.counters[tile], 1);
-        ctl.is_last = (old == a.splits - 1);
-        if (old == a.splits - 1) a.counters[tile] = 0;   // ready for the next launch
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ctl.is_last) {
-        __threadfence();
-        const float* base = a.ws + (size_t)tile * a.splits * (size_t)(BN * BM);
-#pragma unroll 1
-        for (int c = 0; c < BN; c += CH) {
-          float v[CH];
-#pragma unroll
-          for (int j = 0; j < CH; j++) v[j] = 0.0f;
-          // loads of different splits are independent; the additions keep split order
-#pragma unroll 4
-          for (int s = 0; s < a.splits; s++) {
-            const float* sp = base + (size_t)s * (BN * BM) + lane_base + lane;
-            float t[CH];
-#pragma unroll
-            for (int j = 0; j < CH; j++) t[j] = __ldcg(sp + (size_t)(c + j) * BM);
-#pragma unroll
-            for (int j = 0; j < CH; j++) v[j] += t[j];
-          }
-          epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
-        }
+        for (int j = 0; j < CH; j++) mine[(c + j) * BM + lane_base + lane] = __uint_as_float(r[j]);
       }
     }
+  }
+
+  if (a.splits > 1) {
+    // every block of the cluster has left its partial sums; then each sums a slice of rows
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp >= 2 && !ctl.abort_flag) {
+      const float* mine = reinterpret_cast<const float*>(smem);
+      const int e = threadIdx.x - 64;
+      const int rows_per = (BM + a.splits - 1) / a.splits;
+      const int row0 = split * rows_per;
+      const int n_rows = min(rows_per, BM - row0);
+      for (int idx = e; idx < n_rows * BN; idx += 128) {
+        int row = row0 + idx % n_rows, col = idx / n_rows;
+        float v = 0.0f;
+        for (int s2 = 0; s2 < a.splits; s2++) v += ld_peer_f32(mine + col * BM + row, (uint32_t)s2);
+        epilogue_store<BN>(a, pt * BM + row, qt * BN + col, &v, 1);
+      }
+    }
+    // no block may exit while another still reads its shared memory
+    __syncwarp();
+    cluster_sync_all();
   }
 
   tc_fence_before_sync();
@@ -349,7 +351,9 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
 template <int BN>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3 grid,
            cudaStream_t stream) {
-  size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2) + 1024;
+  size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2);
+  if (a.splits > 1 && smem < (size_t)BN * BM * 4) smem = (size_t)BN * BM * 4;
+  smem += 1024;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
@@ -357,13 +361,25 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  gemm_tc_kernel<BN><<<grid, THREADS, smem, stream>>>(mp, mq, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = a.splits;     // the blocks of one tile form a cluster
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN>, mp, mq, a);
+  if (e != cudaSuccess) return (int)e;
   return sglc_launch_status();
 }
 }  // namespace
 
-// Split-K scratch a call may need, in floats and counters, for the plan the launcher would
-// choose; lets the caller size one workspace for all its GEMMs.
+// Orientation, tile width and K split for a problem size.
 static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split,
                  int* tiles_p, int* tiles_q) {
   int kb_total = (K + BK - 1) / BK;
@@ -392,29 +408,25 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
   }
 }
 
-// Floats of workspace and number of counters the call (M,N,K) needs (0,0 without split-K).
-SGLC_API int sglc_gemm_tc_scratch(int M, int N, int K, long long* ws_floats, int* n_counters) {
-  int swap, bn, splits, per, tp, tq;
-  plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
-  *ws_floats = splits > 1 ? (long long)tp * tq * splits * bn * BM : 0;
-  *n_counters = splits > 1 ? tp * tq : 0;
+// The plan the launcher would choose for (M,N,K): for tests and tuning.
+SGLC_API int sglc_gemm_tc_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
+  int per, tp, tq;
+  plan(M, N, K, swap, bn, splits, &per, &tp, &tq);
   return SGLC_OK;
 }
 
 // A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
 // null; out [M,N] rows ldo apart (bfloat16, or float if out_f32), or residual (float, in place).
-// ws / counters: scratch of at least sglc_gemm_tc_scratch's sizes (counters zeroed once; the
-// kernel leaves them zero).  err: device int, set to 1 if a wait ran out.
+// err: device int, set to 1 if a wait ran out.
 SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void* out,
                           float* residual, int M, int N, int K, int lda, int ldo, int out_f32,
-                          int act, float* ws, int* counters, int* err, cudaStream_t stream) {
+                          int act, int* err, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SGLC_OK;
   if (K <= 0) return SGLC_ERR_ARGUMENT;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return SGLC_ERR_UNSUPPORTED;
   int swap, bn, splits, per, tp, tq;
   plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
-  if (splits > 1 && (!ws || !counters)) return SGLC_ERR_ARGUMENT;
   GemmArgs a;
   a.M = M; a.N = N; a.K = K;
   a.swap = swap;
@@ -422,7 +434,7 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
   a.kb_per_split = per;
   a.splits = splits;
   a.bias = bias; a.out = out; a.residual = residual; a.ldo = ldo; a.out_f32 = out_f32; a.act = act;
-  a.ws = ws; a.counters = counters; a.err = err;
+  a.err = err;
   CUtensorMap mp, mq;
   bool ok;
   if (swap) {

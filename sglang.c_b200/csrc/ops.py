@@ -230,15 +230,10 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
     elif dst.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError("gemm_tc: output must be float32 or bfloat16")
     lib = build.load("gemm_tc")
-    ws, counters, err = _tc_buffers(a.device)
-    need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
-    lib.sglc_gemm_tc_scratch(M, N, K, ctypes.byref(need_ws), ctypes.byref(need_c))
-    if need_ws.value > ws.numel() or need_c.value > counters.numel():
-        raise KernelError(f"gemm_tc M={M} N={N} K={K}: split-K scratch of {need_ws.value} floats exceeds "
-                          f"the {ws.numel()} reserved")
+    err = _tc_buffers(a.device)[2]
     code = lib.sglc_gemm_tc(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
                             a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
-                            ACT[act], _ptr(ws), _ptr(counters), _ptr(err), _stream())
+                            ACT[act], _ptr(err), _stream())
     _check(lib, code, f"gemm_tc M={M} N={N} K={K}")
 
 
@@ -269,6 +264,37 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                                      int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
                                      _stream())
     _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
+
+
+# ---------------------------------------------------------------------------
+def attention_prefill_tc_supported(q, cache, scale):
+    D = cache.shape[-1]
+    return (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and D in (64, 128)
+            and scale > 0 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, scale, window,
+                         n_requests, max_q_len):
+    """Causal attention of prompt portions on the tensor cores (tcgen05), bfloat16, head
+    sizes 64 and 128.  q_start int32 [R+1], kv_len int32 [R] (lengths after this step)."""
+    _need_cuda(q, cache, block_table, q_start, kv_len, out)
+    for t, nm in ((block_table, "block_table"), (q_start, "q_start"), (kv_len, "kv_len")):
+        _i32(t, nm)
+    n_pages, two, Hkv, page_size, D = cache.shape
+    if not attention_prefill_tc_supported(q, cache, scale):
+        raise KernelError(f"attention_prefill_tc: head size {D} / dtype {q.dtype} / scale {scale} not "
+                          "supported (bfloat16, head size 64 or 128, positive scale)")
+    if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1 or out.dtype != torch.bfloat16 \
+            or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise KernelError("attention_prefill_tc: query/output rows do not match heads x head_dim")
+    lib = build.load("attention_prefill_tc")
+    err = _tc_buffers(q.device)[2]
+    code = lib.sglc_attention_prefill_tc(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                         block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
+                                         out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D,
+                                         page_size, ctypes.c_float(scale), int(window or 0), _ptr(err),
+                                         _stream())
+    _check(lib, code, f"attention_prefill_tc (head_dim {D})")
 
 
 # ---------------------------------------------------------------------------

@@ -51,5 +51,10 @@ class Runtime:
             # every request brings one token: keys split across blocks
             return ops.attention_decode(q, cache, grp.block_table, ctx.token_req, ctx.positions, out,
                                         n_heads, scale, window, ctx.max_keys)
+        if self.dtype == "bfloat16" and ctx.max_q_len > 1 and ops.attention_prefill_tc_supported(q, cache, scale) \
+                and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
+            # prompt portions (and any decoded tokens beside them): 128-query tiles on the tensor cores
+            return ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads,
+                                            scale, window, ctx.R, ctx.max_q_len)
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys)

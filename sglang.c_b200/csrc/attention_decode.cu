@@ -323,3 +323,87 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, const void* cach
   if (e != cudaSuccess) return (int)e;
   return sglc_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate: the merge scratch is a fixed array in
+// this library (see attention_decode_noalloc.h for who needs this and the rules of use).
+#include "attention_decode_noalloc.h"
+
+// [SGLC_NOALLOC_MAX_WS_FLOATS floats of (m, l, o) records][SGLC_NOALLOC_MAX_COUNTERS ints]
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SGLC_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return SGLC_NOALLOC_ERR_SETUP;
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);     // with `dev` current
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return SGLC_NOALLOC_ERR_SETUP;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return SGLC_OK;
+}
+}  // namespace
+
+SGLC_API const char* sglc_attention_decode_noalloc_error(int code) {
+  if (code == SGLC_NOALLOC_ERR_TOO_LARGE)
+    return "sizes exceed the built-in scratch of the no-allocation entry point "
+           "(T*H*n_splits*(D+2) floats <= 1048576 and T*H <= 16384)";
+  if (code == SGLC_NOALLOC_ERR_SETUP)
+    return "the address of the built-in scratch could not be looked up on this device";
+  return sglc_error_string(code);
+}
+
+SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const void* cache,
+                                           const int* block_table, int bt_stride,
+                                           const int* token_req, const int* positions, void* out,
+                                           int o_stride, int T, int H, int Hkv, int D,
+                                           int page_size, float scale, int window, int max_keys,
+                                           int n_splits, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1 || D <= 0)
+    return SGLC_ERR_ARGUMENT;
+  if (D % 8 != 0 || D > 256 || H > 65535 || n_splits > 32) return SGLC_ERR_UNSUPPORTED;
+  if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return SGLC_ERR_UNSUPPORTED;
+  long long pairs = (long long)T * H;
+  long long floats = pairs * n_splits * (D + 2);
+  if (pairs > SGLC_NOALLOC_MAX_COUNTERS || floats > SGLC_NOALLOC_MAX_WS_FLOATS)
+    return SGLC_NOALLOC_ERR_TOO_LARGE;
+  void* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc != SGLC_OK) return rc;
+  float* ws = reinterpret_cast<float*>(base);
+  int* counters = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) +
+                                         (size_t)SGLC_NOALLOC_MAX_WS_FLOATS * 4);
+  // the counters must start at zero; an earlier call that was cut short may have left some set
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)pairs * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  int eff = window > 0 && window < max_keys ? window : max_keys;
+  int chunk_cap = (eff + n_splits - 1) / n_splits;
+  if (chunk_cap < 2 * n_splits) chunk_cap = 2 * n_splits;
+  size_t n_page_ids = (size_t)chunk_cap / page_size + 2;
+  size_t smem = ((size_t)D + (size_t)WARPS * 256 + (size_t)chunk_cap + n_page_ids) * sizeof(float);
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid(T, H, n_splits);
+  // ranges always merge through the scratch here (never through a cluster), so the launch is plain
+  attention_decode_kernel<<<grid, THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, block_table, bt_stride,
+      token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window,
+      n_splits, chunk_cap, /*use_cluster=*/0, ws, counters);
+  return sglc_launch_status();
+}

@@ -184,6 +184,7 @@ class Engine:
             ctx.h_kv_len.append(old_len[r] + n)
             ctx.h_fresh.append(old_len[r] == 0)
             ctx.h_reqs.append(e.req)
+            ctx.h_state_slots.append(self.cache.slot(e.req))
             max_keys = max(max_keys, old_len[r] + n)
             ctx.max_q_len = max(ctx.max_q_len, n)
             t0 += n
@@ -204,7 +205,7 @@ class Engine:
             else:
                 ctx.groups.append(None)
         decode_only = (T == R and nw == R and all(e.want == [0] for e in entries))
-        if self.use_graphs and decode_only:
+        if self.use_graphs and decode_only and self.model.graph_safe:
             if self.decode_logits is None:
                 self.decode_logits = torch.empty((self.max_requests, self.plan.vocab_size),
                                                  dtype=torch.float32, device=self.rt.device)

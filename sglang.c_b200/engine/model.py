@@ -38,6 +38,11 @@ class Model:
                 raise ValueError(f"running order entry {i} reads the cache of entry {call.cache_of}, "
                                  "which must come earlier")
         self.weight_bytes = 0
+        # a part that reads per-step host values (not only device arrays) cannot be replayed
+        parts = [self.embedding, self.position, self.final_norm, self.head]
+        for layer in self.layers:
+            parts += [layer.block, layer.norm1, layer.mixer, layer.norm2, layer.ffn]
+        self.graph_safe = all(getattr(p, "graph_safe", True) for p in parts)
 
     def load(self, model_dir):
         refs = load_checked(self.plan, model_dir)

@@ -60,8 +60,8 @@ class StepContext:
     """What parts see of a step.  Device arrays (int32): tokens[T], positions[T],
     token_req[T] (index of the token's request within this step), q_start[R+1],
     kv_len[R] (length of each request after this step), state_slots[R],
-    want_rows[W].  Host copies: h_q_len, h_kv_len, h_fresh (request starts at
-    position 0 in this step), max_keys (most keys any token sees)."""
+    want_rows[W].  Host copies: h_q_len, h_kv_len, h_state_slots, h_fresh (request
+    starts at position 0 in this step), max_keys (most keys any token sees)."""
 
     def __init__(self, rt, workspace):
         self.rt = rt
@@ -75,6 +75,7 @@ class StepContext:
         self.h_kv_len = []
         self.h_fresh = []
         self.h_reqs = []
+        self.h_state_slots = []
         self.max_keys = 0
         self.max_q_len = 0
         self.groups: List[GroupStep] = []

@@ -31,6 +31,9 @@ from .plan import WeightDecl  # noqa: F401  (re-exported for part authors)
 class Part:
     category = None
     kind = None
+    # False for a part whose forward reads per-step values on the host (ctx.h_*): a step
+    # that holds such a part is never captured into a CUDA graph
+    graph_safe = True
 
     def __init__(self, params, runtime):
         self.params = dict(params)

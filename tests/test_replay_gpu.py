@@ -21,7 +21,8 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": 2e-5, "bfloat16": 1e-2}
 STORE = {"float32": "float32", "bfloat16": "bfloat16"}
 
-LENGTHS = {"A": [5, 17, 32, 100, 128], "B": [1, 9, 40, 63, 100, 201]}
+# C has head size 64 and 1024 positions: in bfloat16 it runs the tensor-core attention kernels
+LENGTHS = {"A": [5, 17, 32, 100, 128], "B": [1, 9, 40, 63, 100, 201], "C": [130, 257, 64, 400, 1000]}
 
 
 def requests_for(name):
@@ -60,24 +61,25 @@ def run_trace(model_dir, dtype, name, steps, tmp_path, n_pages=None, max_tokens=
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions"])
 def test_each_request_alone(model_dirs, tmp_path, name, dtype, mode):
     d = model_dirs(name, STORE[dtype])
     reqs = requests_for(name)
     steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions}[mode](reqs)
-    got, _ = run_trace(d, dtype, name, steps, tmp_path)
+    got, _ = run_trace(d, dtype, name, steps, tmp_path, max_step_tokens=1024)
     err, where = traces.max_error(got, reference(d, reqs))
     assert err < TOL[dtype], f"{mode}: max error {err} at {where}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_mixed_batches_with_pages_used_again(model_dirs, tmp_path, name, dtype):
     d = model_dirs(name, STORE[dtype])
     V = TINY[name]["vocab_size"]
     P = TINY[name]["n_positions"]
-    lens = [37, 64, 90, 21, 128, 55, 70, 33, 101, 48] if name == "A" else [50, 1, 130, 77, 200, 9, 64, 150, 31, 99]
+    lens = {"A": [37, 64, 90, 21, 128, 55, 70, 33, 101, 48], "B": [50, 1, 130, 77, 200, 9, 64, 150, 31, 99],
+            "C": [300, 129, 520, 64, 260, 700, 33, 128]}[name]
     lens = [min(n, P) for n in lens]
     reqs = {f"m{i}": traces.random_tokens(1000 + i, n, V) for i, n in enumerate(lens)}
     prompt_len = {rid: max(1, len(t) - 20 - 3 * i) for i, (rid, t) in enumerate(reqs.items())}

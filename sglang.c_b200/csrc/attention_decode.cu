@@ -26,36 +26,115 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
   }
 }
 
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_f32(const float* local, int cta_rank) {
+// Optional timeline for tuning (compile with -DSGLC_TIMELINE): block (0,0,0), thread 0 stores
+// the nanosecond timer at a few points into tl_out[slot].
+#ifdef SGLC_TIMELINE
+__device__ unsigned long long g_tl[16];
+#define TL(slot)                                                                      \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {    \
+    unsigned long long t_;                                                            \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
+    g_tl[slot] = t_;                                                                  \
+  }
+#else
+#define TL(slot)
+#endif
+
+// the shared::cluster address of `local` as it lies in the block of rank `cta_rank`
+__device__ __forceinline__ uint32_t map_to_peer(const void* local, int cta_rank) {
   uint32_t laddr = (uint32_t)__cvta_generic_to_shared(local), raddr;
-  float v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
-  return v;
+  return raddr;
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t raddr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
 }
 
+// ---- cross-block signalling inside a cluster (bounded waits) ----
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_init_local(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(count));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// false if the limit ran out
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t addr = (uint32_t)__cvta_generic_to_shared(bar);
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// New keys and values (k_new, v_new: the step's own rows, [T][new_stride], kv heads side by
+// side) are optional.  When given, the token's own key and value are taken from them instead
+// of the cache, and the block whose range holds the token's position also writes them into
+// the cache at slots[t] (page*page_size + offset): the separate cache-write launch is saved.
+// token_req may be null: token t is then the t-th request (a step of single tokens).
 __global__ void __launch_bounds__(THREADS)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
-                        const __nv_bfloat16* __restrict__ cache,
+                        __nv_bfloat16* __restrict__ cache,
                         const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ token_req, const int* __restrict__ positions,
                         __nv_bfloat16* __restrict__ out, int o_stride, int T, int H, int Hkv, int D,
                         int page_size, float scale, int window, int n_splits, int chunk_cap,
-                        int use_cluster, float* __restrict__ ws, int* __restrict__ counters) {
+                        int use_cluster, float* __restrict__ ws, int* __restrict__ counters,
+                        const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                        int new_stride, const int* __restrict__ slots, int nb_max, int* __restrict__ err) {
   extern __shared__ float smem[];
   __shared__ float red[33];
   __shared__ int s_last;
+  __shared__ int s_meta[2];
+  __shared__ __align__(8) uint64_t merge_bar;
   const int t = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
   float* sq = smem;                     // D
   float* part = sq + D;                 // WARPS * 256 partial outputs
   float* sc = part + WARPS * 256;       // chunk_cap scores
-  int* spage = reinterpret_cast<int*>(sc + chunk_cap);   // pages of this range
+  int* spage = reinterpret_cast<int*>(sc + chunk_cap);   // the request's page ids, nb_max of them
+  float* recs = reinterpret_cast<float*>(spage + nb_max);   // merge records (block 0 of a cluster)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int r = token_req[t];
-  const int pos = positions[t];
+  TL(0);
+  pdl_launch_dependents();
+  if (use_cluster) {
+    // block 0's merge barrier exists before any block may signal it: arrive now, wait later
+    if (sp == 0 && tid == 0) mbar_init_local(&merge_bar, (uint32_t)(n_splits - 1));
+    __syncwarp();
+    cluster_arrive();
+  }
+  // Before waiting for the kernel ahead in the stream: everything that kernel cannot have
+  // written.  The step's own data (positions, block tables) was copied in before the step
+  // began, and keys and values of EARLIER positions were cached by earlier steps.  Only the
+  // query and the token's own key and value (position `pos`) come from the kernel ahead.
+  if (token_req == nullptr) {
+    const int* bt = block_table + (size_t)t * bt_stride;
+    for (int i = tid; i < nb_max; i += THREADS) spage[i] = bt[i];
+    if (tid == 0) { s_meta[0] = t; s_meta[1] = positions[t]; }
+  } else {
+    if (tid == 0) { s_meta[0] = token_req[t]; s_meta[1] = positions[t]; }
+  }
+  __syncthreads();
+  const int r = s_meta[0];
+  const int pos = s_meta[1];
+  if (token_req != nullptr) {
+    const int* bt = block_table + (size_t)r * bt_stride;
+    int need = pos / page_size + 1;
+    if (need > nb_max) need = nb_max;
+    for (int i = tid; i < need; i += THREADS) spage[i] = bt[i];
+    __syncthreads();
+  }
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int n = pos - lo + 1;
   int chunk = (n + n_splits - 1) / n_splits;
@@ -64,50 +143,134 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   int k1 = k0 + chunk;
   if (k1 > pos + 1) k1 = pos + 1;
   const int nk = k1 > k0 ? k1 - k0 : 0;
-  const int hk = h / (H / Hkv);
-  const int* bt = block_table + (size_t)r * bt_stride;
+  const int G = H / Hkv;
+  const int hk = h / G;
   const size_t page_elems = (size_t)2 * Hkv * page_size * D;
   const size_t head_off = (size_t)hk * page_size * D;
   const size_t v_off = (size_t)Hkv * page_size * D;
+  const bool fused = k_new != nullptr;
+  const __nv_bfloat16* kn = fused ? k_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
+  const __nv_bfloat16* vn = fused ? v_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
+  TL(1);
 
-  // the range's page ids once, so that the loops below issue independent loads
-  const int b0 = k0 / page_size;
-  const int nb = nk > 0 ? (k1 - 1) / page_size - b0 + 1 : 0;
-  for (int i = tid; i < nb; i += THREADS) spage[i] = bt[b0 + i];
+  // LPR lanes share one key's row (16 bytes each), so a warp reads KG whole rows per load and
+  // consecutive keys of a page are one contiguous stretch.  Key index of (round j, this lane)
+  // = (j * WARPS + warp) * KG + kg.  The first NPRE rounds of keys AND values are requested
+  // before anything is computed, so that they travel together.
+  const int LPR = D / 8;
+  const int KG = 32 / LPR;
+  const int kg = lane / LPR, dl = lane % LPR;
+  const bool active = kg < KG;
+  const int stride = WARPS * KG;
+  const int i_first = warp * KG + kg;
+  constexpr int NPRE = 8;
+  uint4 kpre[NPRE], vpre[NPRE];
+#pragma unroll
+  for (int x = 0; x < NPRE; x++) {
+    int i = i_first + x * stride;
+    kpre[x] = make_uint4(0u, 0u, 0u, 0u);
+    vpre[x] = kpre[x];
+    if (active && i < nk && k0 + i != pos) {
+      int p = k0 + i;
+      const __nv_bfloat16* krow =
+          cache + (size_t)spage[p / page_size] * page_elems + head_off + (size_t)(p % page_size) * D;
+      kpre[x] = __ldg(reinterpret_cast<const uint4*>(krow) + dl);
+      vpre[x] = __ldg(reinterpret_cast<const uint4*>(krow + v_off) + dl);
+    }
+  }
+  pdl_wait();
+  // now the kernel ahead is complete: the query, and the token's own key and value
   const __nv_bfloat16* qp = q + (size_t)t * q_stride + (size_t)h * D;
   for (int d = tid; d < D; d += THREADS) sq[d] = __bfloat162float(qp[d]) * scale;
-  __syncthreads();
-
-  // scores: one key per thread, its row read as 16-byte vectors, eight in flight
-  float lmax = -INFINITY;
-  for (int i = tid; i < nk; i += THREADS) {
-    int p = k0 + i;
-    int page = spage[p / page_size - b0];
-    const uint4* kp = reinterpret_cast<const uint4*>(cache + (size_t)page * page_elems + head_off +
-                                                     (size_t)(p % page_size) * D);
-    float s0 = 0.0f, s1 = 0.0f;
-    for (int g = 0; g < D / 8; g += 8) {
-      uint4 u[8];
 #pragma unroll
-      for (int x = 0; x < 8; x++)
-        if (g + x < D / 8) u[x] = __ldg(kp + g + x);
-#pragma unroll
-      for (int x = 0; x < 8; x++) {
-        if (g + x < D / 8) {
-          float f[8];
-          bf16x8_to_f32(u[x], f);
-          const float* qq = sq + (g + x) * 8;
-          s0 = fmaf(qq[0], f[0], s0); s1 = fmaf(qq[1], f[1], s1);
-          s0 = fmaf(qq[2], f[2], s0); s1 = fmaf(qq[3], f[3], s1);
-          s0 = fmaf(qq[4], f[4], s0); s1 = fmaf(qq[5], f[5], s1);
-          s0 = fmaf(qq[6], f[6], s0); s1 = fmaf(qq[7], f[7], s1);
-        }
+  for (int x = 0; x < NPRE; x++) {
+    int i = i_first + x * stride;
+    if (active && i < nk && k0 + i == pos) {
+      const __nv_bfloat16* krow = fused ? kn
+          : cache + (size_t)spage[pos / page_size] * page_elems + head_off + (size_t)(pos % page_size) * D;
+      const __nv_bfloat16* vrow = fused ? vn : krow + v_off;
+      // plain loads: this data was written by the kernel ahead, not before the step
+      kpre[x] = *(reinterpret_cast<const uint4*>(krow) + dl);
+      vpre[x] = *(reinterpret_cast<const uint4*>(vrow) + dl);
+    }
+  }
+  // the token's own key and value into the cache (one head of a group does it)
+  if (fused && pos >= k0 && pos < k1 && h % G == 0) {
+    int slot = slots[t];
+    if (slot >= 0) {
+      __nv_bfloat16* dst = cache + (size_t)(slot / page_size) * page_elems + head_off +
+                           (size_t)(slot % page_size) * D;
+      for (int c = tid; c < D / 8; c += THREADS) {
+        reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(kn)[c];
+        reinterpret_cast<uint4*>(dst + v_off)[c] = reinterpret_cast<const uint4*>(vn)[c];
       }
     }
-    float s = s0 + s1;
-    sc[i] = s;
-    lmax = fmaxf(lmax, s);
   }
+  __syncthreads();
+  float qreg[8];
+#pragma unroll
+  for (int y = 0; y < 8; y++) qreg[y] = active ? sq[dl * 8 + y] : 0.0f;
+  const bool pow2 = (LPR & (LPR - 1)) == 0;
+  auto row_dot = [&](const uint4& u) {
+    float f[8];
+    bf16x8_to_f32(u, f);
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int y = 0; y < 8; y += 2) {
+      s0 = fmaf(qreg[y], f[y], s0);
+      s1 = fmaf(qreg[y + 1], f[y + 1], s1);
+    }
+    float s = s0 + s1;
+    if (pow2) {
+      for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    } else {
+      float tot = s;
+      for (int o = 1; o < LPR; o++) {
+        int src = kg * LPR + (dl + o) % LPR;
+        tot += __shfl_sync(0xffffffffu, s, active ? src : lane);
+      }
+      s = tot;
+    }
+    return s;
+  };
+  float lmax = -INFINITY;
+#pragma unroll
+  for (int x = 0; x < NPRE; x++) {
+    int i = i_first + x * stride;
+    float s = row_dot(kpre[x]);
+    if (active && i < nk) {
+      if (dl == 0) sc[i] = s;
+      lmax = fmaxf(lmax, s);
+    }
+  }
+  // further rounds; the loop bound is the same for every lane of a warp (shuffles inside)
+  for (int wb = warp * KG + NPRE * stride; wb < nk; wb += 4 * stride) {
+    const int i0 = wb + kg;
+    uint4 u[4];
+#pragma unroll
+    for (int x = 0; x < 4; x++) {
+      int i = i0 + x * stride;
+      u[x] = make_uint4(0u, 0u, 0u, 0u);
+      if (active && i < nk) {
+        int p = k0 + i;
+        const __nv_bfloat16* krow = (fused && p == pos)
+            ? kn
+            : cache + (size_t)spage[p / page_size] * page_elems + head_off + (size_t)(p % page_size) * D;
+        u[x] = p == pos ? *(reinterpret_cast<const uint4*>(krow) + dl)
+                        : __ldg(reinterpret_cast<const uint4*>(krow) + dl);
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < 4; x++) {
+      int i = i0 + x * stride;
+      float s = row_dot(u[x]);
+      if (active && i < nk) {
+        if (dl == 0) sc[i] = s;
+        lmax = fmaxf(lmax, s);
+      }
+    }
+  }
+  TL(2);
   const float m = block_max(lmax, red);
   float lsum = 0.0f;
   for (int i = tid; i < nk; i += THREADS) {
@@ -117,17 +280,20 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   }
   const float l = block_sum(lsum, red);     // also orders the writes of sc before the reads below
 
-  // values: LPR lanes share one key's row (16 bytes each), so a warp reads KG keys per load;
-  // key index = (j * WARPS + warp) * KG + kg, four loads in flight per lane
-  const int LPR = D / 8;
-  const int KG = 32 / LPR;
-  const int kg = lane / LPR, dl = lane % LPR;
-  const bool active = kg < KG;
   float acc[8];
 #pragma unroll
   for (int x = 0; x < 8; x++) acc[x] = 0.0f;
-  const int stride = WARPS * KG;
-  for (int i0 = warp * KG + kg; i0 < nk; i0 += 4 * stride) {
+#pragma unroll
+  for (int x = 0; x < NPRE; x++) {
+    int i = i_first + x * stride;
+    float w = (active && i < nk) ? sc[i] : 0.0f;
+    float f[8];
+    bf16x8_to_f32(vpre[x], f);
+#pragma unroll
+    for (int y = 0; y < 8; y++) acc[y] = fmaf(w, f[y], acc[y]);
+  }
+  for (int wb = warp * KG + NPRE * stride; wb < nk; wb += 4 * stride) {
+    const int i0 = wb + kg;
     uint4 u[4];
     float w[4];
 #pragma unroll
@@ -137,9 +303,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       u[x] = make_uint4(0u, 0u, 0u, 0u);
       if (active && i < nk) {
         int p = k0 + i;
-        int page = spage[p / page_size - b0];
-        u[x] = __ldg(reinterpret_cast<const uint4*>(cache + (size_t)page * page_elems + v_off +
-                                                    head_off + (size_t)(p % page_size) * D) + dl);
+        const __nv_bfloat16* vp = (fused && p == pos)
+            ? vn
+            : cache + (size_t)spage[p / page_size] * page_elems + v_off + head_off +
+                  (size_t)(p % page_size) * D;
+        u[x] = p == pos ? *(reinterpret_cast<const uint4*>(vp) + dl)
+                        : __ldg(reinterpret_cast<const uint4*>(vp) + dl);
         w[x] = sc[i];
       }
     }
@@ -157,6 +326,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int y = 0; y < 8; y++) part[(warp * KG + kg) * D + dl * 8 + y] = acc[y];
   }
   __syncthreads();
+  TL(3);
   const int n_part = WARPS * KG;
 
   __nv_bfloat16* op = out + (size_t)t * o_stride + (size_t)h * D;
@@ -171,44 +341,54 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   }
   const int rec = D + 2;
   if (use_cluster) {
-    // the ranges of one (token, head) are the blocks of a cluster: each leaves (m, l, o) in
-    // its own shared memory, and after a cluster barrier block 0 merges them in range order
-    float* mine = part + WARPS * 256 - rec;      // the tail of the partial-output area is free
-    float osum[2];
-    int cnt = 0;
-    for (int d = tid; d < D; d += THREADS) {
-      float o = 0.0f;
-      for (int w = 0; w < n_part; w++) o += part[w * D + d];
-      osum[cnt++] = o;
-    }
-    __syncthreads();
-    cnt = 0;
-    for (int d = tid; d < D; d += THREADS) mine[2 + d] = osum[cnt++];
-    if (tid == 0) {
-      mine[0] = m;
-      mine[1] = l;
-    }
-    __syncthreads();
-    cluster_sync_all();
+    // the ranges of one (token, head) are the blocks of a cluster.  Blocks 1.. send their
+    // (m, l, o) to block 0's shared memory and signal its barrier; block 0 waits for all of
+    // them (with a limit) and merges in range order.  Nothing remote is touched by a block
+    // after its signal, and block 0 outlives every store into it.
+    __syncwarp();
+    cluster_wait();                  // pairs with the arrive at the top: block 0's barrier exists
+    float* dst_local = recs + (size_t)sp * rec;
     if (sp == 0) {
-      float M = -INFINITY;
-      for (int s = 0; s < n_splits; s++) M = fmaxf(M, ld_peer_f32(mine, s));
-      float L = 0.0f;
-      for (int s = 0; s < n_splits; s++) {
-        float ls = ld_peer_f32(mine + 1, s);
-        L += ls > 0.0f ? ls * expf(ld_peer_f32(mine, s) - M) : 0.0f;
-      }
-      float inv = 1.0f / L;
       for (int d = tid; d < D; d += THREADS) {
         float o = 0.0f;
-        for (int s = 0; s < n_splits; s++) {
-          float ls = ld_peer_f32(mine + 1, s);
-          if (ls > 0.0f) o += ld_peer_f32(mine + 2 + d, s) * expf(ld_peer_f32(mine, s) - M);
-        }
-        op[d] = __float2bfloat16_rn(o * inv);
+        for (int w = 0; w < n_part; w++) o += part[w * D + d];
+        dst_local[2 + d] = o;
       }
+      if (tid == 0) { dst_local[0] = m; dst_local[1] = l; }
+      __syncthreads();
+      TL(4);
+      if (!mbar_wait_cluster(&merge_bar, 0)) {
+        if (tid == 0 && err) atomicExch(err, 1);
+        return;
+      }
+      TL(5);
+    } else {
+      const uint32_t dst = map_to_peer(dst_local, 0);
+      for (int d = tid; d < D; d += THREADS) {
+        float o = 0.0f;
+        for (int w = 0; w < n_part; w++) o += part[w * D + d];
+        st_peer_f32(dst + (uint32_t)(2 + d) * 4u, o);
+      }
+      if (tid == 0) {
+        st_peer_f32(dst, m);
+        st_peer_f32(dst + 4u, l);
+      }
+      __syncthreads();
+      if (tid == 0) mbar_arrive_peer(map_to_peer(&merge_bar, 0));
+      return;
     }
-    cluster_sync_all();      // no block exits while block 0 still reads its shared memory
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; s++) M = fmaxf(M, recs[s * rec]);
+    float L = 0.0f;
+    for (int s = 0; s < n_splits; s++) L += recs[s * rec + 1] > 0.0f ? recs[s * rec + 1] * expf(recs[s * rec] - M) : 0.0f;
+    float inv = 1.0f / L;
+    for (int d = tid; d < D; d += THREADS) {
+      float o = 0.0f;
+      for (int s = 0; s < n_splits; s++)
+        if (recs[s * rec + 1] > 0.0f) o += recs[s * rec + 2 + d] * expf(recs[s * rec] - M);
+      op[d] = __float2bfloat16_rn(o * inv);
+    }
+    TL(6);
     return;
   }
   // more ranges than a cluster holds: (m, l, o) of this range go to a workspace in global
@@ -265,6 +445,12 @@ SGLC_API int sglc_attention_decode_scratch(int T, int H, int D, int n_splits, lo
 }
 
 // How many key ranges the launcher would use for T tokens of H heads with up to max_keys keys.
+#ifdef SGLC_TIMELINE
+SGLC_API int sglc_attention_decode_timeline(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16);
+}
+#endif
+
 SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
   long long blocks = (long long)T * H;
   int want = (int)((2 * 148 + blocks - 1) / blocks);
@@ -280,48 +466,42 @@ SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
 // q, out: bfloat16 rows ([T][q_stride], [T][o_stride]), heads side by side; cache: one layer's
 // bfloat16 pages [n_pages][2][Hkv][page_size][D]; positions[t]: the token's own position (the
 // last key it sees); max_keys: the most keys any token sees (sizes shared memory).
-SGLC_API int sglc_attention_decode(const void* q, int q_stride, const void* cache,
+// k_new, v_new (bfloat16 [T][new_stride]) and slots (int32 [T]) may be null; when given, the
+// tokens' own keys and values are read from them and written into the cache by this launch.
+SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                                    const int* block_table, int bt_stride, const int* token_req,
                                    const int* positions, void* out, int o_stride, int T, int H,
                                    int Hkv, int D, int page_size, float scale, int window,
                                    int max_keys, int n_splits, float* ws, int* counters,
-                                   cudaStream_t stream) {
+                                   const void* k_new, const void* v_new, int new_stride,
+                                   const int* slots, int* err, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1)
     return SGLC_ERR_ARGUMENT;
   if (D % 8 != 0 || D > 256 || H > 65535 || n_splits > 65535) return SGLC_ERR_UNSUPPORTED;
   if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return SGLC_ERR_UNSUPPORTED;
   if (n_splits > 8 && (!ws || !counters)) return SGLC_ERR_ARGUMENT;
+  if (k_new && (!v_new || !slots || new_stride % 8 != 0 || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15)))
+    return SGLC_ERR_UNSUPPORTED;
   int eff = window > 0 && window < max_keys ? window : max_keys;
   int chunk_cap = (eff + n_splits - 1) / n_splits;
   if (chunk_cap < 2 * n_splits) chunk_cap = 2 * n_splits;   // the merge reuses the score array
-  size_t n_page_ids = (size_t)chunk_cap / page_size + 2;
-  size_t smem = ((size_t)D + (size_t)WARPS * 256 + (size_t)chunk_cap + n_page_ids) * sizeof(float);
+  int nb_max = (max_keys + page_size - 1) / page_size;
+  if (nb_max > bt_stride) nb_max = bt_stride;
+  size_t smem = ((size_t)D + (size_t)WARPS * 256 + (size_t)chunk_cap + (size_t)nb_max +
+                 (size_t)8 * (D + 2)) * sizeof(float);
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
   dim3 grid(T, H, n_splits);
   int use_cluster = (n_splits > 1 && n_splits <= 8) ? 1 : 0;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = use_cluster ? n_splits : 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(
-      &cfg, attention_decode_kernel, (const __nv_bfloat16*)q, q_stride,
-      (const __nv_bfloat16*)cache, block_table, bt_stride, token_req, positions,
-      (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_splits, chunk_cap,
-      use_cluster, ws, counters);
-  if (e != cudaSuccess) return (int)e;
-  return sglc_launch_status();
+  return sglc_launch(attention_decode_kernel, grid, dim3(THREADS), smem, stream,
+                     use_cluster ? n_splits : 1, true, (const __nv_bfloat16*)q, q_stride,
+                     (__nv_bfloat16*)cache, block_table, bt_stride, token_req, positions,
+                     (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_splits,
+                     chunk_cap, use_cluster, ws, counters, (const __nv_bfloat16*)k_new,
+                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -391,8 +571,10 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
   int eff = window > 0 && window < max_keys ? window : max_keys;
   int chunk_cap = (eff + n_splits - 1) / n_splits;
   if (chunk_cap < 2 * n_splits) chunk_cap = 2 * n_splits;
-  size_t n_page_ids = (size_t)chunk_cap / page_size + 2;
-  size_t smem = ((size_t)D + (size_t)WARPS * 256 + (size_t)chunk_cap + n_page_ids) * sizeof(float);
+  int nb_max = (max_keys + page_size - 1) / page_size;
+  if (nb_max > bt_stride) nb_max = bt_stride;
+  size_t smem = ((size_t)D + (size_t)WARPS * 256 + (size_t)chunk_cap + (size_t)nb_max +
+                 (size_t)8 * (D + 2)) * sizeof(float);
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
   if (smem > 48 * 1024) {
     e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -402,8 +584,10 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
   dim3 grid(T, H, n_splits);
   // ranges always merge through the scratch here (never through a cluster), so the launch is plain
   attention_decode_kernel<<<grid, THREADS, smem, stream>>>(
-      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, block_table, bt_stride,
-      token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window,
-      n_splits, chunk_cap, /*use_cluster=*/0, ws, counters);
+      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)const_cast<void*>(cache), block_table,
+      bt_stride, token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale,
+      window, n_splits, chunk_cap, /*use_cluster=*/0, ws, counters,
+      /*k_new=*/(const __nv_bfloat16*)nullptr, /*v_new=*/(const __nv_bfloat16*)nullptr, 0,
+      /*slots=*/(const int*)nullptr, nb_max, /*err=*/(int*)nullptr);
   return sglc_launch_status();
 }

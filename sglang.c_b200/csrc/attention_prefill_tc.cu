@@ -78,6 +78,8 @@ attention_prefill_kernel(const Args a) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
   if (qt * BQ >= q_len) return;                    // uniform for the block: nothing allocated yet
@@ -325,8 +327,7 @@ int launch(const Args& a, int R, int max_q_len, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, a.H, R);
-  attention_prefill_kernel<D><<<grid, THREADS, smem, stream>>>(a);
-  return sglc_launch_status();
+  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 1, true, a);
 }
 }  // namespace
 

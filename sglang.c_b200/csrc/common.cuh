@@ -18,7 +18,50 @@ enum { SGLC_OK = 0, SGLC_ERR_UNSUPPORTED = -2, SGLC_ERR_ARGUMENT = -3 };
 
 SGLC_API const char* sglc_error_string(int code);
 
+// Programmatic dependent launch: a kernel launched with it may start while the kernel before
+// it in the stream still runs.  It calls pdl_launch_dependents() early (its successor may be
+// scheduled) and pdl_wait() before it reads or overwrites anything an earlier kernel touches
+// (returns at once when the launch had no programmatic dependency).  sglc_set_pdl(0) turns
+// the launch attribute off for this library.
+static int g_sglc_pdl = 1;
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launch with optional cluster depth (blocks of one grid.z column form a cluster) and the
+// programmatic-dependency attribute.
+template <typename... KArgs, typename... Args>
+static inline int sglc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, int cluster_z, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_z > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = cluster_z;
+    n++;
+  }
+  if (pdl && g_sglc_pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+
 #define SGLC_DEFINE_ERROR_STRING()                                            \
+  SGLC_API void sglc_set_pdl(int on) { g_sglc_pdl = on; }                     \
   SGLC_API const char* sglc_error_string(int code) {                          \
     if (code == SGLC_ERR_UNSUPPORTED) return "size not supported by this kernel"; \
     if (code == SGLC_ERR_ARGUMENT) return "bad argument";                     \

@@ -13,6 +13,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
                              int* __restrict__ err) {
   int t = blockIdx.x;
   if (t >= T) return;
+  pdl_launch_dependents();
+  pdl_wait();
   int tok = tokens[t];
   bool bad = tok < 0 || tok >= V;
   int pos = 0;
@@ -43,11 +45,12 @@ SGLC_API int sglc_embed(const int* tokens, const int* positions, const void* wte
   if (T <= 0) return SGLC_OK;
   int threads = E >= 1024 ? 256 : (E >= 256 ? 128 : 64);
   if (table_dtype == SGLC_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, positions, (const float*)wte,
-                                                   (const float*)wpe, out, T, E, V, P, err);
+    return sglc_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, 1, true, tokens,
+                       positions, (const float*)wte, (const float*)wpe, out, T, E, V, P, err);
   else if (table_dtype == SGLC_BF16)
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
-        tokens, positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, T, E, V, P, err);
+    return sglc_launch(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 1, true,
+                       tokens, positions, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, T,
+                       E, V, P, err);
   else
     return SGLC_ERR_ARGUMENT;
   return sglc_launch_status();

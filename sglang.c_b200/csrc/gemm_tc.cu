@@ -55,6 +55,21 @@ struct GemmArgs {
   int* err;                // set to 1 if a bounded wait ran out
 };
 
+// Optional timeline for tuning (compile with -DSGLC_TIMELINE): block (0,0,0) stores the
+// nanosecond timer at a few points of each role into `a.err[16 + slot]`.
+#ifdef SGLC_TIMELINE
+__device__ __forceinline__ void tl_mark(const int* err, int slot) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    ((unsigned long long*)(err + 16))[slot] = t;
+  }
+}
+#define TL(slot) tl_mark(a.err, slot)
+#else
+#define TL(slot)
+#endif
+
 struct SharedCtl {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
@@ -62,17 +77,6 @@ struct SharedCtl {
   uint32_t tmem_base;
   int abort_flag;
 };
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t cta_rank) {
-  uint32_t laddr = tc::smem_u32(local), raddr;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(laddr), "r"(cta_rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
-  return v;
-}
 
 template <int BN>
 __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, int q0, const float* v,
@@ -160,6 +164,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   const int n_kb = kb1 - kb0;
   const int stages = a.stages;
 
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) TL(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) {
       mbar_init(&ctl.full[s], 1);
@@ -182,12 +188,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl.tmem_base;
   volatile int* abort_flag = &ctl.abort_flag;
+  if (threadIdx.x == 0) TL(1);
+  // split-K partial sums arrive here from the other blocks of the cluster at any time, so the
+  // area is apart from the stage buffers (which this block's MMAs may still be reading)
+  float* red_buf = reinterpret_cast<float*>(smem + (size_t)stages * STAGE_BYTES);
 
   if (warp == 0) {
     // ---- TMA producer ----
     if (elect_one()) {
       int issued = 0;
-      for (int i = 0; i < n_kb; i++) {
+      // Weights never change during a step, so with weights on the P side their first tiles
+      // are requested before waiting for the kernel that produces the activations.
+      const int n_first = min(n_kb, stages);
+      if (a.swap) {
+        for (int i = 0; i < n_first; i++) {
+          mbar_expect_tx(&ctl.full[i], STAGE_BYTES);
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES, &map_p, &ctl.full[i], (kb0 + i) * BK, pt * BM);
+        }
+        TL(2);
+        pdl_wait();
+        TL(3);
+        for (int i = 0; i < n_first; i++)
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + P_BYTES, &map_q, &ctl.full[i], (kb0 + i) * BK,
+                      qt * BN);
+        issued = n_first;
+        TL(4);
+      } else {
+        pdl_wait();
+      }
+      for (int i = issued; i < n_kb; i++) {
         int s = i % stages;
         if (i >= stages && !mbar_wait(&ctl.empty[s], ((i / stages) - 1) & 1, abort_flag)) break;
         uint8_t* sp = smem + (size_t)s * STAGE_BYTES;
@@ -211,6 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         int s = i % stages;
         ok = mbar_wait(&ctl.full[s], (i / stages) & 1, abort_flag);
         if (!ok) break;
+        if (i == 0) TL(5);
         tc_fence_after_sync();
         uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
         uint64_t dp = smem_desc_k_sw128(sp);
@@ -223,12 +253,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         mma_commit(&ctl.empty[s]);    // the stage is free once these MMAs have read it
       }
       if (ok) mma_commit(&ctl.accum);   // accumulator complete
+      TL(6);
     }
   } else {
     // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
     const int lane_base = (warp & 3) * 32;
     const int p_glob = pt * BM + lane_base + lane;
+    // split-K: this block finishes rows [row0, row0 + n_rows) of the tile; thread e takes the
+    // elements e, e + 128, ... of that slice (rows fastest).  Bias and residual of the first
+    // four are fetched now, while the weights stream in.
+    const int e = threadIdx.x - 64;
+    const int rows_per = (BM + a.splits - 1) / a.splits;
+    const int row0 = split * rows_per;
+    const int n_rows = min(rows_per, BM - row0);
+    const int total = a.splits > 1 ? n_rows * BN : 0;
+    float bs0[4], rs0[4];
+    size_t off0[4];
+    bool valid0[4];
+    auto element = [&](int idx, int& lr, int& col, size_t& off, int& n) {
+      bool v = idx < total;
+      lr = v ? idx % n_rows : 0;
+      col = v ? idx / n_rows : 0;
+      int pg = pt * BM + row0 + lr, qg = qt * BN + col;
+      int m = a.swap ? qg : pg;
+      n = a.swap ? pg : qg;
+      off = (size_t)m * a.ldo + n;
+      return v && m < a.M && n < a.N;
+    };
+    if (a.splits > 1) {
+      pdl_wait();              // the residual stream is written by the kernels ahead
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int lr, col, n;
+        valid0[u] = element(e + u * 128, lr, col, off0[u], n);
+        bs0[u] = (valid0[u] && a.bias) ? a.bias[n] : 0.0f;
+        rs0[u] = (valid0[u] && a.residual) ? a.residual[off0[u]] : 0.0f;
+      }
+    }
     bool ok = n_kb > 0 ? mbar_wait(&ctl.accum, 0, abort_flag) : true;
+    if (threadIdx.x == 64) TL(7);
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16);
     constexpr int CH = BN < 32 ? 16 : 32;
@@ -257,9 +320,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         epilogue_store<BN>(a, p_glob, qt * BN + c, v, CH);
       }
     } else if (ok) {
-      // split-K: this block's partial sums into its own shared memory, [column][row] floats
-      // (the stage buffers are free: every MMA that read them has completed)
-      float* mine = reinterpret_cast<float*>(smem);
+      // split-K: the tile's 128 rows are dealt out to the cluster's blocks; every block sends
+      // each row of its partial sums to the shared memory of the block that owns the row,
+      // as [split][column][row of the owner's slice] floats
+      const int prow = lane_base + lane;
+      const int owner = prow / rows_per, lr_mine = prow % rows_per;
+      const float* slot0 = red_buf + (size_t)split * BN * rows_per + lr_mine;
+      const uint32_t remote = map_to_peer(slot0, (uint32_t)owner);
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
         uint32_t r[CH];
@@ -272,33 +339,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           for (int j = 0; j < CH; j++) r[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < CH; j++) mine[(c + j) * BM + lane_base + lane] = __uint_as_float(r[j]);
+        for (int j = 0; j < CH; j++) st_peer_b32(remote + (uint32_t)((c + j) * rows_per) * 4u, r[j]);
       }
+      if (threadIdx.x == 64) TL(8);
+    }
+    if (a.splits > 1) {
+      // one cluster barrier: every block's partial sums are where they are summed.  Nothing
+      // remote is touched afterwards, so a block may exit as soon as it is done.
+      __syncwarp();
+      cluster_arrive();
+      cluster_wait();
+      ok = ok && !ctl.abort_flag;
+      if (threadIdx.x == 64) TL(9);
+      if (ok) {
+        const float* buf = red_buf;
+        // four elements per round, their loads issued together (round 0 was fetched above)
+        for (int base = e; base < total; base += 4 * 128) {
+          float v[4], bs[4], rs[4];
+          size_t off[4];
+          bool valid[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            int lr, col, n;
+            valid[u] = element(base + u * 128, lr, col, off[u], n);
+            float acc = 0.0f;
+            for (int s2 = 0; s2 < a.splits; s2++) acc += buf[((size_t)s2 * BN + col) * rows_per + lr];   // split order
+            v[u] = acc;
+            if (base == e) {
+              bs[u] = bs0[u];
+              rs[u] = rs0[u];
+            } else {
+              bs[u] = (valid[u] && a.bias) ? a.bias[n] : 0.0f;
+              rs[u] = (valid[u] && a.residual) ? a.residual[off[u]] : 0.0f;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            if (!valid[u]) continue;
+            float x = apply_act(v[u] + bs[u], a.act);
+            if (a.residual) a.residual[off[u]] = rs[u] + x;
+            else if (a.out_f32) ((float*)a.out)[off[u]] = x;
+            else ((__nv_bfloat16*)a.out)[off[u]] = __float2bfloat16_rn(x);
+          }
+        }
+      }
+      if (threadIdx.x == 64) TL(10);
     }
   }
-
-  if (a.splits > 1) {
-    // every block of the cluster has left its partial sums; then each sums a slice of rows
-    __syncthreads();
+  if (a.splits > 1 && warp < 2) {
     __syncwarp();
-    cluster_sync_all();
-    if (warp >= 2 && !ctl.abort_flag) {
-      const float* mine = reinterpret_cast<const float*>(smem);
-      const int e = threadIdx.x - 64;
-      const int rows_per = (BM + a.splits - 1) / a.splits;
-      const int row0 = split * rows_per;
-      const int n_rows = min(rows_per, BM - row0);
-      for (int idx = e; idx < n_rows * BN; idx += 128) {
-        int row = row0 + idx % n_rows, col = idx / n_rows;
-        float v = 0.0f;
-        for (int s2 = 0; s2 < a.splits; s2++) v += ld_peer_f32(mine + col * BM + row, (uint32_t)s2);
-        epilogue_store<BN>(a, pt * BM + row, qt * BN + col, &v, 1);
-      }
-    }
-    // no block may exit while another still reads its shared memory
-    __syncwarp();
-    cluster_sync_all();
+    cluster_arrive();        // the producer and MMA warps take part in the cluster barrier too
+    cluster_wait();
   }
+  if (threadIdx.x == 64) TL(11);
 
   tc_fence_before_sync();
   __syncthreads();
@@ -352,7 +445,7 @@ template <int BN>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3 grid,
            cudaStream_t stream) {
   size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2);
-  if (a.splits > 1 && smem < (size_t)BN * BM * 4) smem = (size_t)BN * BM * 4;
+  if (a.splits > 1) smem += (size_t)((BM + a.splits - 1) / a.splits) * a.splits * BN * 4;   // partial sums
   smem += 1024;
   static size_t configured = 0;
   if (smem > configured) {
@@ -361,21 +454,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = a.splits;     // the blocks of one tile form a cluster
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN>, mp, mq, a);
-  if (e != cudaSuccess) return (int)e;
-  return sglc_launch_status();
+  return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, a);
 }
 }  // namespace
 

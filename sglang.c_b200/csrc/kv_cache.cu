@@ -17,6 +17,8 @@ __global__ void kv_write_kernel(const TS* __restrict__ k_src, const TS* __restri
                                 int page_size, int n_pages) {
   int t = blockIdx.x;
   if (t >= T) return;
+  pdl_launch_dependents();
+  pdl_wait();
   int slot = slots[t];
   if (slot < 0) return;
   int page = slot / page_size, off = slot % page_size;
@@ -43,13 +45,13 @@ SGLC_API int sglc_kv_write(const void* k_src, const void* v_src, int src_stride,
   if (T <= 0) return SGLC_OK;
   int threads = Hkv * D >= 512 ? 256 : 128;
   if (src_dtype == SGLC_F32 && cache_dtype == SGLC_F32)
-    kv_write_kernel<float, float><<<T, threads, 0, stream>>>(
-        (const float*)k_src, (const float*)v_src, src_stride, (float*)cache, slots, T, Hkv, D,
-        page_size, n_pages);
+    return sglc_launch(kv_write_kernel<float, float>, dim3(T), dim3(threads), 0, stream, 1, true,
+                       (const float*)k_src, (const float*)v_src, src_stride, (float*)cache, slots, T,
+                       Hkv, D, page_size, n_pages);
   else if (src_dtype == SGLC_BF16 && cache_dtype == SGLC_BF16)
-    kv_write_kernel<__nv_bfloat16, __nv_bfloat16><<<T, threads, 0, stream>>>(
-        (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride,
-        (__nv_bfloat16*)cache, slots, T, Hkv, D, page_size, n_pages);
+    return sglc_launch(kv_write_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(threads), 0,
+                       stream, 1, true, (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src,
+                       src_stride, (__nv_bfloat16*)cache, slots, T, Hkv, D, page_size, n_pages);
   else
     return SGLC_ERR_ARGUMENT;
   return sglc_launch_status();

@@ -16,6 +16,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   __shared__ float red[33];
   int r = blockIdx.x;
   if (r >= n_rows) return;
+  pdl_launch_dependents();
+  pdl_wait();
   int src = rows ? rows[r] : r;
   const float* xr = x + (size_t)src * E;
   float s = 0.0f;
@@ -48,6 +50,56 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// One float4 per thread: the row stays in registers, gain and bias are fetched while the
+// row is in flight, and each reduction costs one barrier (every warp adds the per-warp
+// partial sums itself, in the same order).
+template <typename TO>
+__global__ void layernorm_row4_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                      TO* __restrict__ out, int n_rows, int E, float eps) {
+  __shared__ float red1[32], red2[32];
+  int r = blockIdx.x;
+  if (r >= n_rows) return;
+  pdl_launch_dependents();
+  const int i = threadIdx.x, n4 = E / 4;
+  const int lane = i & 31, w = i >> 5, nw = (blockDim.x + 31) >> 5;
+  const bool has = i < n4;
+  float4 g = make_float4(0, 0, 0, 0), b = g, v = g;
+  if (has) {
+    g = reinterpret_cast<const float4*>(gamma)[i];     // weights: not produced by an earlier kernel
+    b = reinterpret_cast<const float4*>(beta)[i];
+  }
+  pdl_wait();
+  int src = rows ? rows[r] : r;
+  if (has) v = reinterpret_cast<const float4*>(x + (size_t)src * E)[i];
+  float s = warp_sum((v.x + v.y) + (v.z + v.w));
+  if (lane == 0) red1[w] = s;
+  __syncthreads();
+  float tot = 0.0f;
+  for (int k = 0; k < nw; k++) tot += red1[k];
+  const float mean = tot / (float)E;
+  float dx = v.x - mean, dy = v.y - mean, dz = v.z - mean, dw = v.w - mean;
+  float q = has ? (dx * dx + dy * dy) + (dz * dz + dw * dw) : 0.0f;
+  q = warp_sum(q);
+  if (lane == 0) red2[w] = q;
+  __syncthreads();
+  float qt = 0.0f;
+  for (int k = 0; k < nw; k++) qt += red2[k];
+  const float inv = 1.0f / sqrtf(qt / (float)E + eps);
+  if (has) {
+    float y0 = dx * inv * g.x + b.x, y1 = dy * inv * g.y + b.y, y2 = dz * inv * g.z + b.z,
+          y3 = dw * inv * g.w + b.w;
+    TO* o = out + (size_t)r * E + 4 * i;
+    if constexpr (sizeof(TO) == 4) {
+      *reinterpret_cast<float4*>(o) = make_float4(y0, y1, y2, y3);
+    } else {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(y0, y1), h1 = __floats2bfloat162_rn(y2, y3);
+      uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+      *reinterpret_cast<uint2*>(o) = pk;
+    }
+  }
+}
+
 SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
                             void* out, int n_rows, int E, float eps, int out_dtype,
                             cudaStream_t stream) {
@@ -56,13 +108,26 @@ SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma,
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
   int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : (E >= 128 ? 128 : 32));
   bool vec = (E % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  int rc = SGLC_OK;
+  bool al = vec && ((reinterpret_cast<uintptr_t>(gamma) & 15) == 0) &&
+            ((reinterpret_cast<uintptr_t>(beta) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  if (al && E / 4 <= 1024) {
+    int th = ((E / 4 + 31) / 32) * 32;
+    if (out_dtype == SGLC_F32)
+      return sglc_launch(layernorm_row4_kernel<float>, dim3(n_rows), dim3(th), 0, stream, 1, true, x,
+                         rows, gamma, beta, (float*)out, n_rows, E, eps);
+    if (out_dtype == SGLC_BF16)
+      return sglc_launch(layernorm_row4_kernel<__nv_bfloat16>, dim3(n_rows), dim3(th), 0, stream, 1,
+                         true, x, rows, gamma, beta, (__nv_bfloat16*)out, n_rows, E, eps);
+    return SGLC_ERR_ARGUMENT;
+  }
 #define LAUNCH(TO, VEC)                                                                      \
   do {                                                                                       \
     if (smem > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(layernorm_kernel<TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                       \
-    layernorm_kernel<TO, VEC><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (TO*)out, \
-                                                                 n_rows, E, eps);            \
+    rc = sglc_launch(layernorm_kernel<TO, VEC>, dim3(n_rows), dim3(threads), smem, stream, 1,  \
+                     true, x, rows, gamma, beta, (TO*)out, n_rows, E, eps);                  \
   } while (0)
   if (out_dtype == SGLC_F32) {
     if (vec) LAUNCH(float, 4); else LAUNCH(float, 1);
@@ -72,5 +137,5 @@ SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma,
     return SGLC_ERR_ARGUMENT;
   }
 #undef LAUNCH
-  return sglc_launch_status();
+  return rc;
 }

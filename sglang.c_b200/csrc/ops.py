@@ -239,12 +239,16 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
 
 # ---------------------------------------------------------------------------
 def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
-                     max_keys):
-    """Attention of single decoded tokens (one query per request) over the paged bfloat16
-    cache, keys split across blocks and merged in a fixed order."""
-    _need_cuda(q, cache, block_table, token_req, positions, out)
-    for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
+                     max_keys, k_new=None, v_new=None, slots=None):
+    """Attention of single decoded tokens over the paged bfloat16 cache, keys split across
+    blocks and merged in a fixed order.  With k_new/v_new/slots (the step's own keys and
+    values, [T, n_kv_heads*head_dim] views, and their cache slots) the same launch also writes
+    them into the cache; this is valid only when every request brings exactly one token."""
+    _need_cuda(q, cache, block_table, token_req, positions, out, k_new, v_new, slots)
+    for t, nm in ((block_table, "block_table"), (positions, "positions")):
         _i32(t, nm)
+    if token_req is not None:           # None: token t belongs to the step's t-th request
+        _i32(token_req, "token_req")
     T = q.shape[0]
     n_pages, two, Hkv, page_size, D = cache.shape
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -252,16 +256,24 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
     if q.shape[1] != n_heads * D or q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention_decode: query/output rows do not match heads x head_dim")
     lib = build.load("attention_decode")
-    ws, counters, _ = _tc_buffers(q.device)
+    ws, counters, err = _tc_buffers(q.device)
     splits = lib.sglc_attention_decode_splits(T, n_heads, int(max_keys))
     need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
     lib.sglc_attention_decode_scratch(T, n_heads, D, splits, ctypes.byref(need_ws), ctypes.byref(need_c))
     if need_ws.value > ws.numel() or need_c.value > counters.numel():
         splits = 1
+    new_stride = 0
+    if k_new is not None:
+        _i32(slots, "slots")
+        if v_new is None or k_new.dtype != torch.bfloat16 or k_new.shape != (T, Hkv * D) \
+                or k_new.stride(1) != 1 or v_new.stride(1) != 1 or k_new.stride(0) != v_new.stride(0):
+            raise KernelError("attention_decode: new keys/values do not match the cache")
+        new_stride = k_new.stride(0)
     code = lib.sglc_attention_decode(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
                                      block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
                                      out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
                                      int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
+                                     _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots), _ptr(err),
                                      _stream())
     _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
 
@@ -314,3 +326,9 @@ def sample(logits, params, hist_tok, hist_cnt, out_tok, out_logprob=None):
     code = lib.sglc_sample(_ptr(logits), logits.stride(0), V, n, _ptr(params), _ptr(hist_tok),
                            _ptr(hist_cnt), _ptr(out_tok), _ptr(out_logprob), _stream())
     _check(lib, code, "sample")
+
+
+def set_pdl(on):
+    """Turn programmatic dependent launch on or off in every kernel library (on by default)."""
+    for name in build.sources():
+        build.load(name).sglc_set_pdl(1 if on else 0)

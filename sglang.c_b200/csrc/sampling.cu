@@ -53,6 +53,8 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const RowParams* __rest
   __shared__ float chunk_sum[THREADS];
   __shared__ int s_pick;
   int row = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   float* l = logits + (size_t)row * ld;
   RowParams p = params[row];
   int tid = threadIdx.x;
@@ -213,7 +215,6 @@ SGLC_API int sglc_sample(float* logits, int ld, int V, int n_rows, const void* p
   if (n_rows <= 0) return SGLC_OK;
   if (V <= 0) return SGLC_ERR_ARGUMENT;
   static_assert(sizeof(RowParams) == 40, "RowParams is 10 words");
-  sample_kernel<<<n_rows, THREADS, 0, stream>>>(logits, ld, V, (const RowParams*)params, hist_tok,
-                                                hist_cnt, out_tok, out_logprob);
-  return sglc_launch_status();
+  return sglc_launch(sample_kernel, dim3(n_rows), dim3(THREADS), 0, stream, 1, true, logits, ld, V,
+                     (const RowParams*)params, hist_tok, hist_cnt, out_tok, out_logprob);
 }

@@ -42,16 +42,26 @@ class Runtime:
             return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act)
         return ops.gemm_simt(a, w, bias, out=out, residual=residual, act=act)
 
-    def kv_write(self, k, v, cache, slots, n_kv_heads, head_dim):
-        ops.kv_write(k, v, cache, slots, n_kv_heads, head_dim)
-
-    def attention(self, ctx, q, cache, grp, out, n_heads, scale, window):
-        if self.dtype == "bfloat16" and ctx.max_q_len == 1 and cache.shape[-1] % 8 == 0 \
-                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
-            # every request brings one token: keys split across blocks
-            return ops.attention_decode(q, cache, grp.block_table, ctx.token_req, ctx.positions, out,
-                                        n_heads, scale, window, ctx.max_keys)
-        if self.dtype == "bfloat16" and ctx.max_q_len > 1 and ops.attention_prefill_tc_supported(q, cache, scale) \
+    def attend(self, ctx, q, k, v, binding, grp, out, n_heads, n_kv_heads, head_dim, scale, window):
+        """Put the step's keys and values into the cache (if this call owns it) and run causal
+        attention of the step's queries over the cache."""
+        cache = binding.tensor
+        bf16_ok = self.dtype == "bfloat16" and head_dim % 8 == 0 and q.stride(0) % 8 == 0 \
+            and q.data_ptr() % 16 == 0
+        if bf16_ok and ctx.max_q_len == 1:
+            # every request brings one token: keys split across blocks; the same launch writes
+            # the new keys and values when this call owns the cache
+            fuse = binding.write and k.data_ptr() % 16 == 0 and v.data_ptr() % 16 == 0
+            if binding.write and not fuse:
+                ops.kv_write(k, v, cache, grp.slots, n_kv_heads, head_dim)
+            # (token t is the step's t-th request, so no token -> request table is passed)
+            return ops.attention_decode(q, cache, grp.block_table, None, ctx.positions, out,
+                                        n_heads, scale, window, ctx.max_keys,
+                                        k_new=k if fuse else None, v_new=v if fuse else None,
+                                        slots=grp.slots if fuse else None)
+        if binding.write:
+            ops.kv_write(k, v, cache, grp.slots, n_kv_heads, head_dim)
+        if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
             # prompt portions (and any decoded tokens beside them): 128-query tiles on the tensor cores
             return ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads,

@@ -48,9 +48,7 @@ class CausalAttention(Part):
         if position is not None:
             position.rotate(ctx, q, k)
         grp = ctx.group(cache.group)
-        if cache.write:
-            ctx.rt.kv_write(k, v, cache.tensor, grp.slots, Hkv, D)
         o = ctx.alloc((T, H * D), self.rt.act_dtype)
-        ctx.rt.attention(ctx, q, cache.tensor, grp, o, H, float(p["scale"]), p.get("window"))
+        ctx.rt.attend(ctx, q, k, v, cache, grp, o, H, Hkv, D, float(p["scale"]), p.get("window"))
         self.out.forward(ctx, o, residual=residual)
         return residual

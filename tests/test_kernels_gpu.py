@@ -438,3 +438,28 @@ def test_attention_prefill_tc_finds_a_far_key():
         ops.attention_prefill_tc(c["q"], c["cache"], c["bt"], q_start, kv_len, out, H, 1.0, None, 1, 130)
         ref = _attention_reference(c, H, Hkv, D, 1.0, None)
         assert float((out.double().cpu() - ref).abs().max()) < 3e-2, far
+
+
+@pytest.mark.parametrize("case_id", [1, 3, 4, 7])
+def test_attention_decode_writes_new_keys_itself(case_id):
+    """One token per request: the kernel takes the token's own key and value from the step's
+    rows and writes them into the cache; afterwards the cache holds what kv_write would have put."""
+    ops = _ops()
+    lens, _, H, Hkv, D, ps, window = ATTN_CASES[case_id]
+    c = _paged_case(lens, [1] * len(lens), H, Hkv, D, ps, torch.bfloat16, seed=300 + case_id)
+    scale = 1.0 / math.sqrt(D)
+    T = len(lens)
+    ref = _attention_reference(c, H, Hkv, D, scale, window)
+    k_new = torch.stack([K[-1].reshape(-1) for K in c["Ks"]]).to(DEV)
+    v_new = torch.stack([V[-1].reshape(-1) for V in c["Vs"]]).to(DEV)
+    slots = torch.tensor([int(c["bt"][r, (n - 1) // ps]) * ps + (n - 1) % ps for r, n in enumerate(lens)],
+                         dtype=torch.int32, device=DEV)
+    want_cache = c["cache"].clone()
+    holed = c["cache"].clone()
+    for r, n in enumerate(lens):                      # the last position is not in the cache yet
+        holed[int(c["bt"][r, (n - 1) // ps]), :, :, (n - 1) % ps] = 7.0
+    out = torch.empty(T, H * D, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(c["q"], holed, c["bt"], c["token_req"], c["positions"], out, H, scale, window,
+                         max(lens), k_new=k_new, v_new=v_new, slots=slots)
+    assert float((out.double().cpu() - ref).abs().max()) < 2e-2
+    assert torch.equal(holed, want_cache)

@@ -455,6 +455,11 @@ SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
   long long blocks = (long long)T * H;
   int want = (int)((2 * 148 + blocks - 1) / blocks);
   int most = (max_keys + 63) / 64;
+  // a block should not walk more than about 256 keys: beyond what it requests up front, every
+  // further round of keys costs a trip to memory
+  int by_len = (max_keys + 255) / 256;
+  if (by_len > 8) by_len = 8;
+  if (want < by_len) want = by_len;
   if (want > most) want = most;
   // up to 8 ranges merge inside a cluster; more only when there are very few (token, head) pairs
   if (want > 8 && blocks * 8 >= 64) want = 8;

@@ -266,26 +266,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int rows_per = (BM + a.splits - 1) / a.splits;
     const int row0 = split * rows_per;
     const int n_rows = min(rows_per, BM - row0);
-    const int total = a.splits > 1 ? n_rows * BN : 0;
+    constexpr int BNP = BN + 4;            // padded row of partial sums (bank spread, 16-byte aligned)
+    const int total4 = (a.splits > 1 && n_rows > 0) ? n_rows * (BN / 4) : 0;   // (row, 4 columns) items
     float bs0[4], rs0[4];
     size_t off0[4];
     bool valid0[4];
-    auto element = [&](int idx, int& lr, int& col, size_t& off, int& n) {
-      bool v = idx < total;
-      lr = v ? idx % n_rows : 0;
-      col = v ? idx / n_rows : 0;
+    auto element = [&](int lr, int col, size_t& off, int& n) {
       int pg = pt * BM + row0 + lr, qg = qt * BN + col;
       int m = a.swap ? qg : pg;
       n = a.swap ? pg : qg;
       off = (size_t)m * a.ldo + n;
-      return v && m < a.M && n < a.N;
+      return m < a.M && n < a.N;
     };
     if (a.splits > 1) {
       pdl_wait();              // the residual stream is written by the kernels ahead
+      const bool has = e < total4;
+      const int lr = has ? e % n_rows : 0, col = has ? (e / n_rows) * 4 : 0;
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        int lr, col, n;
-        valid0[u] = element(e + u * 128, lr, col, off0[u], n);
+        int n;
+        valid0[u] = element(lr, col + u, off0[u], n) && has;
         bs0[u] = (valid0[u] && a.bias) ? a.bias[n] : 0.0f;
         rs0[u] = (valid0[u] && a.residual) ? a.residual[off0[u]] : 0.0f;
       }
@@ -325,7 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       // as [split][column][row of the owner's slice] floats
       const int prow = lane_base + lane;
       const int owner = prow / rows_per, lr_mine = prow % rows_per;
-      const float* slot0 = red_buf + (size_t)split * BN * rows_per + lr_mine;
+      const float* slot0 = red_buf + ((size_t)split * rows_per + lr_mine) * BNP;
       const uint32_t remote = map_to_peer(slot0, (uint32_t)owner);
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
@@ -339,7 +339,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           for (int j = 0; j < CH; j++) r[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < CH; j++) st_peer_b32(remote + (uint32_t)((c + j) * rows_per) * 4u, r[j]);
+        for (int j = 0; j < CH; j += 4)
+          st_peer_v4(remote + (uint32_t)(c + j) * 4u, r[j], r[j + 1], r[j + 2], r[j + 3]);
       }
       if (threadIdx.x == 64) TL(8);
     }
@@ -353,18 +354,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       if (threadIdx.x == 64) TL(9);
       if (ok) {
         const float* buf = red_buf;
-        // four elements per round, their loads issued together (round 0 was fetched above)
-        for (int base = e; base < total; base += 4 * 128) {
-          float v[4], bs[4], rs[4];
+        // a thread sums four consecutive columns of one row at a time (16-byte reads of every
+        // split's partial sums, added in split order); round 0's bias and residual were fetched above
+        for (int base = e; base < total4; base += 128) {
+          int lr = base % n_rows, col = (base / n_rows) * 4;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s2 = 0; s2 < a.splits; s2++) {
+            float4 t4 = *reinterpret_cast<const float4*>(buf + ((size_t)s2 * rows_per + lr) * BNP + col);
+            acc.x += t4.x; acc.y += t4.y; acc.z += t4.z; acc.w += t4.w;
+          }
+          float v[4] = {acc.x, acc.y, acc.z, acc.w};
+          float bs[4], rs[4];
           size_t off[4];
           bool valid[4];
 #pragma unroll
           for (int u = 0; u < 4; u++) {
-            int lr, col, n;
-            valid[u] = element(base + u * 128, lr, col, off[u], n);
-            float acc = 0.0f;
-            for (int s2 = 0; s2 < a.splits; s2++) acc += buf[((size_t)s2 * BN + col) * rows_per + lr];   // split order
-            v[u] = acc;
+            int n;
+            valid[u] = element(lr, col + u, off[u], n);
             if (base == e) {
               bs[u] = bs0[u];
               rs[u] = rs0[u];
@@ -445,7 +451,7 @@ template <int BN>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3 grid,
            cudaStream_t stream) {
   size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2);
-  if (a.splits > 1) smem += (size_t)((BM + a.splits - 1) / a.splits) * a.splits * BN * 4;   // partial sums
+  if (a.splits > 1) smem += (size_t)((BM + a.splits - 1) / a.splits) * a.splits * (BN + 4) * 4;   // partial sums
   smem += 1024;
   static size_t configured = 0;
   if (smem > configured) {

@@ -85,6 +85,10 @@ __device__ __forceinline__ uint32_t map_to_peer(const void* local, uint32_t cta_
 __device__ __forceinline__ void st_peer_b32(uint32_t raddr, uint32_t v) {
   asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(raddr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_peer_v4(uint32_t raddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
 // one arrival on a barrier in another block; what this block stored before is visible to
 // whoever sees the arrival
 __device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {

@@ -5,6 +5,7 @@ places): portions of prompts beside single decoded tokens, cut anywhere.  It
 runs only the tokens it is given, as one batch, against what earlier steps left
 in the cache, and returns the logits at the wanted places.
 """
+import numpy as np
 import torch
 
 from ..cache import CacheManager
@@ -114,9 +115,14 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.req!r} brings no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < V):
-                    raise StepError(f"request {e.req!r}: token id {t} is outside the vocabulary of {V}")
+            if n == 1:
+                bad = not (0 <= int(e.tokens[0]) < V)
+            else:
+                arr = np.asarray(e.tokens)
+                bad = bool(arr.min() < 0 or arr.max() >= V)
+            if bad:
+                t = next(t for t in e.tokens if not (0 <= int(t) < V))
+                raise StepError(f"request {e.req!r}: token id {t} is outside the vocabulary of {V}")
             if self.cache.length(e.req) + n > P:
                 raise StepError(f"request {e.req!r} would reach {self.cache.length(e.req) + n} positions; "
                                 f"the model has {P}")
@@ -154,39 +160,50 @@ class Engine:
         b = self.bufs
         b.wait_host_free()
         R = len(entries)
-        tok, pos, trq, wr = b.hview("tokens"), b.hview("positions"), b.hview("token_req"), b.hview("want_rows")
-        qs, kl, ss = b.hview("q_start"), b.hview("kv_len"), b.hview("state_slots")
+        tok, pos, trq, wr = b.npview("tokens"), b.npview("positions"), b.npview("token_req"), b.npview("want_rows")
+        qs, kl, ss = b.npview("q_start"), b.npview("kv_len"), b.npview("state_slots")
+        paged = [(gi, b.npview(f"slots{gi}"), b.npview(f"bt{gi}").reshape(self.max_requests, self.b_cap))
+                 for gi in self._paged]
+        ps = self.page_size
         ctx = StepContext(self.rt, self.ws)
         t0 = 0
         nw = 0
         max_keys = 0
         for r, e in enumerate(entries):
             n = len(e.tokens)
-            tok[t0:t0 + n] = torch.tensor(e.tokens, dtype=torch.int32)
-            pos[t0:t0 + n] = torch.arange(old_len[r], old_len[r] + n, dtype=torch.int32)
-            trq[t0:t0 + n] = r
+            o = old_len[r]
+            slot = self.cache.slot(e.req)
+            if n == 1:
+                tok[t0] = e.tokens[0]
+                pos[t0] = o
+                trq[t0] = r
+            else:
+                tok[t0:t0 + n] = e.tokens
+                pos[t0:t0 + n] = np.arange(o, o + n, dtype=np.int32)
+                trq[t0:t0 + n] = r
             qs[r] = t0
-            kl[r] = old_len[r] + n
-            ss[r] = self.cache.slot(e.req)
+            kl[r] = o + n
+            ss[r] = slot
             for w in e.want:
                 wr[nw] = t0 + int(w)
                 nw += 1
-            for gi in self._paged:
+            for gi, sl, bt in paged:
                 table = self.cache.block_table(gi, e.req)
-                sl = b.hview(f"slots{gi}")
-                bt = b.hview(f"bt{gi}")
-                tt = torch.tensor(table, dtype=torch.int32)
-                bt[r * self.b_cap: r * self.b_cap + len(table)] = tt
-                p = torch.arange(old_len[r], old_len[r] + n, dtype=torch.int64)
-                sl[t0:t0 + n] = (tt[p // self.page_size].to(torch.int64) * self.page_size
-                                 + p % self.page_size).to(torch.int32)
+                bt[r, :len(table)] = table
+                if n == 1:
+                    sl[t0] = table[o // ps] * ps + o % ps
+                else:
+                    p = np.arange(o, o + n, dtype=np.int64)
+                    sl[t0:t0 + n] = np.asarray(table, dtype=np.int64)[p // ps] * ps + p % ps
             ctx.h_q_len.append(n)
-            ctx.h_kv_len.append(old_len[r] + n)
-            ctx.h_fresh.append(old_len[r] == 0)
+            ctx.h_kv_len.append(o + n)
+            ctx.h_fresh.append(o == 0)
             ctx.h_reqs.append(e.req)
-            ctx.h_state_slots.append(self.cache.slot(e.req))
-            max_keys = max(max_keys, old_len[r] + n)
-            ctx.max_q_len = max(ctx.max_q_len, n)
+            ctx.h_state_slots.append(slot)
+            if o + n > max_keys:
+                max_keys = o + n
+            if n > ctx.max_q_len:
+                ctx.max_q_len = n
             t0 += n
         qs[R] = t0
         b.upload()
@@ -218,9 +235,13 @@ class Engine:
 
     def _forward_graphed(self, ctx, out):
         from ..csrc import ops
-        # shared memory of the attention kernels is sized for the longest context the model has
-        ctx.max_keys = self.plan.max_positions
-        key = ctx.R
+        # launch shapes depend on the batch size and on an upper bound of the context length:
+        # the bound is the next power of two, so a graph serves until the contexts double
+        bound = 128
+        while bound < ctx.max_keys:
+            bound *= 2
+        ctx.max_keys = min(bound, self.plan.max_positions)
+        key = (ctx.R, ctx.max_keys)
         if key in self._graphs:
             graph, n_launches = self._graphs[key]
             graph.replay()

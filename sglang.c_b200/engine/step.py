@@ -110,6 +110,7 @@ class StepBuffers:
             off += (n + 3) & ~3           # 16-byte aligned fields
         self.total = off
         self.host = torch.zeros(off, dtype=torch.int32).pin_memory()
+        self.np = self.host.numpy()            # the same pinned memory, for fast host-side filling
         self.dev = torch.zeros(off, dtype=torch.int32, device=device)
         self.copied = torch.cuda.Event()
         self._copied_once = False
@@ -117,6 +118,10 @@ class StepBuffers:
     def hview(self, name):
         o, n = self.offsets[name]
         return self.host[o:o + n]
+
+    def npview(self, name):
+        o, n = self.offsets[name]
+        return self.np[o:o + n]
 
     def dview(self, name, n=None):
         o, cap = self.offsets[name]

@@ -14,6 +14,9 @@ class Sampler:
         self.device = device
         self.max_rows = max_rows
         self.h_params = torch.zeros((max_rows, 10), dtype=torch.int32).pin_memory()
+        self.np_i = self.h_params.numpy()                      # the same pinned memory
+        self.np_f = self.np_i.view("float32")
+        self._all_greedy_rows = 0       # rows of d_params known to hold plain greedy records
         self.d_params = torch.zeros((max_rows, 10), dtype=torch.int32, device=device)
         self.d_out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.d_logprob = torch.zeros(max_rows, dtype=torch.float32, device=device)
@@ -36,27 +39,38 @@ class Sampler:
             return ([], []) if want_logprobs else []
         if n > self.max_rows:
             raise ValueError(f"{n} rows exceed the sampler's {self.max_rows}")
-        hp = self.h_params
         hist_tok, hist_cnt = [], []
-        for i, (p, u) in enumerate(zip(params, uniforms)):
-            hb = len(hist_tok)
-            if histories is not None and p.has_penalties() and histories[i]:
-                counts = {}
-                for t in histories[i]:
-                    counts[t] = counts.get(t, 0) + 1
-                hist_tok.extend(counts.keys())
-                hist_cnt.extend(counts.values())
-            b = self._bits
-            hp[i] = torch.tensor([b(p.temperature), b(p.top_p), b(p.min_p), b(u), int(p.top_k),
-                                  b(p.repetition_penalty), b(p.frequency_penalty), b(p.presence_penalty),
-                                  hb, len(hist_tok)], dtype=torch.int32)
-        if len(hist_tok) > self.d_hist_tok.numel():
-            self.d_hist_tok = torch.zeros(2 * len(hist_tok), dtype=torch.int32, device=self.device)
-            self.d_hist_cnt = torch.zeros(2 * len(hist_tok), dtype=torch.int32, device=self.device)
-        if hist_tok:
-            self.d_hist_tok[:len(hist_tok)].copy_(torch.tensor(hist_tok, dtype=torch.int32))
-            self.d_hist_cnt[:len(hist_cnt)].copy_(torch.tensor(hist_cnt, dtype=torch.int32))
-        self.d_params[:n].copy_(hp[:n], non_blocking=True)
+        plain_greedy = all(p.temperature <= 0.0 and not p.has_penalties() for p in params)
+        if plain_greedy and self._all_greedy_rows >= n:
+            pass                        # the device already holds n greedy records
+        else:
+            fi, ii = self.np_f, self.np_i
+            for i, (p, u) in enumerate(zip(params, uniforms)):
+                hb = len(hist_tok)
+                if histories is not None and p.has_penalties() and histories[i]:
+                    counts = {}
+                    for t in histories[i]:
+                        counts[t] = counts.get(t, 0) + 1
+                    hist_tok.extend(counts.keys())
+                    hist_cnt.extend(counts.values())
+                fi[i, 0] = p.temperature
+                fi[i, 1] = p.top_p
+                fi[i, 2] = p.min_p
+                fi[i, 3] = u
+                ii[i, 4] = p.top_k if p.temperature > 0.0 else 0
+                fi[i, 5] = p.repetition_penalty
+                fi[i, 6] = p.frequency_penalty
+                fi[i, 7] = p.presence_penalty
+                ii[i, 8] = hb
+                ii[i, 9] = len(hist_tok)
+            if len(hist_tok) > self.d_hist_tok.numel():
+                self.d_hist_tok = torch.zeros(2 * len(hist_tok), dtype=torch.int32, device=self.device)
+                self.d_hist_cnt = torch.zeros(2 * len(hist_tok), dtype=torch.int32, device=self.device)
+            if hist_tok:
+                self.d_hist_tok[:len(hist_tok)].copy_(torch.tensor(hist_tok, dtype=torch.int32))
+                self.d_hist_cnt[:len(hist_cnt)].copy_(torch.tensor(hist_cnt, dtype=torch.int32))
+            self.d_params[:n].copy_(self.h_params[:n], non_blocking=True)
+            self._all_greedy_rows = n if plain_greedy else 0
         ops.sample(logits, self.d_params[:n], self.d_hist_tok, self.d_hist_cnt, self.d_out[:n],
                    self.d_logprob[:n] if want_logprobs else None)
         self.h_out[:n].copy_(self.d_out[:n], non_blocking=True)

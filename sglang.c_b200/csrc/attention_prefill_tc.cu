@@ -11,6 +11,12 @@
 // shared memory, src/cuda_backend.cu:1600-1651); its tiled form for other architectures is
 // k_attn_flash (:1838-1960, CUDA cores, warp-shuffle online softmax).
 // Head sizes: 64 and 128 here (other sizes run on the plain kernel of attention_simt.cu).
+#include <string.h>
+
+#include <mutex>
+#include <utility>
+#include <vector>
+
 #include "common.cuh"
 #include "tc_common.cuh"
 
@@ -24,6 +30,20 @@ constexpr int BKV = 128;         // keys per tile = MMA N of S
 constexpr int THREADS = 256;     // warps 0-3 softmax, warp 4 MMA + TMEM, warps 5-7 loaders
 constexpr int N_LOADERS = 96;
 constexpr int KV_STAGES = 2;
+
+// Optional timeline for tuning (compile with -DSGLC_TIMELINE): the last query tile of the first
+// (request, head) stores the nanosecond timer at points of its softmax thread 0.
+#ifdef SGLC_TIMELINE
+__device__ unsigned long long g_tl[64];
+#define TL(slot)                                                                            \
+  if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) { \
+    unsigned long long t_;                                                                  \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
+    g_tl[slot] = t_;                                                                        \
+  }
+#else
+#define TL(slot)
+#endif
 
 struct Ctl {
   uint64_t q_full, s_full, p_ready, o_full;
@@ -45,6 +65,7 @@ struct Args {
   int H, Hkv, page_size;
   float scale_log2;       // scale * log2(e)
   int window;
+  int use_tma;            // keys, values and queries arrive by TMA (page_size divides 128)
   int* err;
 };
 
@@ -58,12 +79,20 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// 2^x by the special-function unit (inputs here are <= 0 up to rounding; -inf gives 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // byte offset of 16-byte chunk `c` (0..7) of row `r` in a [rows][128 B] tile with the 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
 template <int D>
 __global__ void __launch_bounds__(THREADS)
-attention_prefill_kernel(const Args a) {
+attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
+                         const __grid_constant__ CUtensorMap map_kv, const Args a) {
   constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
   constexpr int TILE_BYTES = BKV * 128 * DB;       // one K (or V, or Q) tile: [DB][128 rows][128 B]
   constexpr int P_BYTES = BQ * 128 * (BKV / 64);   // P: [2][128 rows][128 B]
@@ -77,7 +106,8 @@ attention_prefill_kernel(const Args a) {
   __shared__ Ctl ctl;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int r = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+  // late query tiles see the most keys: they are started first
+  const int r = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   const int t0 = a.q_start[r];
@@ -95,12 +125,12 @@ attention_prefill_kernel(const Args a) {
   const int hk = h / (a.H / a.Hkv);
 
   if (threadIdx.x == 0) {
-    mbar_init(&ctl.q_full, N_LOADERS);
+    mbar_init(&ctl.q_full, a.use_tma ? 1 : N_LOADERS);
     mbar_init(&ctl.s_full, 1);
     mbar_init(&ctl.p_ready, 128);
     mbar_init(&ctl.o_full, 1);
     for (int s = 0; s < KV_STAGES; s++) {
-      mbar_init(&ctl.kv_full[s], N_LOADERS);
+      mbar_init(&ctl.kv_full[s], a.use_tma ? 1 : N_LOADERS);
       mbar_init(&ctl.kv_empty[s], 1);
     }
     ctl.abort_flag = 0;
@@ -116,8 +146,46 @@ attention_prefill_kernel(const Args a) {
   const uint32_t tmem_base = ctl.tmem_base;
   volatile int* abort_flag = &ctl.abort_flag;
 
-  if (warp >= 5) {
-    // ---- loaders: Q once, then K and V tiles through the block table ----
+  if (warp >= 5 && a.use_tma) {
+    // ---- loader by TMA: one box per (page, K or V, 64-wide block of the head) ----
+    const int lt = threadIdx.x - 160;
+    // rows of a tile that no page fills (beyond the last key, before the window) must hold
+    // finite numbers: zero both stages once; later tiles leave finite data behind
+    for (int c = lt; c < (2 * KV_STAGES * TILE_BYTES) / 16; c += N_LOADERS)
+      reinterpret_cast<uint4*>(sK)[c] = make_uint4(0u, 0u, 0u, 0u);
+    fence_async_proxy();
+    asm volatile("bar.sync 2, 96;" ::: "memory");
+    if (lt == 0) {
+      const int ps = a.page_size;
+      const int* bt = a.block_table + (size_t)r * a.bt_stride;
+      mbar_expect_tx(&ctl.q_full, DB * BQ * 128);
+      for (int blk = 0; blk < DB; blk++)
+        tma_load_2d(sQ + blk * (BQ * 128), &map_q, &ctl.q_full, h * D + blk * 64, t0 + qt * BQ);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; j++) {
+        const int s = j % KV_STAGES;
+        if (j >= KV_STAGES) ok = mbar_wait(&ctl.kv_empty[s], ((j / KV_STAGES) - 1) & 1, abort_flag);
+        if (!ok) break;
+        const int key0 = (kt0 + j) * BKV;
+        int pg0 = key0 / ps;
+        int pg1 = min(last_pos, key0 + BKV - 1) / ps;          // inclusive
+        if (pg0 * ps + ps - 1 < first_key) pg0 = first_key / ps;   // pages wholly before the window
+        const int npg = pg1 - pg0 + 1;
+        mbar_expect_tx(&ctl.kv_full[s], (uint32_t)npg * 2u * DB * (uint32_t)ps * 128u);
+        for (int pi = pg0; pi <= pg1; pi++) {
+          const int page = bt[pi];
+          const uint32_t row_off = (uint32_t)(pi * ps - key0) * 128u;
+          for (int blk = 0; blk < DB; blk++) {
+            tma_load_5d(sK + s * TILE_BYTES + blk * (BKV * 128) + row_off, &map_kv, &ctl.kv_full[s],
+                        blk * 64, 0, hk, 0, page);
+            tma_load_5d(sV + s * TILE_BYTES + blk * (BKV * 128) + row_off, &map_kv, &ctl.kv_full[s],
+                        blk * 64, 0, hk, 1, page);
+          }
+        }
+      }
+    }
+  } else if (warp >= 5) {
+    // ---- loaders by cp.async: Q once, then K and V tiles through the block table ----
     const int lt = threadIdx.x - 160;
     {
       const __nv_bfloat16* qbase = a.q + (size_t)(t0 + qt * BQ) * a.q_stride + (size_t)h * D;
@@ -134,11 +202,8 @@ attention_prefill_kernel(const Args a) {
     const size_t page_elems = (size_t)2 * a.Hkv * a.page_size * D;
     const size_t head_off = (size_t)hk * a.page_size * D;
     const size_t v_off = (size_t)a.Hkv * a.page_size * D;
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; j++) {
+    auto issue_tile = [&](int j) {
       const int s = j % KV_STAGES;
-      if (j >= KV_STAGES) ok = mbar_wait(&ctl.kv_empty[s], ((j / KV_STAGES) - 1) & 1, abort_flag);
-      if (!ok) break;
       const int key0 = (kt0 + j) * BKV;
       const uint32_t dk = smem_u32(sK + s * TILE_BYTES), dv = smem_u32(sV + s * TILE_BYTES);
       for (int c = lt; c < BKV * (D / 8); c += N_LOADERS) {
@@ -156,20 +221,27 @@ attention_prefill_kernel(const Args a) {
         cp_async16(dv + off, valid ? src + v_off : src, valid);
       }
       cp_async_commit();
-      if (j == 0) {
-        cp_async_wait<1>();           // Q has landed
-        fence_async_proxy();
-        mbar_arrive(&ctl.q_full);
+    };
+    // tile j+1 is requested before tile j is waited for, so a tile is announced as soon as it
+    // has landed while the next one is already on its way
+    bool ok = true;
+    issue_tile(0);
+    for (int j = 0; j < n_tiles && ok; j++) {
+      const bool more = j + 1 < n_tiles;
+      if (more) {
+        if (j + 1 >= KV_STAGES)
+          ok = mbar_wait(&ctl.kv_empty[(j + 1) % KV_STAGES], (((j + 1) / KV_STAGES) - 1) & 1, abort_flag);
+        if (!ok) break;
+        issue_tile(j + 1);
+        cp_async_wait<1>();           // all but the newest group: tile j (and Q) have landed
+      } else {
+        cp_async_wait<0>();
       }
-      if (j >= 1) {
-        cp_async_wait<1>();           // tile j-1 has landed
-        fence_async_proxy();
-        mbar_arrive(&ctl.kv_full[(j - 1) % KV_STAGES]);
-      }
+      fence_async_proxy();
+      if (j == 0) mbar_arrive(&ctl.q_full);
+      mbar_arrive(&ctl.kv_full[j % KV_STAGES]);
     }
     cp_async_wait<0>();
-    fence_async_proxy();
-    if (ok) mbar_arrive(&ctl.kv_full[(n_tiles - 1) % KV_STAGES]);
   } else if (warp == 4) {
     // ---- MMA issuer ----
     if (elect_one()) {
@@ -226,11 +298,18 @@ attention_prefill_kernel(const Args a) {
 #pragma unroll
     for (int d = 0; d < D; d++) o[d] = 0.0f;
     bool ok = true;
+    TL(0);
     for (int j = 0; j < n_tiles && ok; j++) {
+      if (j == 4) TL(1);
       ok = mbar_wait(&ctl.s_full, j & 1, abort_flag);
       if (!ok) break;
+      if (j == 4) TL(2);
       tc_fence_after_sync();
       const int key0 = (kt0 + j) * BKV;
+      // a tile needs the mask only where it meets the diagonal, the window's edge or the end
+      // of the rows; elsewhere every key is visible to every row of the tile
+      const bool full_tile = (key0 + BKV - 1 <= pos0) && (rows == BQ) &&
+                             (a.window <= 0 || key0 >= pos0 + BQ - a.window);
       // pass 1: the row's maximum over the keys it may see
       float mx = -INFINITY;
 #pragma unroll 1
@@ -238,16 +317,22 @@ attention_prefill_kernel(const Args a) {
         uint32_t v[32];
         tmem_ld_32x32(tS + c, v);
         tmem_ld_wait();
+        if (full_tile) {
 #pragma unroll
-        for (int x = 0; x < 32; x++) {
-          int key = key0 + c + x;
-          if (row_valid && key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[x]));
+          for (int x = 0; x < 32; x++) mx = fmaxf(mx, __uint_as_float(v[x]));
+        } else {
+#pragma unroll
+          for (int x = 0; x < 32; x++) {
+            int key = key0 + c + x;
+            if (row_valid && key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[x]));
+          }
         }
       }
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a row with no key yet
       const float alpha = exp2f((m - m_use) * a.scale_log2);     // m = -inf gives 0
-      // pass 2: p = exp(s - max) as bfloat16 into shared memory, and the row sum
+      const float neg_m = -m_use * a.scale_log2;
+      // pass 2: p = exp(s - max) = 2^(s*c - max*c) as bfloat16 into shared memory, and the row sum
       float sum = 0.0f;
 #pragma unroll 1
       for (int c = 0; c < BKV; c += 32) {
@@ -257,12 +342,13 @@ attention_prefill_kernel(const Args a) {
         uint32_t packed[16];
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
-          int key = key0 + c + x;
-          float p0 = 0.0f, p1 = 0.0f;
-          if (row_valid && key <= pos && key >= lo)
-            p0 = exp2f((__uint_as_float(v[x]) - m_use) * a.scale_log2);
-          if (row_valid && key + 1 <= pos && key + 1 >= lo)
-            p1 = exp2f((__uint_as_float(v[x + 1]) - m_use) * a.scale_log2);
+          float p0 = ex2_approx(fmaf(__uint_as_float(v[x]), a.scale_log2, neg_m));
+          float p1 = ex2_approx(fmaf(__uint_as_float(v[x + 1]), a.scale_log2, neg_m));
+          if (!full_tile) {
+            int key = key0 + c + x;
+            if (!(row_valid && key <= pos && key >= lo)) p0 = 0.0f;
+            if (!(row_valid && key + 1 <= pos && key + 1 >= lo)) p1 = 0.0f;
+          }
           sum += p0 + p1;
           __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           packed[x / 2] = *reinterpret_cast<uint32_t*>(&hh);
@@ -280,8 +366,10 @@ attention_prefill_kernel(const Args a) {
       tc_fence_before_sync();       // the loads of S are done before the next S may be written
       fence_async_proxy();          // P is visible to the tensor core
       mbar_arrive(&ctl.p_ready);
+      if (j == 4) TL(4);
       ok = mbar_wait(&ctl.o_full, j & 1, abort_flag);
       if (!ok) break;
+      if (j == 4) TL(5);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
@@ -292,7 +380,9 @@ attention_prefill_kernel(const Args a) {
         for (int x = 0; x < 32; x++) o[c + x] = o[c + x] * alpha + __uint_as_float(v[x]);
       }
       tc_fence_before_sync();
+      if (j == 4) TL(6);
     }
+    TL(7);
     if (ok && row_valid) {
       const float inv = 1.0f / l;
       __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row) * a.o_stride + (size_t)h * D;
@@ -315,8 +405,59 @@ attention_prefill_kernel(const Args a) {
   }
 }
 
+// ---- host: tensor maps, kept per (pointer, shape) ----
+struct KeyQ { const void* p; uint64_t rows, cols, ld; };
+struct KeyKV { const void* p; int D, ps, Hkv, n_pages; };
+std::mutex g_mutex;
+std::vector<std::pair<KeyQ, CUtensorMap>> g_qmaps;
+std::vector<std::pair<KeyKV, CUtensorMap>> g_kvmaps;
+
+bool get_q_map(CUtensorMap* out, const void* q, uint64_t rows, uint64_t cols, uint64_t ld) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto& e : g_qmaps)
+    if (e.first.p == q && e.first.rows == rows && e.first.cols == cols && e.first.ld == ld) {
+      *out = e.second;
+      return true;
+    }
+  CUtensorMap m;
+  if (!make_map_bf16_2d(&m, q, rows, cols, ld, BQ)) return false;
+  if (g_qmaps.size() > 256) g_qmaps.clear();
+  g_qmaps.push_back({KeyQ{q, rows, cols, ld}, m});
+  *out = m;
+  return true;
+}
+
+// One layer's pages [n_pages][2][Hkv][page_size][D] as a 5-D tensor, boxes of one page's rows of
+// one head, 64 elements (128 bytes) wide, in the 128-byte swizzle.
+bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto& e : g_kvmaps)
+    if (e.first.p == cache && e.first.D == D && e.first.ps == ps && e.first.Hkv == Hkv &&
+        e.first.n_pages == n_pages) {
+      *out = e.second;
+      return true;
+    }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || ((uintptr_t)cache & 15) || ps > 256) return false;
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, 2, (cuuint64_t)n_pages};
+  cuuint64_t strides[4] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2,
+                           (cuuint64_t)2 * Hkv * ps * D * 2};
+  cuuint32_t box[5] = {64, (cuuint32_t)ps, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUtensorMap m;
+  CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return false;
+  if (g_kvmaps.size() > 1024) g_kvmaps.clear();
+  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages}, m});
+  *out = m;
+  return true;
+}
+
 template <int D>
-int launch(const Args& a, int R, int max_q_len, cudaStream_t stream) {
+int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, int max_q_len,
+           cudaStream_t stream) {
   constexpr int DB = D / 64;
   size_t smem = (size_t)BQ * 128 * DB + (size_t)BQ * 128 * 2 + (size_t)2 * KV_STAGES * BKV * 128 * DB + 1024;
   static bool configured = false;
@@ -324,12 +465,20 @@ int launch(const Args& a, int R, int max_q_len, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, a.H, R);
-  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 1, true, a);
+  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 1, true, mq, mkv, a);
 }
 }  // namespace
+
+#ifdef SGLC_TIMELINE
+SGLC_API int sglc_attention_prefill_timeline(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16);
+}
+#endif
 
 // Head sizes this kernel takes.
 SGLC_API int sglc_attention_prefill_tc_supports(int D) { return D == 64 || D == 128; }
@@ -337,11 +486,13 @@ SGLC_API int sglc_attention_prefill_tc_supports(int D) { return D == 64 || D == 
 // q, out: bfloat16 [T][stride], heads side by side, tokens of request r at q_start[r]..q_start[r+1];
 // cache: one layer's pages [n_pages][2][Hkv][page_size][D]; kv_len[r]: the request's length after
 // this step (its last query sits at kv_len-1); max_q_len: the longest portion (sizes the grid).
+// T: rows of q; n_pages: pages of the cache tensor.
 SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* cache,
                                        const int* block_table, int bt_stride, const int* q_start,
                                        const int* kv_len, void* out, int o_stride, int R,
                                        int max_q_len, int H, int Hkv, int D, int page_size,
-                                       float scale, int window, int* err, cudaStream_t stream) {
+                                       float scale, int window, int T, int n_pages, int* err,
+                                       cudaStream_t stream) {
   if (R <= 0 || max_q_len <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
   if (!(D == 64 || D == 128) || H > 65535 || R > 65535 || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
@@ -358,6 +509,16 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.err = err;
-  if (D == 64) return launch<64>(a, R, max_q_len, stream);
-  return launch<128>(a, R, max_q_len, stream);
+  // TMA needs whole pages inside a 128-key tile and rows it can address
+  CUtensorMap mq, mkv;
+  memset(&mq, 0, sizeof(mq));
+  memset(&mkv, 0, sizeof(mkv));
+  a.use_tma = 0;
+  if (BKV % page_size == 0 && T > 0 && n_pages > 0) {
+    bool ok = get_q_map(&mq, q, (uint64_t)T, (uint64_t)H * D, (uint64_t)q_stride) &&
+              get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages);
+    a.use_tma = ok ? 1 : 0;
+  }
+  if (D == 64) return launch<64>(mq, mkv, a, R, max_q_len, stream);
+  return launch<128>(mq, mkv, a, R, max_q_len, stream);
 }

@@ -21,6 +21,8 @@
 //                           epilogue for that slice.
 // Sizes: K a multiple of 8 and 16-byte aligned rows (TMA's rule); M, N anything (edges are
 // zero-filled on load and masked on store).
+#include <string.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -51,6 +53,7 @@ struct GemmArgs {
   float* residual;         // float [M][ldo], updated in place (then `out` is unused)
   int ldo;
   int out_f32;             // out is float
+  int tma_out;             // many-token tiles leave through shared memory and a TMA store / add
   int act;
   int* err;                // set to 1 if a bounded wait ran out
 };
@@ -147,7 +150,7 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
 template <int BN>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-               const GemmArgs a) {
+               const __grid_constant__ CUtensorMap map_out, const GemmArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // stage buffers need 1024-byte alignment for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -156,6 +159,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   __shared__ SharedCtl ctl;
+  __shared__ float s_bias[BN];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pt = blockIdx.x, qt = blockIdx.y, split = blockIdx.z;
@@ -295,7 +299,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16);
     constexpr int CH = BN < 32 ? 16 : 32;
-    if (ok && a.splits == 1) {
+    if (ok && a.tma_out) {
+      // Many tokens: the tile leaves through shared memory (the stage buffers, free now that
+      // every MMA has read them) in the 128-byte swizzle and one thread hands it to the TMA
+      // engine: a store for bfloat16 output, an add into the float residual stream otherwise.
+      // The engine writes whole lines and drops what lies outside the matrix.
+      if constexpr (BN >= 64) {
+        if (e < BN) s_bias[e] = (a.bias && qt * BN + e < a.N) ? a.bias[qt * BN + e] : 0.0f;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int row = lane_base + lane;
+        const bool to_f32 = a.residual != nullptr;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = apply_act(__uint_as_float(r[j]) + s_bias[c + j], a.act);
+          if (to_f32) {
+            // box = 32 floats (128 bytes) per row: this chunk is row `row` of box c/32
+            uint8_t* box = smem + (size_t)(c / 32) * (BM * 128);
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+              *reinterpret_cast<float4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+          } else {
+            // box = 64 bfloat16 (128 bytes) per row: this chunk is half a row of box c/64
+            uint8_t* box = smem + (size_t)(c / 64) * (BM * 128);
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              int ch = (c % 64) / 8 + q4;
+              __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(v[8 * q4 + 2 * x], v[8 * q4 + 2 * x + 1]);
+              *reinterpret_cast<uint4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) = *reinterpret_cast<uint4*>(hh);
+            }
+          }
+        }
+        fence_async_proxy();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          if (to_f32) {
+            for (int b = 0; b < BN / 32; b++)
+              tma_reduce_add_2d(&map_out, smem + (size_t)b * (BM * 128), qt * BN + b * 32, pt * BM);
+          } else {
+            for (int b = 0; b < BN / 64; b++)
+              tma_store_2d(&map_out, smem + (size_t)b * (BM * 128), qt * BN + b * 64, pt * BM);
+          }
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+      }
+    } else if (ok && a.splits == 1) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += CH) {
         float v[CH];
@@ -412,7 +468,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 struct MapKey {
   const void* base;
   uint64_t rows, cols, ld;
-  uint32_t box_rows;
+  uint32_t box_rows;      // bit 16 set: a float map (output); else bfloat16
   bool operator==(const MapKey& o) const {
     return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
   }
@@ -440,7 +496,9 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
     return true;
   }
   CUtensorMap m;
-  if (!make_map_bf16_2d(&m, base, rows, cols, ld, box_rows)) return false;
+  bool made = (box_rows & 0x10000u) ? make_map_f32_2d(&m, base, rows, cols, ld, box_rows & 0xFFFFu)
+                                    : make_map_bf16_2d(&m, base, rows, cols, ld, box_rows);
+  if (!made) return false;
   if (g_maps.size() > 4096) g_maps.clear();
   g_maps.emplace(key, m);
   *out = m;
@@ -448,8 +506,8 @@ bool get_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, u
 }
 
 template <int BN>
-int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3 grid,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, const GemmArgs& a,
+           dim3 grid, cudaStream_t stream) {
   size_t smem = (size_t)a.stages * (BM * BK * 2 + BN * BK * 2);
   if (a.splits > 1) smem += (size_t)((BM + a.splits - 1) / a.splits) * a.splits * (BN + 4) * 4;   // partial sums
   smem += 1024;
@@ -458,9 +516,18 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, dim3
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    // ask for the largest shared-memory split of the SM, so that two blocks fit side by side
+    // (one block's epilogue then overlaps the other's main loop)
+    cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     configured = smem;
   }
-  return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, a);
+  if (a.tma_out) {
+    // the outgoing tile is staged in the stage buffers: 16 KB per 128-byte-wide box
+    size_t need = (size_t)(a.residual ? BN / 32 : BN / 64) * BM * 128 + 1024;
+    if (smem < need) smem = need;
+  }
+  return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
 }
 }  // namespace
 
@@ -530,6 +597,14 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
     ok = get_map(&mp, A, M, K, lda, BM) && get_map(&mq, W, N, K, K, bn);
   }
   if (!ok) return SGLC_ERR_UNSUPPORTED;
+  // many-token tiles leave by TMA when the output rows can be addressed by a tensor map
+  CUtensorMap mo;
+  memset(&mo, 0, sizeof(mo));
+  a.tma_out = 0;
+  if (!swap && bn >= 64) {
+    if (residual) a.tma_out = get_map(&mo, residual, M, N, ldo, BM | 0x10000u) ? 1 : 0;
+    else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
+  }
   int stage_bytes = BM * BK * 2 + bn * BK * 2;
   int budget = swap ? 96 * 1024 : (bn == 128 ? 100 * 1024 : 100 * 1024);
   int stages = budget / stage_bytes;
@@ -539,10 +614,10 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
   a.stages = stages;
   dim3 grid(tp, tq, splits);
   switch (bn) {
-    case 16: return launch<16>(mp, mq, a, grid, stream);
-    case 32: return launch<32>(mp, mq, a, grid, stream);
-    case 64: return launch<64>(mp, mq, a, grid, stream);
-    case 128: return launch<128>(mp, mq, a, grid, stream);
+    case 16: return launch<16>(mp, mq, mo, a, grid, stream);
+    case 32: return launch<32>(mp, mq, mo, a, grid, stream);
+    case 64: return launch<64>(mp, mq, mo, a, grid, stream);
+    case 128: return launch<128>(mp, mq, mo, a, grid, stream);
   }
   return SGLC_ERR_ARGUMENT;
 }

@@ -304,8 +304,8 @@ def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, s
     code = lib.sglc_attention_prefill_tc(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
                                          block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
                                          out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D,
-                                         page_size, ctypes.c_float(scale), int(window or 0), _ptr(err),
-                                         _stream())
+                                         page_size, ctypes.c_float(scale), int(window or 0), q.shape[0],
+                                         n_pages, _ptr(err), _stream())
     _check(lib, code, f"attention_prefill_tc (head_dim {D})")
 
 

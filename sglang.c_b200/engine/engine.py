@@ -48,10 +48,9 @@ class Engine:
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=runtime.device)
         self.ws = Workspace(runtime.device, self._workspace_bytes())
         self.logits = None
-        self.decode_logits = None      # fixed: the captured decode graphs write here
+        self.max_graphs = 48
         self.steps_run = 0
-        # decode-only steps (one token per request, every row wanted) replay a CUDA graph
-        # captured per batch size; the first such step of a size runs eagerly as warm-up
+        # steps whose launch shapes repeat replay a CUDA graph (see _forward_graphed)
         self.use_graphs = bool(use_graphs)
         self._graphs = {}
         self._graph_seen = set()
@@ -80,7 +79,7 @@ class Engine:
 
     def _logits_buffer(self, n):
         if self.logits is None or self.logits.shape[0] < n:
-            cap = max(n, min(self.max_step_tokens, 64))
+            cap = max(n, self.max_requests, min(self.max_step_tokens, 64))
             self.logits = torch.empty((cap, self.plan.vocab_size), dtype=torch.float32,
                                       device=self.rt.device)
         return self.logits
@@ -221,34 +220,44 @@ class Engine:
                                             b.dview(f"slots{gi}", T), self.page_size))
             else:
                 ctx.groups.append(None)
-        decode_only = (T == R and nw == R and all(e.want == [0] for e in entries))
-        if self.use_graphs and decode_only and self.model.graph_safe:
-            if self.decode_logits is None:
-                self.decode_logits = torch.empty((self.max_requests, self.plan.vocab_size),
-                                                 dtype=torch.float32, device=self.rt.device)
-            logits = self._forward_graphed(ctx, self.decode_logits)
+        if self.use_graphs and self.model.graph_safe:
+            logits = self._forward_graphed(ctx)
         else:
             self.ws.reset()
             logits = self.model.forward(ctx, self.cache, self._logits_buffer(nw))
         self.steps_run += 1
         return logits
 
-    def _forward_graphed(self, ctx, out):
+    def _forward_graphed(self, ctx):
+        """Replay a CUDA graph when this step's launch shapes have been seen before.  The
+        shapes depend on the number of tokens, requests and wanted rows, on the longest
+        portion (in 128-query tiles) and on an upper bound of the context length (the next
+        power of two, so a graph serves until the contexts double).  Everything else a step
+        varies in lies in device arrays at fixed addresses.  A shape runs eagerly the first
+        time it is seen, is captured the second time, and replayed afterwards; the least
+        recently used graphs are dropped beyond `max_graphs`."""
         from ..csrc import ops
-        # launch shapes depend on the batch size and on an upper bound of the context length:
-        # the bound is the next power of two, so a graph serves until the contexts double
         bound = 128
         while bound < ctx.max_keys:
             bound *= 2
         ctx.max_keys = min(bound, self.plan.max_positions)
-        key = (ctx.R, ctx.max_keys)
-        if key in self._graphs:
-            graph, n_launches = self._graphs[key]
+        key = (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
+               ctx.max_keys)
+        before_buf = self.logits
+        out = self._logits_buffer(max(ctx.n_want, 1))
+        if out is not before_buf:
+            self._graphs.clear()             # captured graphs wrote into the old buffer
+        hit = self._graphs.get(key)
+        if hit is not None:
+            graph, n_launches = hit
+            self._graphs[key] = self._graphs.pop(key)      # most recently used last
             graph.replay()
             ops.LAUNCHES += n_launches
             self.graph_replays += 1
             return out[:ctx.n_want]
         if key not in self._graph_seen:
+            if len(self._graph_seen) > 4096:
+                self._graph_seen.clear()
             self._graph_seen.add(key)
             self.ws.reset()
             return self.model.forward(ctx, self.cache, out)
@@ -260,6 +269,8 @@ class Engine:
             self.model.forward(ctx, self.cache, out)
         n_launches = ops.LAUNCHES - before
         ops.LAUNCHES = before
+        while len(self._graphs) >= self.max_graphs:
+            self._graphs.pop(next(iter(self._graphs)))
         self._graphs[key] = (graph, n_launches)
         graph.replay()
         ops.LAUNCHES += n_launches

@@ -36,7 +36,7 @@ constexpr int KV_STAGES = 2;
 #ifdef SGLC_TIMELINE
 __device__ unsigned long long g_tl[64];
 #define TL(slot)                                                                            \
-  if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) { \
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {                \
     unsigned long long t_;                                                                  \
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
     g_tl[slot] = t_;                                                                        \
@@ -97,13 +97,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   constexpr int TILE_BYTES = BKV * 128 * DB;       // one K (or V, or Q) tile: [DB][128 rows][128 B]
   constexpr int P_BYTES = BQ * 128 * (BKV / 64);   // P: [2][128 rows][128 B]
   constexpr int TMEM_COLS = 256;                   // S: columns 0..127, O_tile: 128..128+D
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // All shared memory is dynamic and the kernel has no static shared memory, so the tiles
+  // start at the block's first byte, which the 128-byte swizzle needs at a multiple of 1024.
+  // Without alignment slack two blocks fit on one SM (head size 64).
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sP = sQ + TILE_BYTES;
   uint8_t* sK = sP + P_BYTES;                      // KV_STAGES tiles
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;       // KV_STAGES tiles
-  __shared__ Ctl ctl;
+  Ctl& ctl = *reinterpret_cast<Ctl*>(sV + KV_STAGES * TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // late query tiles see the most keys: they are started first
@@ -113,6 +115,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
   if (qt * BQ >= q_len) return;                    // uniform for the block: nothing allocated yet
+  if (smem_u32(smem) & 1023u) {                    // never seen; the tiles would be mis-swizzled
+    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 1);
+    return;
+  }
   const int kv_len = a.kv_len[r];
   const int pos0 = kv_len - q_len + qt * BQ;       // position of the tile's first query
   const int rows = min(BQ, q_len - qt * BQ);
@@ -459,7 +465,7 @@ template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, int max_q_len,
            cudaStream_t stream) {
   constexpr int DB = D / 64;
-  size_t smem = (size_t)BQ * 128 * DB + (size_t)BQ * 128 * 2 + (size_t)2 * KV_STAGES * BKV * 128 * DB + 1024;
+  size_t smem = (size_t)BQ * 128 * DB + (size_t)BQ * 128 * 2 + (size_t)2 * KV_STAGES * BKV * 128 * DB + 256;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>,

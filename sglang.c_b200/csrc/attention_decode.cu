@@ -93,13 +93,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         int page_size, float scale, int window, int n_splits, int chunk_cap,
                         int use_cluster, float* __restrict__ ws, int* __restrict__ counters,
                         const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
-                        int new_stride, const int* __restrict__ slots, int nb_max, int* __restrict__ err) {
+                        int new_stride, const int* __restrict__ slots, int nb_max, int* __restrict__ err,
+                        const int* __restrict__ token_list) {
   extern __shared__ float smem[];
   __shared__ float red[33];
   __shared__ int s_last;
   __shared__ int s_meta[2];
   __shared__ __align__(8) uint64_t merge_bar;
-  const int t = blockIdx.x, h = blockIdx.y, sp = blockIdx.z;
+  // token_list (optional): the tokens this launch serves, when only some of the step's tokens
+  // are single decoded tokens (the others are prompt portions served by another kernel)
+  const int t = token_list ? token_list[blockIdx.x] : blockIdx.x;
+  const int h = blockIdx.y, sp = blockIdx.z;
   float* sq = smem;                     // D
   float* part = sq + D;                 // WARPS * 256 partial outputs
   float* sc = part + WARPS * 256;       // chunk_cap scores
@@ -393,7 +397,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   }
   // more ranges than a cluster holds: (m, l, o) of this range go to a workspace in global
   // memory, and the block that arrives last merges all ranges
-  float* mine = ws + ((size_t)(t * H + h) * n_splits + sp) * rec;
+  float* mine = ws + ((size_t)(blockIdx.x * H + h) * n_splits + sp) * rec;
   for (int d = tid; d < D; d += THREADS) {
     float o = 0.0f;
     for (int w = 0; w < n_part; w++) o += part[w * D + d];
@@ -406,14 +410,14 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   __threadfence();
   __syncthreads();
   if (tid == 0) {
-    int old = atomicAdd(&counters[t * H + h], 1);
+    int old = atomicAdd(&counters[blockIdx.x * H + h], 1);
     s_last = (old == n_splits - 1);
-    if (old == n_splits - 1) counters[t * H + h] = 0;
+    if (old == n_splits - 1) counters[blockIdx.x * H + h] = 0;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const float* all = ws + (size_t)(t * H + h) * n_splits * rec;
+  const float* all = ws + (size_t)(blockIdx.x * H + h) * n_splits * rec;
   // the ranges' (m, l) into shared memory, then every thread merges its output elements
   float* sm = sc;                   // reuse: 2 * n_splits floats
   for (int s = tid; s < 2 * n_splits; s += THREADS) sm[s] = __ldcg(all + (size_t)(s >> 1) * rec + (s & 1));
@@ -471,6 +475,7 @@ SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
 // q, out: bfloat16 rows ([T][q_stride], [T][o_stride]), heads side by side; cache: one layer's
 // bfloat16 pages [n_pages][2][Hkv][page_size][D]; positions[t]: the token's own position (the
 // last key it sees); max_keys: the most keys any token sees (sizes shared memory).
+// T: the number of tokens this launch serves (all of the step's, or those named by token_list).
 // k_new, v_new (bfloat16 [T][new_stride]) and slots (int32 [T]) may be null; when given, the
 // tokens' own keys and values are read from them and written into the cache by this launch.
 SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
@@ -479,7 +484,8 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                                    int Hkv, int D, int page_size, float scale, int window,
                                    int max_keys, int n_splits, float* ws, int* counters,
                                    const void* k_new, const void* v_new, int new_stride,
-                                   const int* slots, int* err, cudaStream_t stream) {
+                                   const int* slots, int* err, const int* token_list,
+                                   cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1)
     return SGLC_ERR_ARGUMENT;
@@ -506,7 +512,7 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                      (__nv_bfloat16*)cache, block_table, bt_stride, token_req, positions,
                      (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_splits,
                      chunk_cap, use_cluster, ws, counters, (const __nv_bfloat16*)k_new,
-                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err);
+                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err, token_list);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -593,6 +599,6 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
       bt_stride, token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale,
       window, n_splits, chunk_cap, /*use_cluster=*/0, ws, counters,
       /*k_new=*/(const __nv_bfloat16*)nullptr, /*v_new=*/(const __nv_bfloat16*)nullptr, 0,
-      /*slots=*/(const int*)nullptr, nb_max, /*err=*/(int*)nullptr);
+      /*slots=*/(const int*)nullptr, nb_max, /*err=*/(int*)nullptr, /*token_list=*/(const int*)nullptr);
   return sglc_launch_status();
 }

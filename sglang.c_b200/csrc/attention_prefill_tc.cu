@@ -66,6 +66,7 @@ struct Args {
   float scale_log2;       // scale * log2(e)
   int window;
   int use_tma;            // keys, values and queries arrive by TMA (page_size divides 128)
+  int skip_single;        // requests that bring one token are served by the decode kernel
   int* err;
 };
 
@@ -115,6 +116,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
   if (qt * BQ >= q_len) return;                    // uniform for the block: nothing allocated yet
+  if (a.skip_single && q_len == 1) return;
   if (smem_u32(smem) & 1023u) {                    // never seen; the tiles would be mis-swizzled
     if (threadIdx.x == 0 && a.err) atomicExch(a.err, 1);
     return;
@@ -497,8 +499,8 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
                                        const int* block_table, int bt_stride, const int* q_start,
                                        const int* kv_len, void* out, int o_stride, int R,
                                        int max_q_len, int H, int Hkv, int D, int page_size,
-                                       float scale, int window, int T, int n_pages, int* err,
-                                       cudaStream_t stream) {
+                                       float scale, int window, int T, int n_pages, int skip_single,
+                                       int* err, cudaStream_t stream) {
   if (R <= 0 || max_q_len <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
   if (!(D == 64 || D == 128) || H > 65535 || R > 65535 || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
@@ -515,6 +517,7 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
   a.err = err;
+  a.skip_single = skip_single;
   // TMA needs whole pages inside a 128-key tile and rows it can address
   CUtensorMap mq, mkv;
   memset(&mq, 0, sizeof(mq));

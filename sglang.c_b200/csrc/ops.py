@@ -239,17 +239,22 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
 
 # ---------------------------------------------------------------------------
 def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
-                     max_keys, k_new=None, v_new=None, slots=None):
+                     max_keys, k_new=None, v_new=None, slots=None, token_list=None, n_tokens=None):
     """Attention of single decoded tokens over the paged bfloat16 cache, keys split across
     blocks and merged in a fixed order.  With k_new/v_new/slots (the step's own keys and
     values, [T, n_kv_heads*head_dim] views, and their cache slots) the same launch also writes
     them into the cache; this is valid only when every request brings exactly one token."""
-    _need_cuda(q, cache, block_table, token_req, positions, out, k_new, v_new, slots)
+    _need_cuda(q, cache, block_table, token_req, positions, out, k_new, v_new, slots, token_list)
     for t, nm in ((block_table, "block_table"), (positions, "positions")):
         _i32(t, nm)
     if token_req is not None:           # None: token t belongs to the step's t-th request
         _i32(token_req, "token_req")
     T = q.shape[0]
+    if token_list is not None:          # serve only the listed tokens (the first n_tokens entries)
+        _i32(token_list, "token_list")
+        if token_req is None or k_new is not None:
+            raise KernelError("attention_decode: a token list needs token_req and no fused cache write")
+        T = int(n_tokens)
     n_pages, two, Hkv, page_size, D = cache.shape
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 queries, cache and output only")
@@ -265,7 +270,7 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
     new_stride = 0
     if k_new is not None:
         _i32(slots, "slots")
-        if v_new is None or k_new.dtype != torch.bfloat16 or k_new.shape != (T, Hkv * D) \
+        if v_new is None or k_new.dtype != torch.bfloat16 or tuple(k_new.shape) != (T, Hkv * D) \
                 or k_new.stride(1) != 1 or v_new.stride(1) != 1 or k_new.stride(0) != v_new.stride(0):
             raise KernelError("attention_decode: new keys/values do not match the cache")
         new_stride = k_new.stride(0)
@@ -274,7 +279,7 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                                      out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
                                      int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
                                      _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots), _ptr(err),
-                                     _stream())
+                                     _ptr(token_list), _stream())
     _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
 
 
@@ -286,7 +291,7 @@ def attention_prefill_tc_supported(q, cache, scale):
 
 
 def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, scale, window,
-                         n_requests, max_q_len):
+                         n_requests, max_q_len, skip_single=False):
     """Causal attention of prompt portions on the tensor cores (tcgen05), bfloat16, head
     sizes 64 and 128.  q_start int32 [R+1], kv_len int32 [R] (lengths after this step)."""
     _need_cuda(q, cache, block_table, q_start, kv_len, out)
@@ -305,7 +310,7 @@ def attention_prefill_tc(q, cache, block_table, q_start, kv_len, out, n_heads, s
                                          block_table.stride(0), _ptr(q_start), _ptr(kv_len), _ptr(out),
                                          out.stride(0), int(n_requests), int(max_q_len), n_heads, Hkv, D,
                                          page_size, ctypes.c_float(scale), int(window or 0), q.shape[0],
-                                         n_pages, _ptr(err), _stream())
+                                         n_pages, 1 if skip_single else 0, _ptr(err), _stream())
     _check(lib, code, f"attention_prefill_tc (head_dim {D})")
 
 

@@ -161,6 +161,8 @@ class Engine:
         R = len(entries)
         tok, pos, trq, wr = b.npview("tokens"), b.npview("positions"), b.npview("token_req"), b.npview("want_rows")
         qs, kl, ss = b.npview("q_start"), b.npview("kv_len"), b.npview("state_slots")
+        dtk = b.npview("decode_tokens")
+        n_decode = 0
         paged = [(gi, b.npview(f"slots{gi}"), b.npview(f"bt{gi}").reshape(self.max_requests, self.b_cap))
                  for gi in self._paged]
         ps = self.page_size
@@ -176,6 +178,8 @@ class Engine:
                 tok[t0] = e.tokens[0]
                 pos[t0] = o
                 trq[t0] = r
+                dtk[n_decode] = t0
+                n_decode += 1
             else:
                 tok[t0:t0 + n] = e.tokens
                 pos[t0:t0 + n] = np.arange(o, o + n, dtype=np.int32)
@@ -208,6 +212,8 @@ class Engine:
         b.upload()
 
         ctx.T, ctx.R, ctx.n_want, ctx.max_keys = T, R, nw, max_keys
+        ctx.n_decode = n_decode
+        ctx.decode_tokens = b.dview("decode_tokens", max(n_decode, 1))
         ctx.tokens, ctx.positions = b.dview("tokens", T), b.dview("positions", T)
         ctx.token_req, ctx.want_rows = b.dview("token_req", T), b.dview("want_rows", max(nw, 1))
         ctx.q_start, ctx.kv_len = b.dview("q_start", R + 1), b.dview("kv_len", R)
@@ -242,7 +248,7 @@ class Engine:
             bound *= 2
         ctx.max_keys = min(bound, self.plan.max_positions)
         key = (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
-               ctx.max_keys)
+               ctx.max_keys, ctx.n_decode)
         before_buf = self.logits
         out = self._logits_buffer(max(ctx.n_want, 1))
         if out is not before_buf:

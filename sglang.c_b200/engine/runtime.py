@@ -63,8 +63,15 @@ class Runtime:
             ops.kv_write(k, v, cache, grp.slots, n_kv_heads, head_dim)
         if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
-            # prompt portions (and any decoded tokens beside them): 128-query tiles on the tensor cores
-            return ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads,
-                                            scale, window, ctx.R, ctx.max_q_len)
+            # prompt portions in 128-query tiles on the tensor cores; single decoded tokens beside
+            # them go to the split-key kernel (a tile of one query would waste the other 127 rows)
+            split = ctx.n_decode > 0
+            ops.attention_prefill_tc(q, cache, grp.block_table, ctx.q_start, ctx.kv_len, out, n_heads,
+                                     scale, window, ctx.R, ctx.max_q_len, skip_single=split)
+            if split:
+                ops.attention_decode(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
+                                     scale, window, ctx.max_keys, token_list=ctx.decode_tokens,
+                                     n_tokens=ctx.n_decode)
+            return
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
                            scale, window, ctx.max_keys)

@@ -78,6 +78,8 @@ class StepContext:
         self.h_state_slots = []
         self.max_keys = 0
         self.max_q_len = 0
+        self.n_decode = 0              # tokens of requests that bring exactly one token
+        self.decode_tokens = None      # their indices (device int32), meaningful in mixed steps
         self.groups: List[GroupStep] = []
         self.err_flag = None
 
@@ -100,6 +102,7 @@ class StepBuffers:
     def __init__(self, device, t_cap, r_cap, b_cap, n_groups):
         self.t_cap, self.r_cap, self.b_cap, self.n_groups = t_cap, r_cap, b_cap, n_groups
         sizes = [("tokens", t_cap), ("positions", t_cap), ("token_req", t_cap), ("want_rows", t_cap),
+                 ("decode_tokens", r_cap),
                  ("q_start", r_cap + 1), ("kv_len", r_cap), ("state_slots", r_cap)]
         for g in range(n_groups):
             sizes += [(f"slots{g}", t_cap), (f"bt{g}", r_cap * b_cap)]

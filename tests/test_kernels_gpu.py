@@ -463,3 +463,26 @@ def test_attention_decode_writes_new_keys_itself(case_id):
                          max(lens), k_new=k_new, v_new=v_new, slots=slots)
     assert float((out.double().cpu() - ref).abs().max()) < 2e-2
     assert torch.equal(holed, want_cache)
+
+
+def test_attention_kernels_share_a_mixed_step():
+    """Portions of some requests beside single tokens of others: the tile kernel serves the
+    portions and skips the single tokens, the split-key kernel serves exactly those."""
+    ops = _ops()
+    lens, q_lens, H, Hkv, D, ps = [300, 200, 77, 513, 64], [44, 1, 1, 130, 1], 4, 2, 64, 16
+    c = _paged_case(lens, q_lens, H, Hkv, D, ps, torch.bfloat16, seed=900)
+    scale = 1.0 / math.sqrt(D)
+    T = c["q"].shape[0]
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    singles = [int(q_start[r]) for r, n in enumerate(q_lens) if n == 1]
+    token_list = torch.tensor(singles + [0, 0], dtype=torch.int32, device=DEV)
+    out = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_prefill_tc(c["q"], c["cache"], c["bt"], q_start, kv_len, out, H, scale, None, len(lens),
+                             max(q_lens), skip_single=True)
+    torch.cuda.synchronize()
+    assert all(bool(torch.isnan(out[t]).all()) for t in singles)          # left for the other kernel
+    ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, scale, None,
+                         max(lens), token_list=token_list, n_tokens=len(singles))
+    ref = _attention_reference(c, H, Hkv, D, scale, None)
+    assert float((out.double().cpu() - ref).abs().max()) < 2e-2

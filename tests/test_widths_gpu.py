@@ -1,0 +1,59 @@
+"""The layer widths of GPT-2 small, medium and XL (two layers deep, a small vocabulary so that
+the plain implementation stays quick): widths and head counts that are no power of two (1600
+wide, 25 heads, 6400 inner) through the real kernels, whole and cut, in both precisions."""
+import numpy as np
+import pytest
+
+import plain_gpt2
+import traces
+
+pytestmark = pytest.mark.gpu
+
+WIDTHS = {
+    "small": dict(n_embd=768, n_head=12, n_inner=3072),
+    "medium": dict(n_embd=1024, n_head=16, n_inner=4096),
+    "xl": dict(n_embd=1600, n_head=25, n_inner=6400),
+}
+# logits of these models are a few tenths in size (standard init, vocabulary rows N(0, 0.02))
+TOL = {"float32": 5e-5, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def width_dirs(tmp_path_factory):
+    from sglang_c_b200.config import resolve_architecture
+    from sglang_c_b200.weights import write_random_model
+    base = tmp_path_factory.mktemp("widths")
+    made = {}
+
+    def get(name, store):
+        if (name, store) not in made:
+            d = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=2, vocab_size=1031,
+                     n_positions=512, layer_norm_epsilon=1e-5, activation_function="gelu_new", **WIDTHS[name])
+            arch = resolve_architecture(d)
+            made[(name, store)] = write_random_model(str(base / f"{name}_{store}"), arch,
+                                                     arch.config_class.from_dict(d), 9, scheme="varied",
+                                                     store_dtype=store)
+        return made[(name, store)]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["small", "medium", "xl"])
+def test_real_widths_whole_and_cut(width_dirs, tmp_path, name, dtype):
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.engine.replay import replay
+    d = width_dirs(name, dtype)
+    reqs = {"a": traces.random_tokens(1, 150, 1031), "b": traces.random_tokens(2, 37, 1031),
+            "c": traces.random_tokens(3, 260, 1031)}
+    ref = {rid: plain_gpt2.forward_dir(d, toks) for rid, toks in reqs.items()}
+    prompt_len = {"a": 130, "b": 20, "c": 250}
+    for mode, steps in (("whole", traces.whole(reqs)), ("mixed", traces.mixed(reqs, prompt_len, seed=2))):
+        eng = Engine.from_dir(d, dtype=dtype, page_size=16, n_pages=traces.peak_tokens(steps) // 16,
+                              max_requests=4, max_step_tokens=512)
+        out = str(tmp_path / mode)
+        replay(eng, traces.to_lines(steps), out)
+        got = traces.collect(steps, out, 1031)
+        err, where = traces.max_error(got, ref)
+        assert err < TOL[dtype], f"{name} {mode}: max error {err} at {where}"
+        eng.check_device_errors()

@@ -29,6 +29,9 @@ sys.path.insert(0, ROOT)
 SMALL = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=12, n_embd=768, n_head=12,
              n_inner=3072, vocab_size=50257, n_positions=1024, layer_norm_epsilon=1e-5,
              activation_function="gelu_new")
+MEDIUM = dict(SMALL, n_layer=24, n_embd=1024, n_head=16, n_inner=4096)
+XL = dict(SMALL, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)
+MODELS = {"small": SMALL, "medium": MEDIUM, "xl": XL}
 CONTEXT = 512
 BATCH = 8
 PAGE = 16
@@ -227,6 +230,41 @@ def time_e2e(model_dir, batch, context, steps, warmup):
     return (s.stats.decode_tokens - n0) / dt, h2d, d2h
 
 
+def run_mixed(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
+    """The mixed workload: requests with uniform random prompt lengths in [16, 1024] and max_new
+    greedy tokens each, all submitted at once to the scheduler (continuous batching, prompt
+    portions beside decode tokens).  Returns a dict for the JSON line."""
+    import numpy as np
+    import torch
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    rng = np.random.default_rng(seed)
+    P = cfg_d["n_positions"]
+    lens = [int(n) for n in rng.integers(16, P - max_new + 1, size=n_requests)]
+    s = sched_new(model_dir, seed=seed, dtype="bfloat16", page_size=PAGE,
+                  max_tokens=sum(n + max_new + PAGE for n in lens), max_requests=n_requests,
+                  max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
+    V = cfg_d["vocab_size"]
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+    prompts = [[int(t) for t in rng.integers(0, V, size=n)] for n in lens]
+    # warm the kernels and a few graph shapes on a throw-away request
+    w = s.submit_ids(prompts[0][:64], 4, sp)
+    s.run_until_done()
+    s.poll()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for p in prompts:
+        assert s.submit_ids(p, max_new, sp) > 0
+    steps = s.run_until_done()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = s.get_stats()
+    gen = n_requests * max_new
+    return {"requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": gen, "seconds": dt,
+            "steps": steps, "generated_tok_s": gen / dt, "total_tok_s": (gen + sum(lens)) / dt,
+            "n_preempt": st.n_preempt, "graph_replays": s.engine.graph_replays}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,6 +273,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--model", default="small", choices=sorted(MODELS),
+                    help="layer sizes: GPT-2 small (the default and the headline), medium or xl")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="decode: the contract's line; mixed: 64 requests with prompts of 16..1024 "
+                         "tokens and 128 generated tokens each through the scheduler")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -251,10 +294,19 @@ def main():
     from sglang_c_b200.csrc import ops
     from sglang_c_b200.engine import Engine
     pk = peaks()
-    n_layer = args.layers or SMALL["n_layer"]
-    cfg_d = dict(SMALL, n_layer=n_layer)
+    base = MODELS[args.model]
+    n_layer = args.layers or base["n_layer"]
+    cfg_d = dict(base, n_layer=n_layer)
     tmp = tempfile.mkdtemp(prefix="sglc_bench_")
-    model_dir = make_model(tmp, SMALL, n_layer)
+    model_dir = make_model(tmp, base, n_layer)
+    if args.workload == "mixed":
+        r = run_mixed(model_dir, cfg_d)
+        print(json.dumps({"metric": "mixed workload: generated tok/s through the scheduler", "value":
+                          r["generated_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+                          "data": "synthetic: seeded random weights and uniform random token ids",
+                          "config": {"model": f"gpt2-{args.model} layer sizes, random weights",
+                                     "n_layer": n_layer, "n_layer_full": base["n_layer"]}, "mixed": r}))
+        return 0
     eng = Engine.from_dir(model_dir, dtype="bfloat16", page_size=PAGE,
                           max_tokens=64 * (CONTEXT + 256), max_requests=64, max_step_tokens=PREFILL_TOKENS)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")     # larger than the 126 MB L2
@@ -286,14 +338,14 @@ def main():
     e2e_value, h2d, d2h = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
 
     out = {
-        "metric": "decode tok/s at batch 8, context 512 (GPT-2 small layer sizes, random weights)",
+        "metric": f"decode tok/s at batch 8, context 512 (GPT-2 {args.model} layer sizes, random weights)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
-        "config": {"model": "gpt2-small layer sizes, random weights", "n_layer": n_layer,
-                   "n_layer_full": SMALL["n_layer"], "n_embd": SMALL["n_embd"], "n_head": SMALL["n_head"],
-                   "n_inner": SMALL["n_inner"], "vocab_size": SMALL["vocab_size"],
-                   "n_positions": SMALL["n_positions"], "global_batch": BATCH, "seq_len": CONTEXT,
+        "config": {"model": f"gpt2-{args.model} layer sizes, random weights", "n_layer": n_layer,
+                   "n_layer_full": base["n_layer"], "n_embd": base["n_embd"], "n_head": base["n_head"],
+                   "n_inner": base["n_inner"], "vocab_size": base["vocab_size"],
+                   "n_positions": base["n_positions"], "global_batch": BATCH, "seq_len": CONTEXT,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "prefill_tokens": PREFILL_TOKENS,
                    "prefill_shape": "2 prompts x 1024", "l2": "flushed between timed steps",
                    "timing": "CUDA events per step, mean", "cuda_graph": "decode step replays a graph",

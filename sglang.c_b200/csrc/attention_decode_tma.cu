@@ -1,0 +1,402 @@
+// Attention for single decoded tokens, keys and values staged through shared memory by TMA.
+// The same arithmetic and the same merge as attention_decode.cu (one block per (token, head,
+// key range); ranges merged in range order inside a thread-block cluster), but the range's
+// pages are brought in as one 5-D TMA box per page and K/V instead of per-thread loads held in
+// registers.  A block then needs few registers and about 40 KB of shared memory, so five or
+// more blocks fit on an SM: at large batches, where the register version is bound by how many
+// blocks an SM holds, this one keeps several times more bytes in flight.
+// Head sizes 64 and 128, bfloat16, up to 8 key ranges (other cases: attention_decode.cu).
+// The reference's counterparts are named in attention_decode.cu.
+#include <string.h>
+
+#include <mutex>
+#include <utility>
+#include <vector>
+
+#include "common.cuh"
+#include "tc_common.cuh"
+
+SGLC_DEFINE_ERROR_STRING()
+
+namespace {
+using namespace tc;
+constexpr int THREADS = 128;
+constexpr int WARPS = THREADS / 32;
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void st_peer_f32(uint32_t raddr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
+}
+
+struct Args {
+  const __nv_bfloat16* q;
+  int q_stride;
+  __nv_bfloat16* cache;
+  const int* block_table;
+  int bt_stride;
+  const int* token_req;      // null: token t is the step's t-th request
+  const int* positions;
+  const int* token_list;     // null: the launch serves tokens 0..T-1
+  __nv_bfloat16* out;
+  int o_stride;
+  int H, Hkv, page_size;
+  float scale;
+  int window;
+  int n_splits, chunk_cap, rows_cap, nb_max;
+  const __nv_bfloat16* k_new;   // optional: the step's own keys / values and their cache slots
+  const __nv_bfloat16* v_new;
+  int new_stride;
+  const int* slots;
+  int* err;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Args a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  // [K rows_cap x D][V rows_cap x D][q D floats][part WARPS*256][scores rows_cap][pages nb_max][records 8*(D+2)]
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* sV = sK + (size_t)a.rows_cap * D;
+  float* sq = reinterpret_cast<float*>(sV + (size_t)a.rows_cap * D);
+  float* part = sq + D;
+  float* sc = part + WARPS * 256;
+  int* spage = reinterpret_cast<int*>(sc + a.rows_cap);
+  float* recs = reinterpret_cast<float*>(spage + a.nb_max);
+  __shared__ float red[33];
+  __shared__ int s_meta[2];
+  __shared__ int s_abort;
+  __shared__ __align__(8) uint64_t load_bar;
+  __shared__ __align__(8) uint64_t merge_bar;
+
+  const int t = a.token_list ? a.token_list[blockIdx.x] : blockIdx.x;
+  const int h = blockIdx.y, sp = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_splits = a.n_splits, ps = a.page_size;
+  pdl_launch_dependents();
+  if (tid == 0) {
+    mbar_init(&load_bar, 1);
+    if (n_splits > 1 && sp == 0) mbar_init(&merge_bar, (uint32_t)(n_splits - 1));
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  if (n_splits > 1) {
+    // block 0's merge barrier exists before any block may signal it: arrive now, wait later
+    __syncwarp();
+    cluster_arrive();
+  }
+  // Before waiting for the kernel ahead: the step's metadata and the pages of EARLIER
+  // positions, which that kernel cannot have written.
+  if (a.token_req == nullptr) {
+    const int* bt = a.block_table + (size_t)t * a.bt_stride;
+    for (int i = tid; i < a.nb_max; i += THREADS) spage[i] = bt[i];
+    if (tid == 0) { s_meta[0] = t; s_meta[1] = a.positions[t]; }
+  } else {
+    if (tid == 0) { s_meta[0] = a.token_req[t]; s_meta[1] = a.positions[t]; }
+  }
+  __syncthreads();
+  const int r = s_meta[0];
+  const int pos = s_meta[1];
+  if (a.token_req != nullptr) {
+    const int* bt = a.block_table + (size_t)r * a.bt_stride;
+    int need = pos / ps + 1;
+    if (need > a.nb_max) need = a.nb_max;
+    for (int i = tid; i < need; i += THREADS) spage[i] = bt[i];
+    __syncthreads();
+  }
+  const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+  const int n = pos - lo + 1;
+  int chunk = (n + n_splits - 1) / n_splits;
+  if (chunk > a.chunk_cap) chunk = a.chunk_cap;      // cannot happen when the host sized chunk_cap
+  const int k0 = lo + sp * chunk;
+  int k1 = k0 + chunk;
+  if (k1 > pos + 1) k1 = pos + 1;
+  const int nk = k1 > k0 ? k1 - k0 : 0;
+  const int G = a.H / a.Hkv;
+  const int hk = h / G;
+  const int pg0 = k0 / ps;
+  const int pg1 = nk > 0 ? (k1 - 1) / ps : pg0 - 1;   // inclusive
+  const int row0 = k0 - pg0 * ps;                     // the range's first key within the staged pages
+  if (tid == 0 && nk > 0) {
+    const int npg = pg1 - pg0 + 1;
+    mbar_expect_tx(&load_bar, (uint32_t)npg * 2u * (uint32_t)ps * (uint32_t)D * 2u);
+    for (int pi = pg0; pi <= pg1; pi++) {
+      const int page = spage[pi];
+      tma_load_5d(sK + (size_t)(pi - pg0) * ps * D, &map_kv, &load_bar, 0, 0, hk, 0, page);
+      tma_load_5d(sV + (size_t)(pi - pg0) * ps * D, &map_kv, &load_bar, 0, 0, hk, 1, page);
+    }
+  }
+  pdl_wait();
+  // now the kernel ahead is complete: the query, and the token's own key and value
+  const __nv_bfloat16* qp = a.q + (size_t)t * a.q_stride + (size_t)h * D;
+  for (int d = tid; d < D; d += THREADS) sq[d] = __bfloat162float(qp[d]) * a.scale;
+  bool ok = true;
+  if (nk > 0) {
+    volatile int* af = &s_abort;
+    ok = mbar_wait(&load_bar, 0, af);
+  }
+  const bool fused = a.k_new != nullptr;
+  if (ok && pos >= k0 && pos < k1) {
+    // the token's own row: from the step's rows (and into the cache), or re-read from the cache,
+    // where the kernel ahead put it after the page was requested
+    const size_t page_elems = (size_t)2 * a.Hkv * ps * D;
+    const size_t head_off = (size_t)hk * ps * D, v_off = (size_t)a.Hkv * ps * D;
+    const __nv_bfloat16* ksrc;
+    const __nv_bfloat16* vsrc;
+    if (fused) {
+      ksrc = a.k_new + (size_t)t * a.new_stride + (size_t)hk * D;
+      vsrc = a.v_new + (size_t)t * a.new_stride + (size_t)hk * D;
+    } else {
+      ksrc = a.cache + (size_t)spage[pos / ps] * page_elems + head_off + (size_t)(pos % ps) * D;
+      vsrc = ksrc + v_off;
+    }
+    const int row = pos - pg0 * ps;
+    __nv_bfloat16* kdst = nullptr;
+    if (fused && h % G == 0) {
+      int slot = a.slots[t];
+      if (slot >= 0) kdst = a.cache + (size_t)(slot / ps) * page_elems + head_off + (size_t)(slot % ps) * D;
+    }
+    for (int c = tid; c < D / 8; c += THREADS) {
+      uint4 kv = reinterpret_cast<const uint4*>(ksrc)[c];
+      uint4 vv = reinterpret_cast<const uint4*>(vsrc)[c];
+      reinterpret_cast<uint4*>(sK + (size_t)row * D)[c] = kv;
+      reinterpret_cast<uint4*>(sV + (size_t)row * D)[c] = vv;
+      if (kdst) {
+        reinterpret_cast<uint4*>(kdst)[c] = kv;
+        reinterpret_cast<uint4*>(kdst + v_off)[c] = vv;
+      }
+    }
+  }
+  __syncthreads();
+
+  // LPR lanes share one key's row (16 bytes each): a warp reads KG whole rows at a time
+  constexpr int LPR = D / 8;
+  constexpr int KG = 32 / LPR;
+  const int kg = lane / LPR, dl = lane % LPR;
+  const int stride = WARPS * KG;
+  float qreg[8];
+#pragma unroll
+  for (int y = 0; y < 8; y++) qreg[y] = sq[dl * 8 + y];
+  float lmax = -INFINITY;
+  if (ok) {
+    for (int wb = warp * KG; wb < nk; wb += stride) {      // the bound is the same for the whole warp
+      const int i = wb + kg;
+      float s = 0.0f;
+      if (i < nk) {
+        uint4 u = *reinterpret_cast<const uint4*>(sK + (size_t)(row0 + i) * D + dl * 8);
+        float f[8];
+        bf16x8_to_f32(u, f);
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int y = 0; y < 8; y += 2) {
+          s0 = fmaf(qreg[y], f[y], s0);
+          s1 = fmaf(qreg[y + 1], f[y + 1], s1);
+        }
+        s = s0 + s1;
+      }
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (i < nk) {
+        if (dl == 0) sc[i] = s;
+        lmax = fmaxf(lmax, s);
+      }
+    }
+  }
+  const float m = block_max(lmax, red);
+  float lsum = 0.0f;
+  for (int i = tid; i < nk; i += THREADS) {
+    float e = expf(sc[i] - m);
+    sc[i] = e;
+    lsum += e;
+  }
+  const float l = block_sum(lsum, red);     // also orders the writes of sc before the reads below
+  float acc[8];
+#pragma unroll
+  for (int x = 0; x < 8; x++) acc[x] = 0.0f;
+  if (ok) {
+    for (int i = warp * KG + kg; i < nk; i += stride) {
+      uint4 u = *reinterpret_cast<const uint4*>(sV + (size_t)(row0 + i) * D + dl * 8);
+      float w = sc[i];
+      float f[8];
+      bf16x8_to_f32(u, f);
+#pragma unroll
+      for (int y = 0; y < 8; y++) acc[y] = fmaf(w, f[y], acc[y]);
+    }
+  }
+#pragma unroll
+  for (int y = 0; y < 8; y++) part[(warp * KG + kg) * D + dl * 8 + y] = acc[y];
+  __syncthreads();
+  constexpr int n_part = WARPS * KG;
+
+  __nv_bfloat16* op = a.out + (size_t)t * a.o_stride + (size_t)h * D;
+  if (n_splits == 1) {
+    if (!ok) {
+      if (tid == 0 && a.err) atomicExch(a.err, 1);
+      return;
+    }
+    float inv = 1.0f / l;
+    for (int d = tid; d < D; d += THREADS) {
+      float o = 0.0f;
+#pragma unroll
+      for (int w = 0; w < n_part; w++) o += part[w * D + d];
+      op[d] = __float2bfloat16_rn(o * inv);
+    }
+    return;
+  }
+  // Blocks 1.. send their (m, l, o) to block 0's shared memory and signal its barrier; block 0
+  // waits for all of them (with a limit) and merges in range order.  Nothing remote is touched by
+  // a block after its signal, and block 0 outlives every store into it.
+  constexpr int rec = D + 2;
+  __syncwarp();
+  cluster_wait();                    // pairs with the arrive at the top: block 0's barrier exists
+  float* mine = recs + (size_t)sp * rec;
+  if (sp != 0) {
+    const uint32_t dst = map_to_peer(mine, 0);
+    for (int d = tid; d < D; d += THREADS) {
+      float o = 0.0f;
+#pragma unroll
+      for (int w = 0; w < n_part; w++) o += part[w * D + d];
+      st_peer_f32(dst + (uint32_t)(2 + d) * 4u, o);
+    }
+    if (tid == 0) {
+      st_peer_f32(dst, ok ? m : -INFINITY);
+      st_peer_f32(dst + 4u, ok ? l : 0.0f);
+      if (!ok && a.err) atomicExch(a.err, 1);
+    }
+    __syncthreads();
+    if (tid == 0) mbar_arrive_peer(map_to_peer(&merge_bar, 0));
+    return;
+  }
+  for (int d = tid; d < D; d += THREADS) {
+    float o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < n_part; w++) o += part[w * D + d];
+    mine[2 + d] = o;
+  }
+  if (tid == 0) {
+    mine[0] = m;
+    mine[1] = l;
+  }
+  __syncthreads();
+  {
+    volatile int* af = &s_abort;
+    if (!mbar_wait_cluster(&merge_bar, 0, af) || !ok) {
+      if (tid == 0 && a.err) atomicExch(a.err, 1);
+      return;
+    }
+  }
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; s++) M = fmaxf(M, recs[s * rec]);
+  float L = 0.0f;
+  for (int s = 0; s < n_splits; s++) L += recs[s * rec + 1] > 0.0f ? recs[s * rec + 1] * expf(recs[s * rec] - M) : 0.0f;
+  float inv = 1.0f / L;
+  for (int d = tid; d < D; d += THREADS) {
+    float o = 0.0f;
+    for (int s = 0; s < n_splits; s++)
+      if (recs[s * rec + 1] > 0.0f) o += recs[s * rec + 2 + d] * expf(recs[s * rec] - M);
+    op[d] = __float2bfloat16_rn(o * inv);
+  }
+}
+
+// ---- host: the cache as a 5-D tensor, one box = one page's rows of one head (no swizzle) ----
+struct KeyKV { const void* p; int D, ps, Hkv, n_pages; };
+std::mutex g_mutex;
+std::vector<std::pair<KeyKV, CUtensorMap>> g_kvmaps;
+
+bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto& e : g_kvmaps)
+    if (e.first.p == cache && e.first.D == D && e.first.ps == ps && e.first.Hkv == Hkv &&
+        e.first.n_pages == n_pages) {
+      *out = e.second;
+      return true;
+    }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || ((uintptr_t)cache & 15) || ps > 256 || D > 256) return false;
+  cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, 2, (cuuint64_t)n_pages};
+  cuuint64_t strides[4] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2,
+                           (cuuint64_t)2 * Hkv * ps * D * 2};
+  cuuint32_t box[5] = {(cuuint32_t)D, (cuuint32_t)ps, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUtensorMap m;
+  CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return false;
+  if (g_kvmaps.size() > 1024) g_kvmaps.clear();
+  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages}, m});
+  *out = m;
+  return true;
+}
+
+template <int D>
+int launch(const CUtensorMap& mkv, const Args& a, int T, cudaStream_t stream) {
+  size_t smem = (size_t)2 * a.rows_cap * D * 2 +
+                ((size_t)D + (size_t)WARPS * 256 + (size_t)a.rows_cap + (size_t)a.nb_max + (size_t)8 * (D + 2)) * 4;
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    configured = smem;
+  }
+  dim3 grid(T, a.H, a.n_splits);
+  return sglc_launch(attention_decode_tma_kernel<D>, grid, dim3(THREADS), smem, stream, a.n_splits, true, mkv, a);
+}
+}  // namespace
+
+// Whether this kernel takes the case (else: the register-staged kernel of attention_decode.cu).
+SGLC_API int sglc_attention_decode_tma_supports(int D, int page_size, int n_splits) {
+  return (D == 64 || D == 128) && page_size >= 1 && page_size <= 256 && n_splits >= 1 && n_splits <= 8;
+}
+
+// Arguments as sglc_attention_decode (without the global-memory scratch); n_pages: pages of
+// the cache tensor; token_list: optional list of the T tokens to serve.
+SGLC_API int sglc_attention_decode_tma(const void* q, int q_stride, void* cache, const int* block_table,
+                                       int bt_stride, const int* token_req, const int* positions,
+                                       void* out, int o_stride, int T, int H, int Hkv, int D,
+                                       int page_size, float scale, int window, int max_keys,
+                                       int n_splits, const void* k_new, const void* v_new,
+                                       int new_stride, const int* slots, int* err,
+                                       const int* token_list, int n_pages, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_pages <= 0)
+    return SGLC_ERR_ARGUMENT;
+  if (!sglc_attention_decode_tma_supports(D, page_size, n_splits) || H > 65535) return SGLC_ERR_UNSUPPORTED;
+  if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return SGLC_ERR_UNSUPPORTED;
+  if (k_new && (!v_new || !slots || new_stride % 8 != 0 || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15)))
+    return SGLC_ERR_UNSUPPORTED;
+  if ((page_size * D * 2) % 128 != 0) return SGLC_ERR_UNSUPPORTED;   // page blocks stay 128-byte aligned in shared memory
+  CUtensorMap mkv;
+  if (!get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages)) return SGLC_ERR_UNSUPPORTED;
+  Args a;
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.cache = (__nv_bfloat16*)cache;
+  a.block_table = block_table; a.bt_stride = bt_stride;
+  a.token_req = token_req; a.positions = positions; a.token_list = token_list;
+  a.out = (__nv_bfloat16*)out; a.o_stride = o_stride;
+  a.H = H; a.Hkv = Hkv; a.page_size = page_size;
+  a.scale = scale; a.window = window;
+  a.n_splits = n_splits;
+  int eff = window > 0 && window < max_keys ? window : max_keys;
+  a.chunk_cap = (eff + n_splits - 1) / n_splits;
+  // whole pages are staged: the range may start and end inside a page
+  a.rows_cap = ((a.chunk_cap + page_size - 1) / page_size + 1) * page_size;
+  a.nb_max = (max_keys + page_size - 1) / page_size;
+  if (a.nb_max > bt_stride) a.nb_max = bt_stride;
+  a.k_new = (const __nv_bfloat16*)k_new; a.v_new = (const __nv_bfloat16*)v_new;
+  a.new_stride = new_stride; a.slots = slots;
+  a.err = err;
+  if (D == 64) return launch<64>(mkv, a, T, stream);
+  return launch<128>(mkv, a, T, stream);
+}

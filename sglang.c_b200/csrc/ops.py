@@ -238,8 +238,12 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
 
 
 # ---------------------------------------------------------------------------
+USE_TMA_DECODE = True      # tests switch it off to reach the register-staged kernel at head size 64/128
+
+
 def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
-                     max_keys, k_new=None, v_new=None, slots=None, token_list=None, n_tokens=None):
+                     max_keys, k_new=None, v_new=None, slots=None, token_list=None, n_tokens=None,
+                     n_splits=None):
     """Attention of single decoded tokens over the paged bfloat16 cache, keys split across
     blocks and merged in a fixed order.  With k_new/v_new/slots (the step's own keys and
     values, [T, n_kv_heads*head_dim] views, and their cache slots) the same launch also writes
@@ -262,7 +266,7 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
         raise KernelError("attention_decode: query/output rows do not match heads x head_dim")
     lib = build.load("attention_decode")
     ws, counters, err = _tc_buffers(q.device)
-    splits = lib.sglc_attention_decode_splits(T, n_heads, int(max_keys))
+    splits = int(n_splits) if n_splits else lib.sglc_attention_decode_splits(T, n_heads, int(max_keys))
     need_ws, need_c = ctypes.c_longlong(0), ctypes.c_int(0)
     lib.sglc_attention_decode_scratch(T, n_heads, D, splits, ctypes.byref(need_ws), ctypes.byref(need_c))
     if need_ws.value > ws.numel() or need_c.value > counters.numel():
@@ -274,6 +278,20 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                 or k_new.stride(1) != 1 or v_new.stride(1) != 1 or k_new.stride(0) != v_new.stride(0):
             raise KernelError("attention_decode: new keys/values do not match the cache")
         new_stride = k_new.stride(0)
+    if D in (64, 128) and splits <= 8 and (page_size * D * 2) % 128 == 0 and page_size <= 256 \
+            and USE_TMA_DECODE and T * n_heads * splits <= 1536:
+        # keys and values staged through shared memory by TMA (measured faster up to about a
+        # thousand blocks; beyond, the register-staged kernel is a few percent ahead)
+        tlib = build.load("attention_decode_tma")
+        code = tlib.sglc_attention_decode_tma(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                              block_table.stride(0), _ptr(token_req), _ptr(positions),
+                                              _ptr(out), out.stride(0), T, n_heads, Hkv, D, page_size,
+                                              ctypes.c_float(scale), int(window or 0), int(max_keys), splits,
+                                              _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots), _ptr(err),
+                                              _ptr(token_list), n_pages, _stream())
+        if code != -2:                      # -2: the range does not fit its shared memory; use the other kernel
+            _check(tlib, code, f"attention_decode_tma (head_dim {D}, up to {max_keys} keys)")
+            return
     code = lib.sglc_attention_decode(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
                                      block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
                                      out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),

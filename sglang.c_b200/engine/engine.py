@@ -213,6 +213,12 @@ class Engine:
 
         ctx.T, ctx.R, ctx.n_want, ctx.max_keys = T, R, nw, max_keys
         ctx.n_decode = n_decode
+        if self.use_graphs and self.model.graph_safe:
+            # a step whose launch shapes have a captured graph needs nothing but the upload above
+            hit = self._graph_lookup(ctx)
+            if hit is not None:
+                self.steps_run += 1
+                return hit
         ctx.decode_tokens = b.dview("decode_tokens", max(n_decode, 1))
         ctx.tokens, ctx.positions = b.dview("tokens", T), b.dview("positions", T)
         ctx.token_req, ctx.want_rows = b.dview("token_req", T), b.dview("want_rows", max(nw, 1))
@@ -234,6 +240,29 @@ class Engine:
         self.steps_run += 1
         return logits
 
+    def _graph_key(self, ctx):
+        bound = 128
+        while bound < ctx.max_keys:
+            bound *= 2
+        bound = min(bound, self.plan.max_positions)
+        return (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
+                bound, ctx.n_decode), bound
+
+    def _graph_lookup(self, ctx):
+        """Replay the graph of this step's shape if there is one (and its output buffer still
+        stands); returns the logits view or None."""
+        from ..csrc import ops
+        key, _ = self._graph_key(ctx)
+        hit = self._graphs.get(key)
+        if hit is None or self.logits is None or self.logits.shape[0] < max(ctx.n_want, 1):
+            return None
+        graph, n_launches = hit
+        self._graphs[key] = self._graphs.pop(key)          # most recently used last
+        graph.replay()
+        ops.LAUNCHES += n_launches
+        self.graph_replays += 1
+        return self.logits[:ctx.n_want]
+
     def _forward_graphed(self, ctx):
         """Replay a CUDA graph when this step's launch shapes have been seen before.  The
         shapes depend on the number of tokens, requests and wanted rows, on the longest
@@ -243,12 +272,7 @@ class Engine:
         time it is seen, is captured the second time, and replayed afterwards; the least
         recently used graphs are dropped beyond `max_graphs`."""
         from ..csrc import ops
-        bound = 128
-        while bound < ctx.max_keys:
-            bound *= 2
-        ctx.max_keys = min(bound, self.plan.max_positions)
-        key = (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
-               ctx.max_keys, ctx.n_decode)
+        key, ctx.max_keys = self._graph_key(ctx)
         before_buf = self.logits
         out = self._logits_buffer(max(ctx.n_want, 1))
         if out is not before_buf:

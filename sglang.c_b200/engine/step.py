@@ -130,8 +130,12 @@ class StepBuffers:
         o, cap = self.offsets[name]
         return self.dev[o:o + (cap if n is None else n)]
 
-    def upload(self):
-        self.dev.copy_(self.host, non_blocking=True)
+    def upload(self, n_words=None):
+        """Copy the packed block (or its first n_words) to the device on the current stream."""
+        if n_words is None or n_words >= self.total:
+            self.dev.copy_(self.host, non_blocking=True)
+        else:
+            self.dev[:n_words].copy_(self.host[:n_words], non_blocking=True)
         self.copied.record()
         self._copied_once = True
 

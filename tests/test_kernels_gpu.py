@@ -486,3 +486,26 @@ def test_attention_kernels_share_a_mixed_step():
                          max(lens), token_list=token_list, n_tokens=len(singles))
     ref = _attention_reference(c, H, Hkv, D, scale, None)
     assert float((out.double().cpu() - ref).abs().max()) < 2e-2
+
+
+def test_both_decode_attention_kernels_at_head_size_64():
+    """Head sizes 64 and 128 go to the TMA-staged kernel by default; the register-staged one
+    must give the same there (it serves the other head sizes and more than 8 key ranges)."""
+    ops = _ops()
+    for case_id in (5, 6, 7):
+        lens, _, H, Hkv, D, ps, window = ATTN_CASES[case_id]
+        c = _paged_case(lens, [1] * len(lens), H, Hkv, D, ps, torch.bfloat16, seed=400 + case_id)
+        scale = 1.0 / math.sqrt(D)
+        ref = _attention_reference(c, H, Hkv, D, scale, window)
+        outs = []
+        for use_tma in (True, False):
+            ops.USE_TMA_DECODE = use_tma
+            try:
+                out = torch.full((len(lens), H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+                ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, scale,
+                                     window, max(lens))
+            finally:
+                ops.USE_TMA_DECODE = True
+            assert float((out.double().cpu() - ref).abs().max()) < 2e-2, (case_id, use_tma)
+            outs.append(out)
+        assert float((outs[0].float() - outs[1].float()).abs().max()) < 1e-2

@@ -336,6 +336,314 @@ bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int
   return true;
 }
 
+// ---- streaming variant for large batches -------------------------------------------------
+// A fixed number of blocks per SM, each walking a list of (token, head) items.  One warp feeds
+// a ring of shared-memory stages with the item's pages (TMA, one box per page and K/V), and
+// runs ahead of the four warps that consume them, across item boundaries, so a block never
+// waits for a round trip between items: at large batches the one-shot kernels are bound by
+// block lifetime times the number of blocks an SM holds, this one by bytes.  A group of D/8
+// lanes owns every NG-th key of a stage and keeps its own running maximum, sum and output
+// (no block-wide step per stage); the groups are merged once per item in group order.  The
+// token's own key and value come from the step's rows (or the cache) by plain loads after
+// the dependency wait and are folded in by group 0, which also writes them into the cache.
+struct StreamArgs {
+  Args b;
+  int n_items;        // tokens served x heads
+  int tile_pages;     // pages per stage
+  int n_stages;
+  int nb_cap;         // most pages an item can span (sizes nothing; checked by the host)
+};
+constexpr int S_WARPS = 4;                  // consumer warps; warp S_WARPS produces
+constexpr int S_THREADS = (S_WARPS + 1) * 32;
+constexpr int S_MAX_STAGES = 8;
+constexpr int S_PMAX = 8;                   // page ids held per producer lane: 256 pages per item
+
+struct ItemGeom {
+  int lo, first_page, k_base, n_rows, n_tiles, n_pages;
+};
+__device__ __forceinline__ ItemGeom item_geom(int pos, int window, int ps, int tile_keys) {
+  ItemGeom g;
+  g.lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  g.first_page = g.lo / ps;
+  g.k_base = g.first_page * ps;
+  g.n_rows = pos - g.k_base;                       // cached rows ahead of the token's own
+  g.n_tiles = (g.n_rows + tile_keys - 1) / tile_keys;
+  g.n_pages = (g.n_rows + ps - 1) / ps;
+  return g;
+}
+
+template <int D>
+__global__ void __launch_bounds__(S_THREADS)
+attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const StreamArgs sa) {
+  const Args& a = sa.b;
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int LPR = D / 8;                // lanes per key row
+  constexpr int KG = 32 / LPR;              // key groups per warp
+  constexpr int NG = S_WARPS * KG;          // key groups per block
+  constexpr int REC = D + 2;
+  const int ps = a.page_size;
+  const int tile_keys = sa.tile_pages * ps;
+  const int NS = sa.n_stages;
+  const size_t stage_elems = (size_t)2 * tile_keys * D;      // K rows, then V rows
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem);
+  float* merge = reinterpret_cast<float*>(smem + (size_t)NS * stage_elems * 2);   // [2][NG][REC]
+  __shared__ __align__(8) uint64_t full[S_MAX_STAGES];
+  __shared__ __align__(8) uint64_t empty[S_MAX_STAGES];
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = a.H, G = a.H / a.Hkv;
+  pdl_launch_dependents();
+  if (tid == 0) {
+    for (int s = 0; s < NS; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], S_WARPS);
+    }
+    s_abort = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  volatile int* af = &s_abort;
+
+  if (warp == S_WARPS) {
+    // ---- producer: metadata and pages of EARLIER positions only, which the kernel ahead
+    // cannot have written, so nothing here waits for it ----
+    auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
+    auto pos_of = [&](int item) { return item < sa.n_items ? a.positions[token_of(item)] : 0; };
+    auto load_ids = [&](int item, int pos, int* pid) {
+      const int t = token_of(item);
+      const int r = a.token_req ? a.token_req[t] : t;
+      const ItemGeom g = item_geom(pos, a.window, ps, tile_keys);
+      const int* bt = a.block_table + (size_t)r * a.bt_stride + g.first_page;
+#pragma unroll
+      for (int k = 0; k < S_PMAX; k++) {
+        int i = k * 32 + lane;
+        pid[k] = i < g.n_pages ? bt[i] : 0;
+      }
+    };
+    int it = 0;
+    int item = blockIdx.x;
+    int pos_cur = pos_of(item), pos_nxt = pos_of(item + gridDim.x);
+    int pid_cur[S_PMAX], pid_nxt[S_PMAX];
+    if (item < sa.n_items) load_ids(item, pos_cur, pid_cur);
+    bool ok = true;
+    while (item < sa.n_items && ok) {
+      const int item_n = item + gridDim.x;
+      if (item_n < sa.n_items) load_ids(item_n, pos_nxt, pid_nxt);
+      const int pos_n2 = pos_of(item_n + gridDim.x);
+      const ItemGeom g = item_geom(pos_cur, a.window, ps, tile_keys);
+      const int hk = (item % H) / G;
+      for (int j = 0; j < g.n_tiles && ok; j++, it++) {
+        const int s = it % NS;
+        if (it >= NS) {
+          int w = 1;
+          if (lane == 0) w = mbar_wait(&empty[s], ((it / NS) - 1) & 1, af) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, w, 0) != 0;
+          if (!ok) break;
+        }
+        const int pg0 = j * sa.tile_pages;
+        const int npg = min(sa.tile_pages, g.n_pages - pg0);
+        __nv_bfloat16* sk = stages + (size_t)s * stage_elems;
+        __nv_bfloat16* sv = sk + (size_t)tile_keys * D;
+        if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)npg * 2u * (uint32_t)ps * (uint32_t)D * 2u);
+        for (int p = 0; p < npg; p++) {
+          const int idx = pg0 + p;
+          int v = 0;
+#pragma unroll
+          for (int k = 0; k < S_PMAX; k++)
+            if (k == (idx >> 5)) v = pid_cur[k];
+          const int page = __shfl_sync(0xffffffffu, v, idx & 31);
+          if (lane == 0) {
+            tma_load_5d(sk + (size_t)p * ps * D, &map_kv, &full[s], 0, 0, hk, 0, page);
+            tma_load_5d(sv + (size_t)p * ps * D, &map_kv, &full[s], 0, 0, hk, 1, page);
+          }
+        }
+      }
+      item = item_n;
+      pos_cur = pos_nxt;
+      pos_nxt = pos_n2;
+#pragma unroll
+      for (int k = 0; k < S_PMAX; k++) pid_cur[k] = pid_nxt[k];
+    }
+    if (!ok && lane == 0) {
+      // wait, with a limit, for the copies still in flight before the block may exit
+      for (int i = max(0, it - NS); i < it; i++) mbar_wait(&full[i % NS], (i / NS) & 1, af);
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  const int kg = lane / LPR, dl = lane % LPR;
+  const int g_id = warp * KG + kg;
+  const int rows_per_group = tile_keys / NG;
+  const float qscale = a.scale * 1.4426950408889634f;      // scores in base-2 exponent units
+  const size_t page_elems = (size_t)2 * a.Hkv * ps * D;
+  const size_t v_off = (size_t)a.Hkv * ps * D;
+  const bool fused = a.k_new != nullptr;
+  pdl_wait();       // queries and the step's own keys and values come from the kernel ahead
+  auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
+  // what an item needs from global memory is requested one item ahead
+  int item = blockIdx.x;
+  int t_nxt = 0, pos_nxt = 0;
+  uint4 q_nxt = make_uint4(0u, 0u, 0u, 0u);
+  if (item < sa.n_items) {
+    t_nxt = token_of(item);
+    pos_nxt = a.positions[t_nxt];
+    q_nxt = *reinterpret_cast<const uint4*>(a.q + (size_t)t_nxt * a.q_stride + (size_t)(item % H) * D + dl * 8);
+  }
+  int it = 0;
+  bool ok = true;
+  for (int n = 0; item < sa.n_items; item += gridDim.x, n++) {
+    const int t = t_nxt, pos = pos_nxt, h = item % H, hk = h / G;
+    float qreg[8];
+    bf16x8_to_f32(q_nxt, qreg);
+#pragma unroll
+    for (int y = 0; y < 8; y++) qreg[y] *= qscale;
+    // the token's own key and value (group 0 folds them in at the end)
+    uint4 kn = make_uint4(0u, 0u, 0u, 0u), vn = kn;
+    int slot = -1;
+    if (g_id == 0) {
+      const __nv_bfloat16* ksrc;
+      const __nv_bfloat16* vsrc;
+      if (fused) {
+        ksrc = a.k_new + (size_t)t * a.new_stride + (size_t)hk * D;
+        vsrc = a.v_new + (size_t)t * a.new_stride + (size_t)hk * D;
+        slot = a.slots[t];
+      } else {
+        const int r = a.token_req ? a.token_req[t] : t;
+        const int page = a.block_table[(size_t)r * a.bt_stride + pos / ps];
+        ksrc = a.cache + (size_t)page * page_elems + (size_t)hk * ps * D + (size_t)(pos % ps) * D;
+        vsrc = ksrc + v_off;
+      }
+      kn = reinterpret_cast<const uint4*>(ksrc)[dl];
+      vn = reinterpret_cast<const uint4*>(vsrc)[dl];
+    }
+    {
+      const int item_n = item + gridDim.x;
+      if (item_n < sa.n_items) {
+        t_nxt = token_of(item_n);
+        pos_nxt = a.positions[t_nxt];
+        q_nxt = *reinterpret_cast<const uint4*>(a.q + (size_t)t_nxt * a.q_stride + (size_t)(item_n % H) * D + dl * 8);
+      }
+    }
+    const ItemGeom g = item_geom(pos, a.window, ps, tile_keys);
+    float m = -INFINITY, l = 0.0f, acc[8];
+#pragma unroll
+    for (int y = 0; y < 8; y++) acc[y] = 0.0f;
+    for (int j = 0; j < g.n_tiles; j++, it++) {
+      const int s = it % NS;
+      if (ok) ok = mbar_wait(&full[s], (it / NS) & 1, af);
+      if (ok) {
+        const __nv_bfloat16* sk = stages + (size_t)s * stage_elems;
+        const __nv_bfloat16* sv = sk + (size_t)tile_keys * D;
+        const int key0 = g.k_base + j * tile_keys;
+        for (int r0 = 0; r0 < rows_per_group; r0 += 4) {
+          float sc[4];
+          bool valid[4];
+          float mt = m;
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            const int row = g_id + NG * (r0 + u);
+            const int key = key0 + row;
+            valid[u] = (r0 + u) < rows_per_group && key >= g.lo && key < pos;
+            float sum = 0.0f;
+            if (valid[u]) {
+              uint4 kq = *reinterpret_cast<const uint4*>(sk + (size_t)row * D + dl * 8);
+              float f[8];
+              bf16x8_to_f32(kq, f);
+              float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+              for (int y = 0; y < 8; y += 2) {
+                s0 = fmaf(qreg[y], f[y], s0);
+                s1 = fmaf(qreg[y + 1], f[y + 1], s1);
+              }
+              sum = s0 + s1;
+            }
+#pragma unroll
+            for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            sc[u] = sum;
+            if (valid[u]) mt = fmaxf(mt, sum);
+          }
+          if (mt > -INFINITY) {
+            const float corr = exp2f(m - mt);        // 0 at the first keys (m = -inf)
+            l *= corr;
+#pragma unroll
+            for (int y = 0; y < 8; y++) acc[y] *= corr;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+              if (valid[u]) {
+                const int row = g_id + NG * (r0 + u);
+                const float pw = exp2f(sc[u] - mt);
+                uint4 vq = *reinterpret_cast<const uint4*>(sv + (size_t)row * D + dl * 8);
+                float f[8];
+                bf16x8_to_f32(vq, f);
+                l += pw;
+#pragma unroll
+                for (int y = 0; y < 8; y++) acc[y] = fmaf(pw, f[y], acc[y]);
+              }
+            }
+            m = mt;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);       // the stage may be refilled
+    }
+    if (g_id == 0) {
+      float f[8];
+      bf16x8_to_f32(kn, f);
+      float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+      for (int y = 0; y < 8; y += 2) {
+        s0 = fmaf(qreg[y], f[y], s0);
+        s1 = fmaf(qreg[y + 1], f[y + 1], s1);
+      }
+      float sum = s0 + s1;
+#pragma unroll
+      for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu >> (32 - LPR), sum, o);
+      const float mt = fmaxf(m, sum);
+      const float corr = exp2f(m - mt), pw = exp2f(sum - mt);
+      bf16x8_to_f32(vn, f);
+      l = l * corr + pw;
+#pragma unroll
+      for (int y = 0; y < 8; y++) acc[y] = fmaf(pw, f[y], acc[y] * corr);
+      m = mt;
+      if (fused && slot >= 0 && h % G == 0) {
+        __nv_bfloat16* kdst = a.cache + (size_t)(slot / ps) * page_elems + (size_t)hk * ps * D + (size_t)(slot % ps) * D;
+        reinterpret_cast<uint4*>(kdst)[dl] = kn;
+        reinterpret_cast<uint4*>(kdst + v_off)[dl] = vn;
+      }
+    }
+    // merge the groups in group order
+    float* mrec = merge + (size_t)(n & 1) * NG * REC;
+    float* mine = mrec + (size_t)g_id * REC;
+    if (dl == 0) {
+      mine[0] = m;
+      mine[1] = l;
+    }
+#pragma unroll
+    for (int y = 0; y < 8; y++) mine[2 + dl * 8 + y] = acc[y];
+    asm volatile("bar.sync 1, %0;" ::"n"(S_WARPS * 32) : "memory");
+    if (tid < D) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < NG; w++) M = fmaxf(M, mrec[w * REC]);
+      float L = 0.0f, o = 0.0f;
+#pragma unroll
+      for (int w = 0; w < NG; w++) {
+        const float lw = mrec[w * REC + 1];
+        if (lw > 0.0f) {
+          const float e = exp2f(mrec[w * REC] - M);
+          L += lw * e;
+          o += mrec[w * REC + 2 + tid] * e;
+        }
+      }
+      if (ok) a.out[(size_t)t * a.o_stride + (size_t)h * D + tid] = __float2bfloat16_rn(o / L);
+    }
+  }
+  if (!ok && tid == 0 && a.err) atomicExch(a.err, 1);
+}
+
 template <int D>
 int launch(const CUtensorMap& mkv, const Args& a, int T, cudaStream_t stream) {
   size_t smem = (size_t)2 * a.rows_cap * D * 2 +
@@ -399,4 +707,86 @@ SGLC_API int sglc_attention_decode_tma(const void* q, int q_stride, void* cache,
   a.err = err;
   if (D == 64) return launch<64>(mkv, a, T, stream);
   return launch<128>(mkv, a, T, stream);
+}
+
+// Whether the streaming kernel takes the case.
+SGLC_API int sglc_attention_decode_stream_supports(int D, int page_size, int max_keys, int window) {
+  if (!(D == 64 || D == 128) || page_size < 4 || page_size > 128) return 0;
+  const int NG = 4 * (32 / (D / 8));
+  int tile_pages = page_size >= 64 ? 1 : 64 / page_size;
+  if (64 % page_size != 0 && page_size < 64) return 0;
+  if ((tile_pages * page_size) % NG != 0) return 0;
+  int eff = window > 0 && window < max_keys ? window : max_keys;
+  if ((eff + page_size - 1) / page_size + 1 > 32 * S_PMAX) return 0;
+  return 1;
+}
+
+// Same arguments and result as sglc_attention_decode_tma (n_splits has no meaning here: a block
+// walks whole (token, head) items).  Meant for many items; any number is served.
+SGLC_API int sglc_attention_decode_stream(const void* q, int q_stride, void* cache, const int* block_table,
+                                          int bt_stride, const int* token_req, const int* positions,
+                                          void* out, int o_stride, int T, int H, int Hkv, int D,
+                                          int page_size, float scale, int window, int max_keys,
+                                          const void* k_new, const void* v_new, int new_stride,
+                                          const int* slots, int* err, const int* token_list,
+                                          int n_pages, cudaStream_t stream) {
+  if (T <= 0) return SGLC_OK;
+  if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_pages <= 0)
+    return SGLC_ERR_ARGUMENT;
+  if (!sglc_attention_decode_stream_supports(D, page_size, max_keys, window)) return SGLC_ERR_UNSUPPORTED;
+  if (q_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) return SGLC_ERR_UNSUPPORTED;
+  if (k_new && (!v_new || !slots || new_stride % 8 != 0 || ((uintptr_t)k_new & 15) || ((uintptr_t)v_new & 15)))
+    return SGLC_ERR_UNSUPPORTED;
+  if ((page_size * D * 2) % 128 != 0) return SGLC_ERR_UNSUPPORTED;
+  if ((long long)T * H > 0x7fffffffLL) return SGLC_ERR_UNSUPPORTED;
+  CUtensorMap mkv;
+  if (!get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages)) return SGLC_ERR_UNSUPPORTED;
+  StreamArgs sa;
+  memset(&sa, 0, sizeof(sa));
+  Args& a = sa.b;
+  a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.cache = (__nv_bfloat16*)cache;
+  a.block_table = block_table; a.bt_stride = bt_stride;
+  a.token_req = token_req; a.positions = positions; a.token_list = token_list;
+  a.out = (__nv_bfloat16*)out; a.o_stride = o_stride;
+  a.H = H; a.Hkv = Hkv; a.page_size = page_size;
+  a.scale = scale; a.window = window;
+  a.n_splits = 1;
+  a.k_new = (const __nv_bfloat16*)k_new; a.v_new = (const __nv_bfloat16*)v_new;
+  a.new_stride = new_stride; a.slots = slots;
+  a.err = err;
+  sa.n_items = T * H;
+  sa.tile_pages = page_size >= 64 ? 1 : 64 / page_size;
+  const int tile_keys = sa.tile_pages * page_size;
+  const size_t stage_bytes = (size_t)2 * tile_keys * D * 2;
+  const int NG = 4 * (32 / (D / 8));
+  const size_t fixed = (size_t)2 * NG * (D + 2) * 4;
+  // three blocks per SM, and as many stages as then fit (at least 3, at most 8)
+  int n_stages = (int)((72 * 1024 - fixed) / stage_bytes);
+  if (n_stages > S_MAX_STAGES) n_stages = S_MAX_STAGES;
+  if (n_stages < 3) n_stages = 3;
+  sa.n_stages = n_stages;
+  const size_t smem = (size_t)n_stages * stage_bytes + fixed;
+  if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+  }
+  int per_sm = (int)((220 * 1024) / (smem + 2048));
+  if (per_sm > 3) per_sm = 3;
+  if (per_sm < 1) per_sm = 1;
+  int grid = n_sm * per_sm;
+  if (grid > sa.n_items) grid = sa.n_items;
+  auto kern = D == 64 ? attention_decode_stream_kernel<64> : attention_decode_stream_kernel<128>;
+  static size_t configured[2] = {0, 0};
+  size_t& conf = configured[D == 64 ? 0 : 1];
+  if (smem > 48 * 1024 && smem > conf) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    conf = smem;
+  }
+  return sglc_launch(kern, dim3(grid), dim3(S_THREADS), smem, stream, 1, true, mkv, sa);
 }

@@ -238,16 +238,19 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None):
 
 
 # ---------------------------------------------------------------------------
+STREAM_MIN_ITEMS = 160     # (token, head) items from which the streaming decode kernel is used
 USE_TMA_DECODE = True      # tests switch it off to reach the register-staged kernel at head size 64/128
 
 
 def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
                      max_keys, k_new=None, v_new=None, slots=None, token_list=None, n_tokens=None,
-                     n_splits=None):
+                     n_splits=None, variant=None):
     """Attention of single decoded tokens over the paged bfloat16 cache, keys split across
     blocks and merged in a fixed order.  With k_new/v_new/slots (the step's own keys and
     values, [T, n_kv_heads*head_dim] views, and their cache slots) the same launch also writes
-    them into the cache; this is valid only when every request brings exactly one token."""
+    them into the cache; this is valid only when every request brings exactly one token.
+    Three kernels serve it, chosen by the size of the launch (or named by `variant`, for tests
+    and tuning: "stream", "tma", "register")."""
     _need_cuda(q, cache, block_table, token_req, positions, out, k_new, v_new, slots, token_list)
     for t, nm in ((block_table, "block_table"), (positions, "positions")):
         _i32(t, nm)
@@ -278,8 +281,26 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                 or k_new.stride(1) != 1 or v_new.stride(1) != 1 or k_new.stride(0) != v_new.stride(0):
             raise KernelError("attention_decode: new keys/values do not match the cache")
         new_stride = k_new.stride(0)
+    if variant not in (None, "stream", "tma", "register"):
+        raise KernelError(f"attention_decode: unknown variant {variant!r}")
+    if variant == "stream" or (variant is None and USE_TMA_DECODE and T * n_heads >= STREAM_MIN_ITEMS):
+        # many (token, head) items: resident blocks stream them through a ring of TMA stages
+        tlib = build.load("attention_decode_tma")
+        if tlib.sglc_attention_decode_stream_supports(D, page_size, int(max_keys), int(window or 0)) \
+                and (page_size * D * 2) % 128 == 0:
+            code = tlib.sglc_attention_decode_stream(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),
+                                                     block_table.stride(0), _ptr(token_req), _ptr(positions),
+                                                     _ptr(out), out.stride(0), T, n_heads, Hkv, D, page_size,
+                                                     ctypes.c_float(scale), int(window or 0), int(max_keys),
+                                                     _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots),
+                                                     _ptr(err), _ptr(token_list), n_pages, _stream())
+            _check(tlib, code, f"attention_decode_stream (head_dim {D}, up to {max_keys} keys)")
+            return
+        if variant == "stream":
+            raise KernelError(f"attention_decode_stream does not take head_dim {D}, page size {page_size}, "
+                              f"{max_keys} keys")
     if D in (64, 128) and splits <= 8 and (page_size * D * 2) % 128 == 0 and page_size <= 256 \
-            and USE_TMA_DECODE and T * n_heads * splits <= 1536:
+            and ((variant is None and USE_TMA_DECODE and T * n_heads * splits <= 1536) or variant == "tma"):
         # keys and values staged through shared memory by TMA (measured faster up to about a
         # thousand blocks; beyond, the register-staged kernel is a few percent ahead)
         tlib = build.load("attention_decode_tma")
@@ -289,7 +310,7 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                                               ctypes.c_float(scale), int(window or 0), int(max_keys), splits,
                                               _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots), _ptr(err),
                                               _ptr(token_list), n_pages, _stream())
-        if code != -2:                      # -2: the range does not fit its shared memory; use the other kernel
+        if code != -2 or variant == "tma":  # -2: the range does not fit its shared memory; use the other kernel
             _check(tlib, code, f"attention_decode_tma (head_dim {D}, up to {max_keys} keys)")
             return
     code = lib.sglc_attention_decode(_ptr(q), q.stride(0), _ptr(cache), _ptr(block_table),

@@ -488,6 +488,94 @@ def test_attention_kernels_share_a_mixed_step():
     assert float((out.double().cpu() - ref).abs().max()) < 2e-2
 
 
+STREAM_CASES = [
+    # lens, H, Hkv, D, page_size, window
+    ([1, 2, 17, 64, 65, 300], 3, 3, 64, 16, None),
+    ([700, 3, 130, 64], 12, 12, 64, 16, None),
+    ([90, 50, 17, 200], 2, 2, 64, 16, 24),                 # a window: its edge falls inside a page
+    ([300, 129], 6, 2, 64, 8, None),                       # grouped heads, small pages
+    ([260, 90, 1], 2, 2, 128, 16, None),                   # head size 128
+    ([200, 77], 2, 1, 128, 32, 33),
+    ([500, 64, 63], 4, 4, 64, 64, None),                   # a page per stage
+    ([130, 9], 5, 5, 64, 4, 100),
+    (list(range(1, 61)), 12, 12, 64, 16, None),            # 720 items: blocks walk several items each
+    ([1500] + [40] * 50, 10, 10, 64, 16, None),            # one long request among short ones
+]
+
+
+@pytest.mark.parametrize("case_id", range(len(STREAM_CASES)))
+def test_attention_decode_streaming_kernel(case_id):
+    """The streaming decode kernel (resident blocks walking (token, head) items through a ring of
+    TMA stages) against the float64 reference; rows of the cache that hold no key are NaN, so a
+    masked row that leaked into a sum would show.  Also with the token's own key and value taken
+    from the step's rows and written into the cache by the kernel."""
+    ops = _ops()
+    lens, H, Hkv, D, ps, window = STREAM_CASES[case_id]
+    c = _paged_case(lens, [1] * len(lens), H, Hkv, D, ps, torch.bfloat16, seed=500 + case_id)
+    scale = 1.0 / math.sqrt(D)
+    T = len(lens)
+    ref = _attention_reference(c, H, Hkv, D, scale, window)
+    used = torch.zeros(c["cache"].shape[0], ps, dtype=torch.bool)
+    for r, n in enumerate(lens):
+        for p in range(n):
+            used[int(c["bt"][r, p // ps]), p % ps] = True
+    cache = c["cache"].clone()
+    cache[(~used).to(DEV)[:, None, None, :].expand(-1, 2, Hkv, -1)] = float("nan")
+    for max_keys in (max(lens), max(1024, max(lens))):
+        out = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(c["q"], cache, c["bt"], c["token_req"], c["positions"], out, H, scale, window,
+                             max_keys, variant="stream")
+        err = float((out.double().cpu() - ref).abs().max())
+        assert err < 2e-2, err
+        out2 = torch.empty_like(out)
+        ops.attention_decode(c["q"], cache, c["bt"], c["token_req"], c["positions"], out2, H, scale, window,
+                             max_keys, variant="stream")
+        assert torch.equal(out, out2)
+    # the token's own key and value from the step's rows; its cache row is not written yet
+    k_new = torch.stack([K[-1].reshape(-1) for K in c["Ks"]]).to(DEV)
+    v_new = torch.stack([V[-1].reshape(-1) for V in c["Vs"]]).to(DEV)
+    slots = torch.tensor([int(c["bt"][r, (n - 1) // ps]) * ps + (n - 1) % ps for r, n in enumerate(lens)],
+                         dtype=torch.int32, device=DEV)
+    holed = cache.clone()
+    for r, n in enumerate(lens):
+        holed[int(c["bt"][r, (n - 1) // ps]), :, :, (n - 1) % ps] = float("nan")
+    out3 = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(c["q"], holed, c["bt"], None if case_id % 2 else c["token_req"], c["positions"], out3, H,
+                         scale, window, max(lens), k_new=k_new, v_new=v_new, slots=slots, variant="stream")
+    assert torch.equal(out3, out)
+    assert torch.equal(torch.nan_to_num(holed, nan=-7.0), torch.nan_to_num(cache, nan=-7.0))
+    assert int(ops.tc_error_flag(out.device).item()) == 0
+
+
+def test_attention_decode_streaming_kernel_finds_a_far_key_and_serves_a_token_list():
+    ops = _ops()
+    H, Hkv, D, ps = 2, 2, 64, 16
+    for far in (0, 15, 16, 63, 64, 255, 256, 300, 698):
+        c = _paged_case([700], [1], H, Hkv, D, ps, torch.bfloat16, seed=far, far_key=far)
+        out = torch.empty(1, H * D, dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, 1.0, None, 700,
+                             variant="stream")
+        ref = _attention_reference(c, H, Hkv, D, 1.0, None)
+        assert float((out.double().cpu() - ref).abs().max()) < 2e-2, far
+    # single tokens picked out of a mixed step by a list
+    lens, q_lens, H, Hkv = [300, 200, 77, 513, 64], [44, 1, 1, 130, 1], 4, 2
+    c = _paged_case(lens, q_lens, H, Hkv, D, ps, torch.bfloat16, seed=901)
+    q_start = [0] + list(np.cumsum(q_lens))
+    singles = [int(q_start[r]) for r, n in enumerate(q_lens) if n == 1]
+    token_list = torch.tensor(singles + [0, 0], dtype=torch.int32, device=DEV)
+    T = c["q"].shape[0]
+    out = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], out, H, 0.125, None,
+                         max(lens), token_list=token_list, n_tokens=len(singles), variant="stream")
+    ref = _attention_reference(c, H, Hkv, D, 0.125, None)
+    got = out.double().cpu()
+    for t in range(T):
+        if t in singles:
+            assert float((got[t] - ref[t]).abs().max()) < 2e-2
+        else:
+            assert bool(torch.isnan(out[t]).all())
+
+
 def test_both_decode_attention_kernels_at_head_size_64():
     """Head sizes 64 and 128 go to the TMA-staged kernel by default; the register-staged one
     must give the same there (it serves the other head sizes and more than 8 key ranges)."""

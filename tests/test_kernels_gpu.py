@@ -500,6 +500,8 @@ STREAM_CASES = [
     ([130, 9], 5, 5, 64, 4, 100),
     (list(range(1, 61)), 12, 12, 64, 16, None),            # 720 items: blocks walk several items each
     ([1500] + [40] * 50, 10, 10, 64, 16, None),            # one long request among short ones
+    ([1100] * 40, 12, 12, 64, 16, None),                   # several long items per block
+    ([77, 200, 3], 3, 1, 128, 64, None),                   # head size 128, a page per stage
 ]
 
 

@@ -192,6 +192,28 @@ class CacheManager:
         self._len[req] = new_len
         return True
 
+    def grow_by_one(self, reqs, needs_page):
+        """One more position for each of `reqs`; needs_page holds the indices of those whose
+        new position begins a page (the caller has checked can_extend_all for them).  Only for
+        groups without a window: nothing is given back here."""
+        for i, req in enumerate(reqs):
+            if i in needs_page:
+                ok = self.extend(req, self._len[req] + 1)
+                if not ok:
+                    raise CacheError("grow_by_one ran out of pages after can_extend_all")
+            else:
+                self._len[req] += 1
+
+    def shrink_by_one(self, reqs, took_page):
+        """Undo grow_by_one: one position less for each of `reqs`; those whose indices are in
+        took_page give back the page that the position began."""
+        for i, req in enumerate(reqs):
+            self._len[req] -= 1
+            if i in took_page:
+                for g in self.groups:
+                    if g.need.kind == "paged_kv":
+                        g.pool.unref(g.tables[req].pop())
+
     def free_request(self, req):
         """Return every page and the state slot of a request."""
         if req not in self._slot:

@@ -43,6 +43,9 @@ class Engine:
                                   make_tensor=runtime.make_tensor, cache_dtype=runtime.cache_dtype_name)
         self.b_cap = (plan.max_positions + self.page_size - 1) // self.page_size
         self._paged = self.cache.paged_groups()
+        self._any_window = any(self.cache.groups[gi].need.window is not None for gi in self._paged)
+        self._rep = None                  # what a repeated step of single tokens updates in place
+        self._prepared = None             # prepare_repeat's mark: indices of requests that took a page
         self.bufs = StepBuffers(runtime.device, self.max_step_tokens, self.max_requests, self.b_cap,
                                 len(self.cache.groups))
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=runtime.device)
@@ -86,12 +89,16 @@ class Engine:
 
     # -- requests ---------------------------------------------------------------
     def add_request(self, req):
+        self.cancel_prepared()
+        self._rep = None
         slot = self.cache.add_request(req)
         if slot is None:
             raise StepError(f"all {self.max_requests} request slots are taken")
         return slot
 
     def end_request(self, req):
+        self.cancel_prepared()
+        self._rep = None
         self.cache.free_request(req)
 
     def has_request(self, req):
@@ -147,6 +154,11 @@ class Engine:
         V = self.plan.vocab_size
         if not entries:
             return torch.empty((0, V), dtype=torch.float32, device=self.rt.device)
+        if self._rep is not None:
+            ctx = self._step_repeat(entries, self._rep)
+            if ctx is not None:
+                return self._run(ctx)
+            self.cancel_prepared()           # prepared for another step than this one
         T = self._validate(entries)
         wants = [(e.req, self.cache.length(e.req) + len(e.tokens)) for e in entries]
         if not self.cache.can_extend_all(wants):
@@ -213,6 +225,118 @@ class Engine:
 
         ctx.T, ctx.R, ctx.n_want, ctx.max_keys = T, R, nw, max_keys
         ctx.n_decode = n_decode
+        # a step of single tokens is likely to come again with the same requests: keep what
+        # the next one can update in place
+        self._rep = None
+        if n_decode == R and not self._any_window:
+            self._rep = dict(reqs=[e.req for e in entries], want=[list(e.want) for e in entries],
+                             lens=np.asarray(ctx.h_kv_len, dtype=np.int64), slots=list(ctx.h_state_slots), nw=nw)
+        return self._run(ctx)
+
+    def _step_repeat(self, entries, rep):
+        """The step after a step of single tokens, for the same requests in the same order with
+        the same wanted places: the packed arrays of the last step are updated in place
+        (positions and lengths grow by one; a cache slot is the next one unless a page begins)
+        instead of being built again.  Returns None, having changed nothing, when the step is
+        of another kind or not valid (the general path then words the error)."""
+        R = len(entries)
+        reqs = rep["reqs"]
+        if R != len(reqs):
+            return None
+        want = rep["want"]
+        for r, e in enumerate(entries):
+            if e.req != reqs[r] or len(e.tokens) != 1 or list(e.want) != want[r]:
+                return None
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        if toks.min() < 0 or toks.max() >= self.plan.vocab_size:
+            return None
+        if self._prepared is None and not self.prepare_repeat(reqs):
+            return None
+        return self._finish_prepared(toks)
+
+    def prepare_repeat(self, reqs):
+        """Everything of the next step that does not depend on its token ids, done ahead (while
+        the device still runs the last step): valid when the next step brings one token for each
+        of `reqs`, the requests of the last step in the same order.  Grows the requests in the
+        cache and updates the packed arrays on the host.  Returns False, having changed nothing,
+        if the last step was of another kind, a request would pass the model's positions, or
+        pages are short.  Followed by run_prepared(tokens) or cancel_prepared()."""
+        rep = self._rep
+        if rep is None or self._prepared is not None or list(reqs) != rep["reqs"]:
+            return False
+        R = len(rep["reqs"])
+        o = rep["lens"]
+        if int(o.max()) + 1 > self.plan.max_positions:
+            return False
+        ps = self.page_size
+        cross = np.nonzero(o % ps == 0)[0]
+        if len(cross) and not self.cache.can_extend_all([(rep["reqs"][r], int(o[r]) + 1) for r in cross]):
+            return False
+        crossed = set(int(r) for r in cross)
+        self.cache.grow_by_one(rep["reqs"], crossed)
+        b = self.bufs
+        b.wait_host_free()
+        b.npview("positions")[:R] = o
+        b.npview("kv_len")[:R] = o + 1
+        for gi in self._paged:
+            sl = b.npview(f"slots{gi}")
+            sl[:R] += 1
+            if len(cross):
+                bt = b.npview(f"bt{gi}").reshape(self.max_requests, self.b_cap)
+                for r in cross:
+                    blk = int(o[r]) // ps
+                    page = self.cache.block_table(gi, rep["reqs"][r])[blk]
+                    bt[r, blk] = page
+                    sl[r] = page * ps
+        self._prepared = crossed
+        return True
+
+    def has_prepared(self):
+        return self._prepared is not None
+
+    def run_prepared(self, tokens):
+        """Run the step that prepare_repeat set up, with these token ids (one per request)."""
+        if self._prepared is None:
+            raise StepError("no prepared step (prepare_repeat first)")
+        toks = np.asarray(tokens, dtype=np.int64)
+        if toks.shape != (len(self._rep["reqs"]),) or toks.min() < 0 or toks.max() >= self.plan.vocab_size:
+            self.cancel_prepared()
+            raise StepError("run_prepared: one token id inside the vocabulary for each request")
+        return self._run(self._finish_prepared(toks))
+
+    def cancel_prepared(self):
+        """Undo prepare_repeat: the requests shrink back by one position, pages taken for them
+        return to the pool.  The next step is built in full."""
+        if self._prepared is None:
+            return
+        self.cache.shrink_by_one(self._rep["reqs"], self._prepared)
+        self._prepared = None
+        self._rep = None
+
+    def _finish_prepared(self, toks):
+        rep = self._rep
+        R = len(rep["reqs"])
+        o = rep["lens"]
+        b = self.bufs
+        b.npview("tokens")[:R] = toks
+        b.upload()
+        self._prepared = None
+        rep["lens"] = o + 1
+        ctx = StepContext(self.rt, self.ws)
+        ctx.T, ctx.R, ctx.n_want, ctx.n_decode = R, R, rep["nw"], R
+        ctx.max_keys = int(o.max()) + 1
+        ctx.max_q_len = 1
+        ctx.h_q_len = [1] * R
+        ctx.h_kv_len = (o + 1).tolist()
+        ctx.h_fresh = [False] * R
+        ctx.h_reqs = list(rep["reqs"])
+        ctx.h_state_slots = rep["slots"]
+        return ctx
+
+    def _run(self, ctx):
+        """Run the model on a step whose packed arrays are on their way to the device."""
+        b = self.bufs
+        T, R, nw, n_decode = ctx.T, ctx.R, ctx.n_want, ctx.n_decode
         if self.use_graphs and self.model.graph_safe:
             # a step whose launch shapes have a captured graph needs nothing but the upload above
             hit = self._graph_lookup(ctx)

@@ -91,6 +91,10 @@ class Scheduler:
         self.stats = SchedStats(prefill_chunk=self.prefill_chunk, pool_pages=engine.cache.n_pages)
         # any object with Sampler.sample's signature; the default samples on the device
         self.sampler = sampler if sampler is not None else Sampler(engine.rt.device, engine.max_requests)
+        # prepare the next step of single tokens on the host while the device runs this one
+        # (only engines that offer it: Engine.prepare_repeat)
+        self.prepare_ahead = hasattr(engine, "prepare_repeat")
+        self._ahead = None
 
     # -- entry points (names of the reference's C interface) --------------------
     def submit_ids(self, ids, max_new=16, sp=None):
@@ -216,22 +220,47 @@ class Scheduler:
 
     def step(self):
         """Run one step; returns how many requests finished in it."""
-        chosen = self.plan_step()
-        if not chosen:
-            return 0
-        entries, sampled = [], []
-        for r, n in chosen:
-            toks = r.tokens[r.n_computed:r.n_computed + n]
-            last = (r.n_computed + n == len(r.prompt) + len(r.gen))
-            entries.append(StepEntry(r.id, toks, [n - 1] if last else []))
-            if last:
-                sampled.append(r)
-            if r.n_computed + n <= len(r.prompt):
-                self.stats.prefill_tokens += n
-        logits = self.engine.step(entries)
+        chosen = None
+        if self._ahead is not None:
+            # the last call prepared this step while the device was busy: it stands if nothing
+            # has changed since (no request finished, aborted, or arrived)
+            ahead, self._ahead = self._ahead, None
+            if self.engine.has_prepared() and not self.waiting and ahead == [r.id for r in self.running]:
+                chosen = [(r, 1) for r in self.running]
+                sampled = list(self.running)
+                logits = self.engine.run_prepared([r.gen[-1] for r in self.running])
+            else:
+                self.engine.cancel_prepared()
+        if chosen is None:
+            chosen = self.plan_step()
+            if not chosen:
+                return 0
+            entries, sampled = [], []
+            for r, n in chosen:
+                np_ = len(r.prompt)
+                if r.n_computed >= np_:                   # past the prompt: no need to join the lists
+                    toks = r.gen[r.n_computed - np_:r.n_computed - np_ + n]
+                else:
+                    toks = r.tokens[r.n_computed:r.n_computed + n]
+                last = (r.n_computed + n == np_ + len(r.gen))
+                entries.append(StepEntry(r.id, toks, [n - 1] if last else []))
+                if last:
+                    sampled.append(r)
+                if r.n_computed + n <= np_:
+                    self.stats.prefill_tokens += n
+            logits = self.engine.step(entries)
         for r, n in chosen:
             r.n_computed += n
         self.stats.n_steps += 1
+        # While the device runs this step: if every running request is sampled in it and none
+        # waits, the next step most likely brings one token for each of them, and all of it but
+        # the token ids can be prepared now.  (A request that ends in this step ends the
+        # preparation with it: Engine.end_request cancels.)
+        if self.prepare_ahead and not self.waiting and len(sampled) == len(self.running) \
+                and all(len(r.gen) + 1 < r.max_new for r in sampled):
+            ids = [r.id for r in self.running]
+            if self.engine.prepare_repeat(ids):
+                self._ahead = ids
         finished = 0
         if sampled:
             us = []

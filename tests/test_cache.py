@@ -58,6 +58,32 @@ def test_requests_grow_page_by_page_and_give_all_back():
     m.check()
 
 
+def test_grow_by_one_and_its_undo():
+    """The engine's ahead-of-time growth of a step of single tokens: one position more for every
+    request, a page for those that begin one, and all of it taken back."""
+    m = _mgr(n_pages=8)
+    for r, n in (("a", 4), ("b", 6), ("c", 8)):
+        m.add_request(r)
+        assert m.extend(r, n)
+    free, tables = m.n_free_pages(), {r: list(m.block_table(0, r)) for r in "abc"}
+    reqs = ["a", "b", "c"]
+    took = {0, 2}                                    # positions 4 and 8 begin pages
+    assert m.can_extend_all([("a", 5), ("c", 9)])
+    m.grow_by_one(reqs, took)
+    assert [m.length(r) for r in reqs] == [5, 7, 9]
+    assert m.n_free_pages() == free - 2 and len(m.block_table(0, "a")) == 2 and len(m.block_table(1, "c")) == 3
+    m.check()
+    m.shrink_by_one(reqs, took)
+    assert [m.length(r) for r in reqs] == [4, 6, 8]
+    assert m.n_free_pages() == free and {r: list(m.block_table(0, r)) for r in "abc"} == tables
+    m.check()
+    m.grow_by_one(reqs, took)                        # and kept this time
+    for r in reqs:
+        m.free_request(r)
+    assert m.n_free_pages() == 8
+    m.check()
+
+
 def test_slots_run_out():
     m = _mgr(max_requests=2)
     assert m.add_request(1) is not None and m.add_request(2) is not None

@@ -133,6 +133,48 @@ def test_page_pressure_preempts_and_output_stays(model_dirs, dtype):
             check_greedy(d, p, g, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_prepared_ahead_change_nothing(model_dirs, dtype):
+    """The scheduler prepares the next step of single tokens while the device runs the current
+    one, and drops the preparation when a request ends, is aborted or arrives.  With requests
+    that end at different times (lengths, a stop id), an arrival and an abort in between, the
+    tokens are those of a scheduler that prepares nothing, and no page is lost."""
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    name = "B"
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    prompts = [traces.random_tokens(50 + i, n, V) for i, n in enumerate([7, 30, 15, 44, 3])]
+    max_new = [40, 9, 25, 33, 40]
+
+    def run(ahead, stop_ids):
+        s = sched_new(d, dtype=dtype, page_size=PAGE_SIZE[name], max_tokens=1024, max_requests=8,
+                      max_step_tokens=64, prefill_chunk=24)
+        s.prepare_ahead = ahead
+        ids = [s.submit_ids(p, m, SamplingParams(temperature=0.0, stop_ids=list(stop_ids) if i == 0 else []))
+               for i, (p, m) in enumerate(zip(prompts[:4], max_new[:4]))]
+        steps = 0
+        while s.nactive() > 0:
+            s.step()
+            steps += 1
+            if steps == 12:
+                ids.append(s.submit_ids(prompts[4], max_new[4], SamplingParams(temperature=0.0)))
+            if steps == 20:
+                s.abort(ids[3])
+        out = [list(s.requests[i].gen) for i in ids]
+        st = s.get_stats()
+        assert st.pool_free == st.pool_pages
+        s.engine.cache.check()
+        return out, s.engine.graph_replays
+
+    plain, _ = run(False, [])
+    stop = [plain[0][17]]                              # request 0 ends on a token of its own
+    want, _ = run(False, stop)
+    got, _ = run(True, stop)
+    assert len(want[0]) <= 17 and len(want[1]) == 9
+    assert got == want
+
+
 def test_command_line_with_random_weights(tmp_path):
     import json
     cfg = tmp_path / "config.json"

@@ -71,7 +71,7 @@ def test_grow_by_one_and_its_undo():
     assert m.can_extend_all([("a", 5), ("c", 9)])
     m.grow_by_one(reqs, took)
     assert [m.length(r) for r in reqs] == [5, 7, 9]
-    assert m.n_free_pages() == free - 2 and len(m.block_table(0, "a")) == 2 and len(m.block_table(1, "c")) == 3
+    assert m.n_free_pages() == free - 2 and len(m.block_table(0, "a")) == 2 and len(m.block_table(0, "c")) == 3
     m.check()
     m.shrink_by_one(reqs, took)
     assert [m.length(r) for r in reqs] == [4, 6, 8]

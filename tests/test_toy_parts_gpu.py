@@ -1,7 +1,9 @@
 """The framework takes parts and architectures it has never seen, registered from here
 without a change to its files: a mixer with per-request state of its own (in slots, not
 pages), a running order that names a layer twice, a call that reads the cache another call
-wrote, and a layer with a window beside layers without.  Each toy model is compared with a
+wrote, a layer with a window beside layers without, a feed-forward that routes each token to
+experts (in some layers only), and a position encoding that turns queries and keys instead of
+adding a table.  Each toy model is compared with a
 plain restatement written here from the plain implementation's parts.  These are toys, not
 models of anyone's."""
 import dataclasses
@@ -19,6 +21,8 @@ from conftest import TINY
 pytestmark = pytest.mark.gpu
 TOL = {"float32": 3e-5, "bfloat16": 1.5e-2}
 DECAY = 0.75
+N_EXPERTS = 3
+ROTARY_BASE = 100.0
 
 
 def _register():
@@ -57,6 +61,75 @@ def _register():
                 t0 += n
             ctx.rt.gemm(y.to(h.dtype), self.w, None, residual=residual)
 
+    @register_part("feed_forward", "toy_routed")
+    class RoutedFeedForward(Part):
+        """Router logits h·Wrᵀ and their softmax in 32-bit; the top_k experts of a token are kept and
+        their weights made to sum to one; expert e is one matrix; residual += sum_e p_e (h·Weᵀ).
+        (Products by torch here: a toy in a test, not a kernel of the engine.)"""
+        graph_safe = False
+
+        @classmethod
+        def declare_weights(cls, params):
+            return {"router": WeightDecl((params["n_experts"], params["size"]), "matrix"),
+                    "experts": WeightDecl((params["n_experts"] * params["size"], params["size"]), "residual_matrix")}
+
+        def load(self, tensors, store):
+            self.router = store.matrix(tensors["router"])
+            self.experts = store.matrix(tensors["experts"])
+
+        def forward(self, ctx, h, residual):
+            n_e, size, k = self.params["n_experts"], self.params["size"], self.params["top_k"]
+            hf = h.float()
+            p = torch.softmax(hf @ self.router.float().t(), dim=-1)
+            if k < n_e:
+                kept = torch.zeros_like(p).scatter_(1, p.topk(k, dim=-1).indices, 1.0)
+                p = p * kept
+                p = p / p.sum(-1, keepdim=True)
+            we = self.experts.float().view(n_e, size, size)
+            for e in range(n_e):
+                residual += p[:, e:e + 1] * (hf @ we[e].t())
+            return residual
+
+    @register_part("position", "toy_rotary")
+    class ToyRotary(Part):
+        """Nothing at the embedding; inside a mixer, the two halves of every head of q and k are
+        turned by the angle position * base^(-i/half), computed in 32-bit."""
+        graph_safe = False
+
+        def additive_table(self):
+            return None
+
+        def apply_embedding(self, ctx, x):
+            pass
+
+        def rotate(self, ctx, q, k):
+            D = self.params["head_dim"]
+            half = D // 2
+            inv = float(self.params["base"]) ** (-torch.arange(half, device=q.device, dtype=torch.float32) / half)
+            ang = ctx.positions.float()[:, None] * inv[None, :]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            for x in (q, k):
+                xv = x.unflatten(1, (-1, D))
+                a, b = xv[..., :half].float(), xv[..., half:].float()
+                na, nb = a * cos - b * sin, b * cos + a * sin       # both before either is written
+                xv[..., :half] = na.to(x.dtype)
+                xv[..., half:] = nb.to(x.dtype)
+
+    def plan_routed(top_k):
+        def make(cfg):
+            plan = build_plan(cfg)
+            for l, layer in enumerate(plan.layers):
+                if l % 2 == 1:
+                    layer.ffn = PartSpec("toy_routed", {"size": cfg.n_embd, "n_experts": N_EXPERTS, "top_k": top_k},
+                                         {"router": f"h.{l}.toy.router.weight", "experts": f"h.{l}.toy.experts.weight"})
+            return plan
+        return make
+
+    def plan_rotary(cfg):
+        plan = build_plan(cfg)
+        plan.position = PartSpec("toy_rotary", {"head_dim": cfg.n_embd // cfg.n_head, "base": ROTARY_BASE}, {})
+        return plan
+
     def plan_state(cfg):
         plan = build_plan(cfg)
         for l, layer in enumerate(plan.layers):
@@ -78,6 +151,9 @@ def _register():
     register_architecture("ToyStateForTest", GPT2Config, plan_state)
     register_architecture("ToyOrderForTest", GPT2Config, plan_order)
     register_architecture("ToyWindowForTest", GPT2Config, plan_window)
+    register_architecture("ToyRoutedForTest", GPT2Config, plan_routed(1))
+    register_architecture("ToyMixtureForTest", GPT2Config, plan_routed(N_EXPERTS))
+    register_architecture("ToyRotaryForTest", GPT2Config, plan_rotary)
 
 
 @pytest.fixture(scope="module")
@@ -166,7 +242,59 @@ def plain_window(cfg, w, toks):
     return _finish(x, w, st)
 
 
-PLAIN = {"ToyStateForTest": plain_state, "ToyOrderForTest": plain_order, "ToyWindowForTest": plain_window}
+def plain_routed(top_k):
+    def f(cfg, w, toks):
+        st = plain_gpt2.settings(cfg)
+        E = st["E"]
+        x = plain_gpt2.embedding(toks, w["wte.weight"], w["wpe.weight"])
+        for l in range(st["L"]):
+            x = plain_gpt2.attention_block(x, w, l, st)
+            if l % 2 == 1:
+                p_ = f"h.{l}."
+                h = plain_gpt2.layer_norm(x, w[p_ + "ln_2.weight"], w[p_ + "ln_2.bias"], st["eps"])
+                lg = h @ w[p_ + "toy.router.weight"].T
+                pr = np.exp(lg - lg.max(-1, keepdims=True))
+                pr = pr / pr.sum(-1, keepdims=True)
+                if top_k < N_EXPERTS:
+                    drop = np.argsort(-pr, axis=-1)[:, top_k:]
+                    np.put_along_axis(pr, drop, 0.0, axis=-1)
+                    pr = pr / pr.sum(-1, keepdims=True)
+                we = w[p_ + "toy.experts.weight"].reshape(N_EXPERTS, E, E)
+                for e in range(N_EXPERTS):
+                    x = x + pr[:, e:e + 1] * (h @ we[e].T)
+            else:
+                x = plain_gpt2.mlp_block(x, w, l, st)
+        return _finish(x, w, st)
+    return f
+
+
+def plain_rotary(cfg, w, toks):
+    st = plain_gpt2.settings(cfg)
+    H, E = st["H"], st["E"]
+    D = E // H
+    half = D // 2
+    x = w["wte.weight"][np.asarray(toks)].astype(np.float64)        # no position table
+    pos = np.arange(len(toks), dtype=np.float64)
+    inv = ROTARY_BASE ** (-np.arange(half, dtype=np.float64) / half)
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+
+    def turn(m):
+        v = m.reshape(len(toks), H, D)
+        a, b = v[..., :half], v[..., half:]
+        return np.concatenate([a * cos - b * sin, b * cos + a * sin], axis=-1).reshape(len(toks), E)
+
+    for l in range(st["L"]):
+        h, q, k, v = _qkv(x, w, l, st)
+        a = plain_gpt2.causal_attention(turn(q), turn(k), v, H, plain_gpt2.attention_scale(st, l))
+        x = _attn_out(x, a, w, l)
+        x = plain_gpt2.mlp_block(x, w, l, st)
+    return _finish(x, w, st)
+
+
+PLAIN = {"ToyStateForTest": plain_state, "ToyOrderForTest": plain_order, "ToyWindowForTest": plain_window,
+         "ToyRoutedForTest": plain_routed(1), "ToyMixtureForTest": plain_routed(N_EXPERTS),
+         "ToyRotaryForTest": plain_rotary}
 
 
 def run(model_dir, dtype, steps, tmp_path, n_pages, page_size=8):
@@ -181,9 +309,14 @@ def run(model_dir, dtype, steps, tmp_path, n_pages, page_size=8):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("arch", ["ToyStateForTest", "ToyOrderForTest", "ToyWindowForTest"])
+@pytest.mark.parametrize("arch", ["ToyStateForTest", "ToyOrderForTest", "ToyWindowForTest", "ToyRoutedForTest",
+                                  "ToyMixtureForTest", "ToyRotaryForTest"])
 @pytest.mark.parametrize("tiny", ["A", "B"])
 def test_toy_models_in_every_cut(toy_dirs, tmp_path, arch, tiny, dtype):
+    if arch == "ToyRoutedForTest" and dtype == "bfloat16":
+        # two router logits that nearly tie may change places under bfloat16 rounding, and the
+        # output then differs by a whole expert; the mixture over all experts has no such step
+        pytest.skip("top-1 routing is compared in 32-bit; the mixture covers bfloat16")
     d = toy_dirs(arch, tiny, dtype)
     cfg, w = plain_gpt2.read_model_dir(d)
     V = TINY[tiny]["vocab_size"]

@@ -56,6 +56,7 @@ struct GemmArgs {
   int tma_out;             // many-token tiles leave through shared memory and a TMA store / add
   int act;
   int* err;                // set to 1 if a bounded wait ran out
+  int tiles_p, n_tiles;    // many-token kernel: row tiles, and all tiles (a block walks several)
 };
 
 // Optional timeline for tuning (compile with -DSGLC_TIMELINE): block (0,0,0) stores the
@@ -85,6 +86,22 @@ __device__ __forceinline__ void tl_mark(const GemmArgs& a, int slot) {
 #define TL(slot)
 #endif
 
+// The tanh form of GELU as u * sigmoid(2k(u + 0.044715 u^3)), which is the same function
+// (0.5 (1 + tanh x) = sigmoid 2x) without the cancellation of 1 + tanh for negative inputs, by
+// one exponential and one division of the fast kind (2 ulp each): a few instructions where
+// tanhf takes twenty, and an epilogue of 128 x 128 values a tile is made of them.
+__device__ __forceinline__ float gelu_tanh_sigmoid(float u) {
+  const float z = 1.5957691216057308f * (u + 0.044715f * u * u * u);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * 1.4426950408889634f));
+  return __fdividef(u, 1.0f + e);
+}
+__device__ __forceinline__ float act_tc(float u, int act) {
+  if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_sigmoid(u);
+  if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
+  return u;
+}
+
 struct SharedCtl {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
@@ -105,7 +122,7 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
     for (int j = 0; j < nq; j++) {
       int m = q0 + j;
       if (m >= a.M) break;
-      float x = apply_act(v[j] + b, a.act);
+      float x = act_tc(v[j] + b, a.act);
       size_t o = (size_t)m * a.ldo + n;
       if (a.residual) a.residual[o] += x;
       else if (a.out_f32) ((float*)a.out)[o] = x;
@@ -135,7 +152,7 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
     } else if (a.out_f32) {
       float* dst = (float*)a.out + row + q0;
       for (int j = 0; j < nq && q0 + j < a.N; j++)
-        dst[j] = apply_act(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act);
+        dst[j] = act_tc(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act);
     } else {
       __nv_bfloat16* dst = (__nv_bfloat16*)a.out + row + q0;
       if (vec_ok && ((uintptr_t)dst & 15) == 0 && nq % 8 == 0) {
@@ -144,16 +161,16 @@ __device__ __forceinline__ void epilogue_store(const GemmArgs& a, int p_glob, in
           __align__(16) __nv_bfloat162 h[4];
 #pragma unroll
           for (int t = 0; t < 4; t++) {
-            float x0 = apply_act(v[j + 2 * t] + (a.bias ? a.bias[q0 + j + 2 * t] : 0.0f), a.act);
+            float x0 = act_tc(v[j + 2 * t] + (a.bias ? a.bias[q0 + j + 2 * t] : 0.0f), a.act);
             float x1 =
-                apply_act(v[j + 2 * t + 1] + (a.bias ? a.bias[q0 + j + 2 * t + 1] : 0.0f), a.act);
+                act_tc(v[j + 2 * t + 1] + (a.bias ? a.bias[q0 + j + 2 * t + 1] : 0.0f), a.act);
             h[t] = __floats2bfloat162_rn(x0, x1);
           }
           *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<uint4*>(h);
         }
       } else {
         for (int j = 0; j < nq && q0 + j < a.N; j++)
-          dst[j] = __float2bfloat16_rn(apply_act(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act));
+          dst[j] = __float2bfloat16_rn(act_tc(v[j] + (a.bias ? a.bias[q0 + j] : 0.0f), a.act));
       }
     }
   }
@@ -328,7 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           tmem_ld_wait();
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; j++) v[j] = apply_act(__uint_as_float(r[j]) + s_bias[c + j], a.act);
+          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + s_bias[c + j], a.act);
           if (to_f32) {
             // box = 32 floats (128 bytes) per row: this chunk is row `row` of box c/32
             uint8_t* box = smem + (size_t)(c / 32) * (BM * 128);
@@ -450,7 +467,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 #pragma unroll
           for (int u = 0; u < 4; u++) {
             if (!valid[u]) continue;
-            float x = apply_act(v[u] + bs[u], a.act);
+            float x = act_tc(v[u] + bs[u], a.act);
             if (a.residual) a.residual[off[u]] = rs[u] + x;
             else if (a.out_f32) ((float*)a.out)[off[u]] = x;
             else ((__nv_bfloat16*)a.out)[off[u]] = __float2bfloat16_rn(x);
@@ -473,6 +490,238 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- many tokens (prefill): one resident block per SM walks the tiles ----------------------
+// At this model's widths a product is one to three 128 x 128 tiles per SM, and a tile's start
+// (first operands 1 us after the block begins) and end (2 us of reading the accumulator, bias,
+// activation and the way out through shared memory) weigh as much as its main loop.  Here a
+// block stays and takes tile after tile: the operand ring never drains between tiles, and with
+// two accumulators in tensor memory the four epilogue warps finish tile i while the MMA warp
+// already works on tile i+1.  The tile leaves in boxes of 128 bytes a row through a ring of two
+// 16 KB buffers (TMA store for bfloat16, TMA add into the float residual stream).
+struct StreamCtl {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                      const __grid_constant__ CUtensorMap map_out, const GemmArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int W_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+  constexpr int BOX_BYTES = BM * 128;            // one outgoing box: 128 rows of 128 bytes
+  __shared__ StreamCtl ctl;
+  __shared__ float s_bias[2][BN];
+  __shared__ int s_go[2];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = a.stages;
+  uint8_t* epi = smem + (size_t)stages * STAGE_BYTES;       // two boxes
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) TL(0);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; s++) {
+      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&ctl.acc_full[b], 1);
+      mbar_init(&ctl.acc_empty[b], 4);           // one arrival per epilogue warp
+    }
+    ctl.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_w);
+    if (a.tma_out) tma_prefetch_desc(&map_out);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl.tmem_base, 2 * BN);          // two accumulators side by side
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+  const int n_kb = a.kb_total;
+
+  if (warp == 0) {
+    // ---- TMA producer: one ring of stages across all of the block's tiles ----
+    if (elect_one()) {
+      TL(1);
+      pdl_wait();
+      TL(2);
+      int kc = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x) {
+        const int pt = t % a.tiles_p, qt = t / a.tiles_p;
+        for (int i = 0; i < n_kb; i++, kc++) {
+          const int s = kc % stages;
+          if (kc >= stages && !mbar_wait(&ctl.empty[s], ((kc / stages) - 1) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sp = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&ctl.full[s], STAGE_BYTES);
+          tma_load_2d(sp, &map_a, &ctl.full[s], i * BK, pt * BM);
+          tma_load_2d(sp + A_BYTES, &map_w, &ctl.full[s], i * BK, qt * BN);
+        }
+      }
+      if (*abort_flag) {
+        // wait, with a limit, for the copies still in flight before the block may exit
+        for (int i = max(0, kc - stages); i < kc; i++)
+          mbar_wait(&ctl.full[i % stages], (i / stages) & 1, abort_flag);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+      int kc = 0, n = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x, n++) {
+        const int buf = n & 1;
+        if (n >= 2) {
+          // the epilogue has read this accumulator's last tile out of tensor memory
+          ok = mbar_wait(&ctl.acc_empty[buf], ((n >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+        for (int i = 0; i < n_kb; i++, kc++) {
+          const int s = kc % stages;
+          ok = mbar_wait(&ctl.full[s], (kc / stages) & 1, abort_flag);
+          if (!ok) break;
+          if (kc == 0) TL(3);
+          tc_fence_after_sync();
+          const uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc_k_sw128(sp);
+          const uint64_t dw = smem_desc_k_sw128(sp + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            mma_bf16(acc, da + 2 * k, dw + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          mma_commit(&ctl.empty[s]);
+        }
+        if (ok) mma_commit(&ctl.acc_full[buf]);
+        if (n < 3) TL(4 + n);
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+    const int e = threadIdx.x - 64;
+    const int lane_base = (warp & 3) * 32;
+    const int row = lane_base + lane;
+    const bool to_f32 = a.residual != nullptr;
+    const int box_cols = to_f32 ? 32 : 64;
+    int n = 0, boxes = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, n++) {
+      const int pt = t % a.tiles_p, qt = t / a.tiles_p;
+      const int buf = n & 1;
+      float* bias_s = s_bias[buf];
+      if (e < BN) bias_s[e] = (a.bias && qt * BN + e < a.N) ? a.bias[qt * BN + e] : 0.0f;
+      if (ok) ok = mbar_wait(&ctl.acc_full[buf], (n >> 1) & 1, abort_flag);
+      tc_fence_after_sync();
+      // one thread decides for all whether the tile is finished or given up (a wait ran out
+      // somewhere in the block): the barriers below need every thread on the same side
+      if (threadIdx.x == 64 && n < 2) TL(7 + 2 * n);
+      if (threadIdx.x == 64) s_go[buf] = (ok && *abort_flag == 0) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
+      ok = s_go[buf] != 0;
+      const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
+      if (ok && a.tma_out) {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) {
+            // the accumulator has been read: the MMA warp may fill it again
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
+          }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
+          const bool first_of_box = (c % box_cols) == 0;
+          uint8_t* box = epi + (size_t)(boxes & 1) * BOX_BYTES;
+          if (first_of_box) {
+            // the store that used this buffer two boxes ago has read it
+            if (threadIdx.x == 64) tma_store_wait_read_but_one();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+          if (to_f32) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+              *reinterpret_cast<float4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int ch = (c % 64) / 8 + q4;
+              __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(v[8 * q4 + 2 * x], v[8 * q4 + 2 * x + 1]);
+              *reinterpret_cast<uint4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) = *reinterpret_cast<uint4*>(hh);
+            }
+          }
+          const bool last_of_box = ((c + 32) % box_cols) == 0;
+          if (last_of_box) {
+            fence_async_proxy();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+              const int x0 = qt * BN + (c + 32 - box_cols);
+              if (to_f32) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
+              else tma_store_2d(&map_out, box, x0, pt * BM);
+              tma_store_commit();
+            }
+            boxes++;
+          }
+        }
+      } else if (ok) {
+        // output rows that a tensor map cannot address: plain stores
+        const int p_glob = pt * BM + row;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
+          }
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+          epilogue_store<BN>(a, p_glob, qt * BN + c, v, 32);
+        }
+      }
+      if (threadIdx.x == 64 && n < 3) TL(n == 0 ? 8 : (n == 1 ? 10 : 11));
+    }
+    if (threadIdx.x == 64) TL(12);
+    if (threadIdx.x == 64) tma_store_wait_read();      // shared memory must outlive the last stores' reads
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -541,6 +790,37 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, 
   }
   return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
 }
+template <int BN>
+int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a,
+                  cudaStream_t stream) {
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+  }
+  const size_t stage_bytes = (size_t)BM * BK * 2 + (size_t)BN * BK * 2;
+  int stages = (int)(((size_t)226 * 1024 - 2 * BM * 128 - 2048) / stage_bytes);
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  // (the first call settles how many stages the device grants beside the kernel's static part)
+  static int granted = 0;
+  if (granted == 0) {
+    for (; stages >= 2; stages--) {
+      const size_t want = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
+      if (cudaFuncSetAttribute(gemm_tc_stream_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+          cudaSuccess)
+        break;
+      cudaGetLastError();
+    }
+    if (stages < 2) return SGLC_ERR_UNSUPPORTED;
+    granted = stages;
+  }
+  stages = granted;
+  a.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
+  int grid = a.n_tiles < n_sm ? a.n_tiles : n_sm;
+  return sglc_launch(gemm_tc_stream_kernel<BN>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a);
+}
 }  // namespace
 
 #if defined(SGLC_TIMELINE) && defined(SGLC_TL_ONLY_N)
@@ -552,6 +832,10 @@ SGLC_API int sglc_gemm_tc_timeline(unsigned long long* out) {
 // Tuning hook: the most K splits of the few-token orientation (0: the built-in choice).
 static int g_max_splits = 0;
 SGLC_API void sglc_gemm_tc_set_max_splits(int n) { g_max_splits = n; }
+// Tuning hook: more than 128 tokens go to the kernel whose blocks walk the tiles (1, default) or
+// to one block per tile (0).
+static int g_stream_kernel = 1;
+SGLC_API void sglc_gemm_tc_set_stream_kernel(int on) { g_stream_kernel = on; }
 
 // Orientation, tile width and K split for a problem size.
 static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split,
@@ -575,7 +859,10 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
   } else {
     *swap = 0;
     int tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
-    *bn = (tiles128 >= 148 || N <= 64) ? 128 : 64;
+    // a block of the many-token kernel walks its tiles one after the other: wide tiles (fewer
+    // bytes from L2 per flop) as soon as they occupy half of the SMs; one block per tile
+    // (the other kernel) wants a tile for every SM first
+    *bn = (tiles128 >= (g_stream_kernel ? 74 : 148) || N <= 64) ? 128 : 64;
     *tiles_p = (M + BM - 1) / BM;
     *tiles_q = (N + *bn - 1) / *bn;
     *splits = 1;
@@ -627,6 +914,11 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
   if (!swap && bn >= 64) {
     if (residual) a.tma_out = get_map(&mo, residual, M, N, ldo, BM | 0x10000u) ? 1 : 0;
     else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
+  }
+  if (!swap && g_stream_kernel) {
+    a.tiles_p = tp;
+    a.n_tiles = tp * tq;
+    return bn == 128 ? launch_stream<128>(mp, mq, mo, a, stream) : launch_stream<64>(mp, mq, mo, a, stream);
   }
   int stage_bytes = BM * BK * 2 + bn * BK * 2;
   int budget = swap ? 96 * 1024 : (bn == 128 ? 100 * 1024 : 100 * 1024);

@@ -41,12 +41,24 @@ __device__ unsigned long long g_tl[64];
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
     g_tl[slot] = t_;                                                                        \
   }
+__device__ unsigned long long g_tl_blocks[2 * 2048];     // per block: start and end
+#define TLB(slot)                                                                           \
+  if (threadIdx.x == 0) {                                                                   \
+    const unsigned b_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;     \
+    if (b_ < 2048) {                                                                        \
+      unsigned long long t_;                                                                \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                \
+      g_tl_blocks[2 * b_ + slot] = t_;                                                      \
+    }                                                                                       \
+  }
 #else
 #define TL(slot)
+#define TLB(slot)
 #endif
 
 struct Ctl {
   uint64_t q_full, s_full, p_ready, o_full;
+  uint64_t land_free, land_full;       // the hand-over between the two blocks of a split tile
   uint64_t kv_full[KV_STAGES], kv_empty[KV_STAGES];
   uint32_t tmem_base;
   int abort_flag;
@@ -67,6 +79,7 @@ struct Args {
   int window;
   int use_tma;            // keys, values and queries arrive by TMA (page_size divides 128)
   int skip_single;        // requests that bring one token are served by the decode kernel
+  int split_min;          // key tiles from which a query tile is shared by the cluster's two blocks
   int* err;
 };
 
@@ -109,27 +122,76 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   Ctl& ctl = *reinterpret_cast<Ctl*>(sV + KV_STAGES * TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // late query tiles see the most keys: they are started first
-  const int r = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
+  // The launch is a list of clusters of two blocks per (request, head), heaviest first (blocks
+  // are handed out x first, then y, so every request's heaviest work starts first).  A query
+  // tile with split_min or more key tiles takes a whole cluster: rank 0 walks the first half
+  // of the key tiles and rank 1 the rest, and rank 1 hands its running maximum, sum and output
+  // rows over through distributed shared memory.  The lighter query tiles go two to a cluster,
+  // the heaviest of them with the lightest (an idle partner would hold its place on the SM
+  // until the cluster ends).  Without the split the launch lasts as long as its longest tile
+  // (the last query tile of the longest request) while most SMs have long finished.
+  const int r = blockIdx.x / a.H, h = blockIdx.x % a.H, rank = blockIdx.z, cl = blockIdx.y;
   pdl_launch_dependents();
+  TLB(0);
+  TLB(1);
   pdl_wait();
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
-  if (qt * BQ >= q_len) return;                    // uniform for the block: nothing allocated yet
   if (a.skip_single && q_len == 1) return;
   if (smem_u32(smem) & 1023u) {                    // never seen; the tiles would be mis-swizzled
     if (threadIdx.x == 0 && a.err) atomicExch(a.err, 1);
     return;
   }
   const int kv_len = a.kv_len[r];
+  const int nq = (q_len + BQ - 1) / BQ;
+  // key tiles of query tile t: from the tile of the first key its first row may see to the tile
+  // of its last row's own position
+  auto key_tiles = [&](int t, int& first_tile) {
+    const int p0 = kv_len - q_len + t * BQ;
+    const int lp = p0 + min(BQ, q_len - t * BQ) - 1;
+    int fk = 0;
+    if (a.window > 0 && p0 - a.window + 1 > 0) fk = p0 - a.window + 1;
+    first_tile = fk / BKV;
+    return lp / BKV - first_tile + 1;
+  };
+  int n_split = 0;
+  for (int t = 0; t < nq; t++) {
+    int ft;
+    n_split += key_tiles(t, ft) >= a.split_min ? 1 : 0;
+  }
+  const bool split = cl < n_split;
+  // this block's query tile: the cl-th split tile from the top, or among the others (from the
+  // top) number cl - n_split for rank 0 and, from the bottom, the same number for rank 1
+  int qt = -1;
+  {
+    const int n_rest = nq - n_split;
+    const int want = split ? cl : (rank == 0 ? cl - n_split : n_rest - 1 - (cl - n_split));
+    if (split || (cl - n_split < (n_rest + 1) / 2 && (rank == 0 || want > cl - n_split))) {
+      int seen = 0;
+      for (int t = nq - 1; t >= 0; t--) {
+        int ft;
+        const bool sp = key_tiles(t, ft) >= a.split_min;
+        if (sp == split) {
+          if (seen == want) {
+            qt = t;
+            break;
+          }
+          seen++;
+        }
+      }
+    }
+  }
+  if (qt < 0) return;                              // nothing for this block (its partner knows)
   const int pos0 = kv_len - q_len + qt * BQ;       // position of the tile's first query
   const int rows = min(BQ, q_len - qt * BQ);
   const int last_pos = pos0 + rows - 1;
   int first_key = 0;
   if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
-  const int kt0 = first_key / BKV;
-  const int kt1 = last_pos / BKV;                  // inclusive
-  const int n_tiles = kt1 - kt0 + 1;
+  int kt_first;
+  const int n_all = key_tiles(qt, kt_first);
+  const int n_mine0 = split ? n_all / 2 : n_all;   // rank 0 also merges and stores: the smaller half
+  const int kt0 = (!split || rank == 0) ? kt_first : kt_first + n_mine0;
+  const int n_tiles = (!split || rank == 0) ? n_mine0 : n_all - n_mine0;
   const int hk = h / (a.H / a.Hkv);
 
   if (threadIdx.x == 0) {
@@ -137,6 +199,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     mbar_init(&ctl.s_full, 1);
     mbar_init(&ctl.p_ready, 128);
     mbar_init(&ctl.o_full, 1);
+    mbar_init(&ctl.land_free, 1);
+    mbar_init(&ctl.land_full, 128);
     for (int s = 0; s < KV_STAGES; s++) {
       mbar_init(&ctl.kv_full[s], a.use_tma ? 1 : N_LOADERS);
       mbar_init(&ctl.kv_empty[s], 1);
@@ -153,6 +217,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl.tmem_base;
   volatile int* abort_flag = &ctl.abort_flag;
+  if (split) {
+    // both blocks' barriers exist before either signals the other's
+    cluster_arrive();
+    cluster_wait();
+  }
 
   if (warp >= 5 && a.use_tma) {
     // ---- loader by TMA: one box per (page, K or V, 64-wide block of the head) ----
@@ -308,10 +377,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     bool ok = true;
     TL(0);
     for (int j = 0; j < n_tiles && ok; j++) {
-      if (j == 4) TL(1);
+      if (j == 2) TL(1);
       ok = mbar_wait(&ctl.s_full, j & 1, abort_flag);
       if (!ok) break;
-      if (j == 4) TL(2);
+      if (j == 2) TL(2);
       tc_fence_after_sync();
       const int key0 = (kt0 + j) * BKV;
       // a tile needs the mask only where it meets the diagonal, the window's edge or the end
@@ -374,10 +443,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_before_sync();       // the loads of S are done before the next S may be written
       fence_async_proxy();          // P is visible to the tensor core
       mbar_arrive(&ctl.p_ready);
-      if (j == 4) TL(4);
+      if (j == 2) TL(4);
       ok = mbar_wait(&ctl.o_full, j & 1, abort_flag);
       if (!ok) break;
-      if (j == 4) TL(5);
+      if (j == 2) TL(5);
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
@@ -388,9 +457,45 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         for (int x = 0; x < 32; x++) o[c + x] = o[c + x] * alpha + __uint_as_float(v[x]);
       }
       tc_fence_before_sync();
-      if (j == 4) TL(6);
+      if (j == 2) TL(6);
     }
     TL(7);
+    if (split) {
+      // The landing area is rank 0's K/V stages, free once its own tiles are done:
+      // [1 + D/4 pieces of 16 bytes][128 rows]: piece 0 = (max, sum), then the output row.
+      float4* land = reinterpret_cast<float4*>(sK);
+      if (rank == 1) {
+        if (ok) ok = mbar_wait_cluster(&ctl.land_free, 0, abort_flag);
+        const uint32_t dst = map_to_peer(land, 0u) + (uint32_t)row * 16u;
+        st_peer_v4(dst, __float_as_uint(m), __float_as_uint(ok ? l : 0.0f), 0u, 0u);
+#pragma unroll
+        for (int c = 0; c < D / 4; c++)
+          st_peer_v4(dst + (uint32_t)(c + 1) * (BQ * 16u), __float_as_uint(o[4 * c]), __float_as_uint(o[4 * c + 1]),
+                     __float_as_uint(o[4 * c + 2]), __float_as_uint(o[4 * c + 3]));
+        mbar_arrive_peer(map_to_peer(&ctl.land_full, 0u));
+        ok = false;                                   // rank 0 stores the rows
+      } else {
+        asm volatile("bar.sync 1, 128;" ::: "memory");    // every row of this block is done with K and V
+        if (threadIdx.x == 0) mbar_arrive_peer(map_to_peer(&ctl.land_free, 1u));
+        TL(8);
+        if (!mbar_wait_cluster(&ctl.land_full, 0, abort_flag)) ok = false;
+        TL(9);
+        const float4 ml = land[row];
+        const float m2 = ml.x, l2 = ml.y;
+        const float mm = fmaxf(m, m2);
+        const float m_use = mm == -INFINITY ? 0.0f : mm;
+        const float a1 = exp2f((m - m_use) * a.scale_log2), a2 = exp2f((m2 - m_use) * a.scale_log2);
+        l = l * a1 + l2 * a2;
+#pragma unroll
+        for (int c = 0; c < D / 4; c++) {
+          const float4 v = land[(c + 1) * BQ + row];
+          o[4 * c] = o[4 * c] * a1 + v.x * a2;
+          o[4 * c + 1] = o[4 * c + 1] * a1 + v.y * a2;
+          o[4 * c + 2] = o[4 * c + 2] * a1 + v.z * a2;
+          o[4 * c + 3] = o[4 * c + 3] * a1 + v.w * a2;
+        }
+      }
+    }
     if (ok && row_valid) {
       const float inv = 1.0f / l;
       __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row) * a.o_stride + (size_t)h * D;
@@ -406,6 +511,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 
   tc_fence_before_sync();
   __syncthreads();
+  TLB(1);
   if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
   if (warp == 4) {
     tc_fence_after_sync();
@@ -477,8 +583,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, 
                          cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  dim3 grid((max_q_len + BQ - 1) / BQ, a.H, R);
-  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 1, true, mq, mkv, a);
+  dim3 grid(a.H * R, (max_q_len + BQ - 1) / BQ, 2);      // two blocks (one cluster) per query tile
+  return sglc_launch(attention_prefill_kernel<D>, grid, dim3(THREADS), smem, stream, 2, true, mq, mkv, a);
 }
 }  // namespace
 
@@ -486,7 +592,14 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, 
 SGLC_API int sglc_attention_prefill_timeline(unsigned long long* out) {
   return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16);
 }
+SGLC_API int sglc_attention_prefill_block_times(unsigned long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tl_blocks, sizeof(unsigned long long) * 2 * 2048);
+}
 #endif
+
+// Tuning hook: key tiles from which a query tile is split over two blocks (default 5).
+static int g_split_min = 5;
+SGLC_API void sglc_attention_prefill_set_split_min(int n) { g_split_min = n < 2 ? 2 : n; }
 
 // Head sizes this kernel takes.
 SGLC_API int sglc_attention_prefill_tc_supports(int D) { return D == 64 || D == 128; }
@@ -503,7 +616,7 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
                                        int* err, cudaStream_t stream) {
   if (R <= 0 || max_q_len <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0) return SGLC_ERR_ARGUMENT;
-  if (!(D == 64 || D == 128) || H > 65535 || R > 65535 || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
+  if (!(D == 64 || D == 128) || H > 65535 || R > 32767 || max_q_len > 65535 * BQ || !(scale > 0.0f)) return SGLC_ERR_UNSUPPORTED;
   if (q_stride % 8 != 0 || o_stride % 8 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
       ((uintptr_t)cache & 15))
     return SGLC_ERR_UNSUPPORTED;
@@ -518,6 +631,7 @@ SGLC_API int sglc_attention_prefill_tc(const void* q, int q_stride, const void* 
   a.window = window;
   a.err = err;
   a.skip_single = skip_single;
+  a.split_min = g_split_min;
   // TMA needs whole pages inside a 128-key tile and rows it can address
   CUtensorMap mq, mkv;
   memset(&mq, 0, sizeof(mq));

@@ -29,6 +29,18 @@ __global__ void kv_write_kernel(const TS* __restrict__ k_src, const TS* __restri
   const TS* ks = k_src + (size_t)t * src_stride;
   const TS* vs = v_src + (size_t)t * src_stride;
   int HD = Hkv * D;
+  if (sizeof(TS) == sizeof(TC) && (D * sizeof(TC)) % 16 == 0 && (((uintptr_t)ks | (uintptr_t)vs) & 15) == 0 &&
+      ((size_t)src_stride * sizeof(TS)) % 16 == 0) {
+    // same type on both sides and 16-byte aligned rows: whole 16-byte pieces
+    constexpr int PER = 16 / sizeof(TC);
+    for (int i = threadIdx.x; i < HD / PER; i += blockDim.x) {
+      int h = (i * PER) / D, d = (i * PER) % D;
+      size_t o = ((size_t)h * page_size + off) * D + d;
+      *reinterpret_cast<uint4*>(kp + o) = *reinterpret_cast<const uint4*>(ks + (size_t)i * PER);
+      *reinterpret_cast<uint4*>(vp + o) = *reinterpret_cast<const uint4*>(vs + (size_t)i * PER);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < HD; i += blockDim.x) {
     int h = i / D, d = i % D;
     size_t o = ((size_t)h * page_size + off) * D + d;
@@ -43,7 +55,7 @@ SGLC_API int sglc_kv_write(const void* k_src, const void* v_src, int src_stride,
                            const int* slots, int T, int Hkv, int D, int page_size, int n_pages,
                            int src_dtype, int cache_dtype, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
-  int threads = Hkv * D >= 512 ? 256 : 128;
+  int threads = Hkv * D >= 2048 ? 256 : (Hkv * D >= 512 ? 128 : 64);
   if (src_dtype == SGLC_F32 && cache_dtype == SGLC_F32)
     return sglc_launch(kv_write_kernel<float, float>, dim3(T), dim3(threads), 0, stream, 1, true,
                        (const float*)k_src, (const float*)v_src, src_stride, (float*)cache, slots, T,

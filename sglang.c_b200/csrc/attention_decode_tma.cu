@@ -346,6 +346,13 @@ bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int
 // (no block-wide step per stage); the groups are merged once per item in group order.  The
 // token's own key and value come from the step's rows (or the cache) by plain loads after
 // the dependency wait and are folded in by group 0, which also writes them into the cache.
+// 2^x by the special-function unit (arguments here are <= 0 up to rounding; -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct StreamArgs {
   Args b;
   int n_items;        // tokens served x heads
@@ -537,6 +544,8 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
         const __nv_bfloat16* sk = stages + (size_t)s * stage_elems;
         const __nv_bfloat16* sv = sk + (size_t)tile_keys * D;
         const int key0 = g.k_base + j * tile_keys;
+        // a stage in the middle of an item holds keys of the item only: no per-key test there
+        const bool whole = key0 >= g.lo && key0 + tile_keys <= pos;
         for (int r0 = 0; r0 < rows_per_group; r0 += 4) {
           float sc[4];
           bool valid[4];
@@ -545,7 +554,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
           for (int u = 0; u < 4; u++) {
             const int row = g_id + NG * (r0 + u);
             const int key = key0 + row;
-            valid[u] = (r0 + u) < rows_per_group && key >= g.lo && key < pos;
+            valid[u] = (r0 + u) < rows_per_group && (whole || (key >= g.lo && key < pos));
             float sum = 0.0f;
             if (valid[u]) {
               uint4 kq = *reinterpret_cast<const uint4*>(sk + (size_t)row * D + dl * 8);
@@ -565,7 +574,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
             if (valid[u]) mt = fmaxf(mt, sum);
           }
           if (mt > -INFINITY) {
-            const float corr = exp2f(m - mt);        // 0 at the first keys (m = -inf)
+            const float corr = ex2(m - mt);          // 0 at the first keys (m = -inf)
             l *= corr;
 #pragma unroll
             for (int y = 0; y < 8; y++) acc[y] *= corr;
@@ -573,7 +582,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
             for (int u = 0; u < 4; u++) {
               if (valid[u]) {
                 const int row = g_id + NG * (r0 + u);
-                const float pw = exp2f(sc[u] - mt);
+                const float pw = ex2(sc[u] - mt);
                 uint4 vq = *reinterpret_cast<const uint4*>(sv + (size_t)row * D + dl * 8);
                 float f[8];
                 bf16x8_to_f32(vq, f);
@@ -602,7 +611,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
 #pragma unroll
       for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu >> (32 - LPR), sum, o);
       const float mt = fmaxf(m, sum);
-      const float corr = exp2f(m - mt), pw = exp2f(sum - mt);
+      const float corr = ex2(m - mt), pw = ex2(sum - mt);
       bf16x8_to_f32(vn, f);
       l = l * corr + pw;
 #pragma unroll
@@ -633,7 +642,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
       for (int w = 0; w < NG; w++) {
         const float lw = mrec[w * REC + 1];
         if (lw > 0.0f) {
-          const float e = exp2f(mrec[w * REC] - M);
+          const float e = ex2(mrec[w * REC] - M);
           L += lw * e;
           o += mrec[w * REC + 2 + tid] * e;
         }

@@ -100,6 +100,54 @@ __global__ void layernorm_row4_kernel(const float* __restrict__ x, const int* __
   }
 }
 
+// Many rows (prompt portions), bfloat16 output: a warp per row, the row in registers (lane l
+// holds the 16-byte pieces l, l+32, ...), no block-wide barrier.  Used for the bfloat16 path
+// only: its order of additions differs from the kernels above, and in the 32-bit path a row's
+// bits must not depend on how many rows share its step.
+template <int NV>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                      __nv_bfloat16* __restrict__ out, int n_rows, int E, float eps) {
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int n4 = E / 4;
+  pdl_wait();
+  if (r >= n_rows) return;
+  const int src = rows ? rows[r] : r;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * E);
+  float4 v[NV];
+  float s = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = lane + 32 * j;
+    v[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  }
+  const float mean = warp_sum(s) / (float)E;
+  float q = 0.0f;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    if (lane + 32 * j < n4) {
+      float dx = v[j].x - mean, dy = v[j].y - mean, dz = v[j].z - mean, dw = v[j].w - mean;
+      q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+    }
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(q) / (float)E + eps);
+  __nv_bfloat16* o = out + (size_t)r * E;
+#pragma unroll
+  for (int j = 0; j < NV; j++) {
+    const int i = lane + 32 * j;
+    if (i < n4) {
+      const float4 g = reinterpret_cast<const float4*>(gamma)[i], b = reinterpret_cast<const float4*>(beta)[i];
+      __nv_bfloat162 h0 = __floats2bfloat162_rn((v[j].x - mean) * inv * g.x + b.x, (v[j].y - mean) * inv * g.y + b.y);
+      __nv_bfloat162 h1 = __floats2bfloat162_rn((v[j].z - mean) * inv * g.z + b.z, (v[j].w - mean) * inv * g.w + b.w);
+      *reinterpret_cast<uint2*>(o + 4 * i) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+    }
+  }
+}
+
 SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma, const float* beta,
                             void* out, int n_rows, int E, float eps, int out_dtype,
                             cudaStream_t stream) {
@@ -111,6 +159,20 @@ SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma,
   int rc = SGLC_OK;
   bool al = vec && ((reinterpret_cast<uintptr_t>(gamma) & 15) == 0) &&
             ((reinterpret_cast<uintptr_t>(beta) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  if (al && out_dtype == SGLC_BF16 && n_rows >= 64 && E / 4 <= 32 * 16) {
+    const int nv = (E / 4 + 31) / 32;
+    const dim3 grid((n_rows + 7) / 8), block(256);
+#define WARP_LAUNCH(NV)                                                                               \
+  return sglc_launch(layernorm_warp_kernel<NV>, grid, block, 0, stream, 1, true, x, rows, gamma, beta, \
+                     (__nv_bfloat16*)out, n_rows, E, eps)
+    if (nv <= 2) WARP_LAUNCH(2);
+    if (nv <= 4) WARP_LAUNCH(4);
+    if (nv <= 6) WARP_LAUNCH(6);
+    if (nv <= 8) WARP_LAUNCH(8);
+    if (nv <= 13) WARP_LAUNCH(13);
+    WARP_LAUNCH(16);
+#undef WARP_LAUNCH
+  }
   if (al && E / 4 <= 1024) {
     int th = ((E / 4 + 31) / 32) * 32;
     if (out_dtype == SGLC_F32)

@@ -294,12 +294,23 @@ class Engine:
     def has_prepared(self):
         return self._prepared is not None
 
-    def run_prepared(self, tokens):
-        """Run the step that prepare_repeat set up, with these token ids (one per request)."""
+    def run_prepared(self, tokens=None, device_tokens=None):
+        """Run the step that prepare_repeat set up, with these token ids (one per request): a
+        list on the host, or an int32 device tensor whose first entries are the ids in request
+        order (what a sampler left on the device: the step is then queued without the host
+        having seen them; ids outside the vocabulary raise the embedding kernel's error flag)."""
         if self._prepared is None:
             raise StepError("no prepared step (prepare_repeat first)")
+        R = len(self._rep["reqs"])
+        if device_tokens is not None:
+            if device_tokens.dtype != torch.int32 or device_tokens.numel() < R or not device_tokens.is_cuda:
+                self.cancel_prepared()
+                raise StepError("run_prepared: device_tokens must be an int32 device tensor of one id per request")
+            ctx = self._finish_prepared(None)
+            self.bufs.dview("tokens", R).copy_(device_tokens[:R], non_blocking=True)
+            return self._run(ctx)
         toks = np.asarray(tokens, dtype=np.int64)
-        if toks.shape != (len(self._rep["reqs"]),) or toks.min() < 0 or toks.max() >= self.plan.vocab_size:
+        if toks.shape != (R,) or toks.min() < 0 or toks.max() >= self.plan.vocab_size:
             self.cancel_prepared()
             raise StepError("run_prepared: one token id inside the vocabulary for each request")
         return self._run(self._finish_prepared(toks))
@@ -318,7 +329,8 @@ class Engine:
         R = len(rep["reqs"])
         o = rep["lens"]
         b = self.bufs
-        b.npview("tokens")[:R] = toks
+        if toks is not None:
+            b.npview("tokens")[:R] = toks
         b.upload()
         self._prepared = None
         rep["lens"] = o + 1

@@ -93,8 +93,12 @@ class Scheduler:
         self.sampler = sampler if sampler is not None else Sampler(engine.rt.device, engine.max_requests)
         # prepare the next step of single tokens on the host while the device runs this one
         # (only engines that offer it: Engine.prepare_repeat)
-        self.prepare_ahead = hasattr(engine, "prepare_repeat")
-        self._ahead = None
+        # a step's ids are read one call later (see step): needs the engine's prepared steps
+        # and a sampler that can be launched without waiting
+        self.lagging = hasattr(engine, "prepare_repeat") and hasattr(self.sampler, "launch") \
+            and hasattr(self.sampler, "fetch")
+        self._ahead = None               # ids of the requests the engine holds a prepared step for
+        self._flight = None              # (requests sampled, sampler ticket) of the step not yet read
 
     # -- entry points (names of the reference's C interface) --------------------
     def submit_ids(self, ids, max_new=16, sp=None):
@@ -219,22 +223,38 @@ class Scheduler:
         return chosen
 
     def step(self):
-        """Run one step; returns how many requests finished in it."""
-        chosen = None
-        if self._ahead is not None:
-            # the last call prepared this step while the device was busy: it stands if nothing
-            # has changed since (no request finished, aborted, or arrived)
+        """Run one step; returns how many requests finished in this call.
+
+        With the device sampler and an engine that can prepare a step ahead, a step's sampled
+        ids are read one call later: a call first queues the next step of single tokens behind
+        the step in flight (its ids pass from the sampler to the embedding on the device), then
+        waits for the ids of the step in flight and appends them, then prepares the step after
+        on the host.  So the device always has the next step queued while the host does its
+        bookkeeping.  Whatever changes the set of running requests (one ends, is aborted,
+        arrives) makes the next call take the plain path: wait, plan, launch.  A request that
+        ends while a step with it is already queued has that step's id dropped."""
+        flight, self._flight = self._flight, None
+        nxt = None
+        if flight is not None and self._ahead is not None:
             ahead, self._ahead = self._ahead, None
             if self.engine.has_prepared() and not self.waiting and ahead == [r.id for r in self.running]:
-                chosen = [(r, 1) for r in self.running]
+                # queued without having seen the ids of the step in flight
                 sampled = list(self.running)
-                logits = self.engine.run_prepared([r.gen[-1] for r in self.running])
+                logits = self.engine.run_prepared(device_tokens=self.sampler.d_out)
+                for r in sampled:
+                    r.n_computed += 1
+                self.stats.n_steps += 1
+                nxt = (sampled, self._launch_sampler(logits, sampled), [r.n_computed for r in sampled])
             else:
                 self.engine.cancel_prepared()
-        if chosen is None:
+        finished = self._collect(flight) if flight is not None else 0
+        if nxt is None:
+            if self._ahead is not None:          # (prepared in the last call, and not usable after all)
+                self._ahead = None
+                self.engine.cancel_prepared()
             chosen = self.plan_step()
             if not chosen:
-                return 0
+                return finished
             entries, sampled = [], []
             for r, n in chosen:
                 np_ = len(r.prompt)
@@ -249,40 +269,61 @@ class Scheduler:
                 if r.n_computed + n <= np_:
                     self.stats.prefill_tokens += n
             logits = self.engine.step(entries)
-        for r, n in chosen:
-            r.n_computed += n
-        self.stats.n_steps += 1
-        # While the device runs this step: if every running request is sampled in it and none
-        # waits, the next step most likely brings one token for each of them, and all of it but
-        # the token ids can be prepared now.  (A request that ends in this step ends the
-        # preparation with it: Engine.end_request cancels.)
-        if self.prepare_ahead and not self.waiting and len(sampled) == len(self.running) \
-                and all(len(r.gen) + 1 < r.max_new for r in sampled):
+            for r, n in chosen:
+                r.n_computed += n
+            self.stats.n_steps += 1
+            nxt = (sampled, self._launch_sampler(logits, sampled) if sampled else None,
+                   [r.n_computed for r in sampled])
+        sampled = nxt[0]
+        if not self.lagging:
+            # results in the same call (a sampler or an engine that cannot run ahead)
+            return finished + self._collect(nxt)
+        self._flight = nxt
+        # While the device runs the step just queued: if every running request is sampled in it,
+        # none waits and none can end by its length, the step after brings one token for each of
+        # them, and all of it but the ids is prepared now.  (A request that ends meanwhile ends
+        # the preparation with it: Engine.end_request cancels.)
+        if not self.waiting and sampled and len(sampled) == len(self.running) \
+                and all(len(r.gen) + 1 < r.max_new and not r.sp.has_penalties() for r in sampled):
             ids = [r.id for r in self.running]
             if self.engine.prepare_repeat(ids):
                 self._ahead = ids
-        finished = 0
-        if sampled:
-            us = []
-            for r in sampled:
-                if r.sp.greedy:
-                    us.append(0.0)
-                else:
-                    r.rng, u = uniform(r.rng)
-                    us.append(u)
-            out = self.sampler.sample(logits, [r.sp for r in sampled], us,
-                                      histories=[r.gen for r in sampled],
-                                      want_logprobs=self.want_logprobs)
-            toks, lps = out if self.want_logprobs else (out, None)
-            for i, r in enumerate(sampled):
-                if self._append(r, toks[i], lps[i] if lps else None):
-                    finished += 1
         return finished
 
-    def _append(self, r, tok, logprob):
+    def _launch_sampler(self, logits, sampled):
+        us = []
+        for r in sampled:
+            if r.sp.greedy:
+                us.append(0.0)
+            else:
+                r.rng, u = uniform(r.rng)
+                us.append(u)
+        args = (logits, [r.sp for r in sampled], us)
+        kw = dict(histories=[r.gen for r in sampled], want_logprobs=self.want_logprobs)
+        if self.lagging:
+            return self.sampler.launch(*args, **kw)
+        return self.sampler.sample(*args, **kw)          # a sampler without launch/fetch: results at once
+
+    def _collect(self, flight):
+        """Take a step's sampled ids and append them; returns how many requests ended."""
+        sampled, ticket, n_after = flight
+        if not sampled:
+            return 0
+        out = self.sampler.fetch(ticket) if self.lagging else ticket
+        toks, lps = out if self.want_logprobs else (out, None)
+        finished = 0
+        for i, r in enumerate(sampled):
+            if r.state != RUNNING:
+                continue                 # ended or aborted after this step was queued: its id is dropped
+            if self._append(r, toks[i], lps[i] if lps else None, n_after[i]):
+                finished += 1
+        return finished
+
+    def _append(self, r, tok, logprob, n_computed):
         """The reference's req_sample_append (src/scheduler.c:288-310): eos or a
         stop id ends the request without being appended; then max_new and the
-        model's positions."""
+        model's positions.  n_computed: the request's tokens in the cache after the step
+        that gave `tok` (a later step may be queued already)."""
         if tok == self.eos_token_id and self.eos_token_id is not None and not r.sp.ignore_eos:
             self.running.remove(r)
             self._finish(r, "eos")
@@ -299,7 +340,7 @@ class Scheduler:
             self.running.remove(r)
             self._finish(r, "length")
             return True
-        if r.n_computed + 1 >= self.engine.plan.max_positions:
+        if n_computed + 1 >= self.engine.plan.max_positions:
             self.running.remove(r)
             self._finish(r, "context")
             return True

@@ -6,8 +6,9 @@ The default run has the layer sizes of GPT-2 small (n_layer 12, n_embd 768,
 n_head 12, n_inner 3072, vocab 50257, positions 1024) with random weights in
 bfloat16, a batch of 8 requests decoding at a context of 512 tokens, pages of
 16.  A "step" is one decode step of the whole batch.  One JSON line is printed:
-`value` is decoded tokens a second with the step timed on the device (CUDA
-events around every step, L2 flushed between steps); `e2e` is the same through
+`value` is decoded tokens a second with the steps timed on the device (one pair
+of CUDA events around all K steps, each step's sampled ids feeding the next; a
+step reads more than L2 holds, so nothing is flushed); `e2e` is the same through
 the Python entry point (scheduler, host token ids in and out); `prefill` is one
 step of 2,048 prompt tokens (2 x 1,024); `roofline` is the decode step's bytes
 (every weight once, the cache of the live requests) over its time, against the
@@ -128,8 +129,11 @@ def make_model(tmp, cfg_d, n_layer=None):
 
 
 def time_decode(eng, batch, context, steps, warmup, flush):
-    """Device time of `steps` decode steps of `batch` requests that hold `context`
-    tokens each; returns (ms per step list, launches per step)."""
+    """Device time of `steps` decode steps in a row of `batch` requests that hold `context`
+    tokens each, one pair of CUDA events around all of them; returns (ms per step list,
+    launches in the timed region).  The steps are real decoding (each step's sampled ids are the
+    next step's input) and are queued one ahead, as the scheduler does.  L2 is not flushed in
+    between: a step reads more than L2 holds (weights and cache of the live requests)."""
     import numpy as np
     import torch
     from sglang_c_b200.csrc import ops
@@ -148,25 +152,32 @@ def time_decode(eng, batch, context, steps, warmup, flush):
         eng.step([StepEntry(r, todo[r][done:done + n], []) for r in reqs])
         done += n
     sampler = Sampler(eng.rt.device, max(batch, 1))
-    sp = [SamplingParams(temperature=0.0)] * batch
     toks = [int(t) for t in rng.integers(0, V, size=batch)]
-    times = []
     launches = 0
-    for it in range(warmup + steps):
-        if flush is not None:
-            flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = ops.LAUNCHES
-        e0.record()
-        logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(reqs, toks)])
+
+    def one_step(first):
+        # the step's ids come from the sampler's output of the step before, on the device; its
+        # host side (cache growth, packed arrays) is prepared while the device runs that step
+        if first or not eng.prepare_repeat(reqs):
+            logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(reqs, toks)])
+        else:
+            logits = eng.run_prepared(device_tokens=sampler.d_out)
         ops.sample(logits, sampler.d_params[:batch], sampler.d_hist_tok, sampler.d_hist_cnt,
                    sampler.d_out[:batch])
-        e1.record()
-        torch.cuda.synchronize()
-        toks = sampler.d_out[:batch].tolist()
-        if it >= warmup:
-            times.append(e0.elapsed_time(e1))
-            launches += ops.LAUNCHES - l0
+
+    one_step(True)
+    for it in range(warmup):
+        one_step(False)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ops.LAUNCHES
+    e0.record()
+    for it in range(steps):
+        one_step(False)
+    e1.record()
+    torch.cuda.synchronize()
+    launches = ops.LAUNCHES - l0
+    times = [e0.elapsed_time(e1) / steps] * steps
     for r in reqs:
         eng.end_request(r)
     return times, launches
@@ -214,7 +225,7 @@ def time_e2e(model_dir, batch, context, steps, warmup):
     sp = SamplingParams(temperature=0.0, ignore_eos=True)
     for _ in range(batch):
         s.submit_ids([int(t) for t in rng.integers(0, V, size=context)], warmup + steps + 32, sp)
-    while any(r.n_pending != 1 or r.n_computed == 0 for r in s.running) or s.waiting:
+    while s.waiting or any(r.n_computed < len(r.prompt) for r in s.running):
         s.step()                                   # prompts done; every request decodes from here
     for _ in range(warmup):
         s.step()
@@ -347,8 +358,8 @@ def main():
                    "n_inner": base["n_inner"], "vocab_size": base["vocab_size"],
                    "n_positions": base["n_positions"], "global_batch": BATCH, "seq_len": CONTEXT,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "prefill_tokens": PREFILL_TOKENS,
-                   "prefill_shape": "2 prompts x 1024", "l2": "flushed between timed steps",
-                   "timing": "CUDA events per step, mean", "cuda_graph": "decode step replays a graph",
+                   "prefill_shape": "2 prompts x 1024", "l2": "a step reads more than L2 holds (no flush)",
+                   "timing": "CUDA events around all steps", "cuda_graph": "decode step replays a graph",
                    "peaks": pk["source"]},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,

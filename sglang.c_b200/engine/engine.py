@@ -44,6 +44,7 @@ class Engine:
         self.b_cap = (plan.max_positions + self.page_size - 1) // self.page_size
         self._paged = self.cache.paged_groups()
         self._any_window = any(self.cache.groups[gi].need.window is not None for gi in self._paged)
+        self._max_heads = max([int(lp.mixer.params.get("n_heads", 1)) for lp in plan.layers] + [1])
         self._rep = None                  # what a repeated step of single tokens updates in place
         self._prepared = None             # prepare_repeat's mark: indices of requests that took a page
         self.bufs = StepBuffers(runtime.device, self.max_step_tokens, self.max_requests, self.b_cap,
@@ -335,6 +336,7 @@ class Engine:
         self._prepared = None
         rep["lens"] = o + 1
         ctx = StepContext(self.rt, self.ws)
+        ctx.repeating = True             # steady decoding: a new launch shape is captured at once
         ctx.T, ctx.R, ctx.n_want, ctx.n_decode = R, R, rep["nw"], R
         ctx.max_keys = int(o.max()) + 1
         ctx.max_q_len = 1
@@ -377,9 +379,22 @@ class Engine:
         return logits
 
     def _graph_key(self, ctx):
-        bound = 128
-        while bound < ctx.max_keys:
-            bound *= 2
+        # The context bound sizes the shared memory of the decode attention of small batches
+        # (a block stages its whole key range), and what a block holds of an SM decides whether
+        # it can start, and prefetch, while the kernels ahead still run: there the bound moves in
+        # steps of 128 keys up to 1024 and of about an eighth of the length beyond (a capture
+        # every 128 steps costs less than the tighter bound wins).  Other steps take the next
+        # power of two, so a graph serves until the contexts double.
+        from ..csrc import ops
+        if ctx.n_decode == ctx.T and ctx.T * self._max_heads < ops.STREAM_MIN_ITEMS:
+            g = 128
+            while g * 8 < ctx.max_keys:
+                g *= 2
+            bound = ((ctx.max_keys + g - 1) // g) * g
+        else:
+            bound = 128
+            while bound < ctx.max_keys:
+                bound *= 2
         bound = min(bound, self.plan.max_positions)
         return (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
                 bound, ctx.n_decode), bound
@@ -402,11 +417,11 @@ class Engine:
     def _forward_graphed(self, ctx):
         """Replay a CUDA graph when this step's launch shapes have been seen before.  The
         shapes depend on the number of tokens, requests and wanted rows, on the longest
-        portion (in 128-query tiles) and on an upper bound of the context length (the next
-        power of two, so a graph serves until the contexts double).  Everything else a step
+        portion (in 128-query tiles) and on an upper bound of the context length (see _graph_key).  Everything else a step
         varies in lies in device arrays at fixed addresses.  A shape runs eagerly the first
         time it is seen, is captured the second time, and replayed afterwards; the least
-        recently used graphs are dropped beyond `max_graphs`."""
+        recently used graphs are dropped beyond `max_graphs`.  (A step of steady decoding, which
+        will come again, is captured the first time.)"""
         from ..csrc import ops
         key, ctx.max_keys = self._graph_key(ctx)
         before_buf = self.logits
@@ -421,7 +436,7 @@ class Engine:
             ops.LAUNCHES += n_launches
             self.graph_replays += 1
             return out[:ctx.n_want]
-        if key not in self._graph_seen:
+        if key not in self._graph_seen and not ctx.repeating:
             if len(self._graph_seen) > 4096:
                 self._graph_seen.clear()
             self._graph_seen.add(key)

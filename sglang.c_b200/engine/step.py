@@ -78,6 +78,7 @@ class StepContext:
         self.h_state_slots = []
         self.max_keys = 0
         self.max_q_len = 0
+        self.repeating = False         # the step repeats the last one's shape (steady decoding)
         self.n_decode = 0              # tokens of requests that bring exactly one token
         self.decode_tokens = None      # their indices (device int32), meaningful in mixed steps
         self.groups: List[GroupStep] = []

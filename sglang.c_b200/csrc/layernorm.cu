@@ -100,7 +100,7 @@ __global__ void layernorm_row4_kernel(const float* __restrict__ x, const int* __
   }
 }
 
-// Many rows (prompt portions), bfloat16 output: a warp per row, the row in registers (lane l
+// Many rows (prompt portions of a thousand tokens and more), bfloat16 output: a warp per row, the row in registers (lane l
 // holds the 16-byte pieces l, l+32, ...), no block-wide barrier.  Used for the bfloat16 path
 // only: its order of additions differs from the kernels above, and in the 32-bit path a row's
 // bits must not depend on how many rows share its step.
@@ -159,7 +159,7 @@ SGLC_API int sglc_layernorm(const float* x, const int* rows, const float* gamma,
   int rc = SGLC_OK;
   bool al = vec && ((reinterpret_cast<uintptr_t>(gamma) & 15) == 0) &&
             ((reinterpret_cast<uintptr_t>(beta) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-  if (al && out_dtype == SGLC_BF16 && n_rows >= 64 && E / 4 <= 32 * 16) {
+  if (al && out_dtype == SGLC_BF16 && n_rows >= 1024 && E / 4 <= 32 * 16) {   // (8 rows a block: enough blocks for every SM)
     const int nv = (E / 4 + 31) / 32;
     const dim3 grid((n_rows + 7) / 8), block(256);
 #define WARP_LAUNCH(NV)                                                                               \

@@ -47,7 +47,7 @@ def test_embed(T, E, V, P, dtype):
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n,E,eps", [(1, 16, 1e-5), (33, 96, 1e-6), (7, 1600, 1e-5), (3, 50, 1e-3), (2, 4099, 1e-5),
-                                     (300, 768, 1e-5), (65, 1600, 1e-5), (129, 96, 1e-6), (70, 2048, 1e-5), (64, 24, 1e-5)])
+                                     (1300, 768, 1e-5), (1025, 1600, 1e-5), (1100, 96, 1e-6), (1024, 2048, 1e-5), (2000, 24, 1e-5)])
 def test_layernorm(n, E, eps, out_dtype):
     ops = _ops()
     x = _rand(n, E, seed=4, scale=3.0) + 1.5

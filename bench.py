@@ -293,7 +293,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "integemjack/sglang.c is a C/CMake project without a Python package: "
-                          "pip install of /root/reference finds no setup.py or pyproject.toml"}))
+                          "pip install of its source tree finds no setup.py or pyproject.toml"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

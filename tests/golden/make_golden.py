@@ -1,7 +1,7 @@
 """Makes tests/golden/gpt2_tiny_reference.json: logits of the reference's own CPU
 GPT-2 (integemjack/sglang.c, src/gpt2.c) on a tiny random model.
 
-Usage:  python tests/golden/make_golden.py [/path/to/reference]
+Usage:  python tests/golden/make_golden.py REFERENCE_TREE
 
 It compiles the reference's C sources, unmodified, with gcc into a shared library
 in a temporary folder, writes a tiny random model folder with this repository's
@@ -58,7 +58,9 @@ def tokens():
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py REFERENCE_TREE   (a checkout of integemjack/sglang.c)")
+    ref = sys.argv[1]
     tmp = tempfile.mkdtemp(prefix="sglc_golden_")
     lib = os.path.join(tmp, "libsglref.so")
     cmd = ["gcc", "-std=c11", "-O2", "-fopenmp", "-D_GNU_SOURCE", "-shared", "-fPIC",

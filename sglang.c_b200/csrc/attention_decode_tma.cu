@@ -306,15 +306,17 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Ar
 }
 
 // ---- host: the cache as a 5-D tensor, one box = one page's rows of one head (no swizzle) ----
-struct KeyKV { const void* p; int D, ps, Hkv, n_pages; };
+struct KeyKV { const void* p; int D, ps, Hkv, n_pages, swizzled; };
 std::mutex g_mutex;
 std::vector<std::pair<KeyKV, CUtensorMap>> g_kvmaps;
 
-bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages) {
+// swizzled: boxes 64 elements (128 bytes) wide in the 128-byte swizzle (the streaming kernel's
+// ldmatrix reads), else whole rows as they lie
+bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int n_pages, bool swizzled = false) {
   std::lock_guard<std::mutex> lock(g_mutex);
   for (auto& e : g_kvmaps)
     if (e.first.p == cache && e.first.D == D && e.first.ps == ps && e.first.Hkv == Hkv &&
-        e.first.n_pages == n_pages) {
+        e.first.n_pages == n_pages && e.first.swizzled == (int)swizzled) {
       *out = e.second;
       return true;
     }
@@ -323,58 +325,82 @@ bool get_kv_map(CUtensorMap* out, const void* cache, int D, int ps, int Hkv, int
   cuuint64_t dims[5] = {(cuuint64_t)D, (cuuint64_t)ps, (cuuint64_t)Hkv, 2, (cuuint64_t)n_pages};
   cuuint64_t strides[4] = {(cuuint64_t)D * 2, (cuuint64_t)ps * D * 2, (cuuint64_t)Hkv * ps * D * 2,
                            (cuuint64_t)2 * Hkv * ps * D * 2};
-  cuuint32_t box[5] = {(cuuint32_t)D, (cuuint32_t)ps, 1, 1, 1};
+  cuuint32_t box[5] = {(cuuint32_t)(swizzled ? 64 : D), (cuuint32_t)ps, 1, 1, 1};
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUtensorMap m;
   CUresult rc = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box,
-                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzled ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return false;
   if (g_kvmaps.size() > 1024) g_kvmaps.clear();
-  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages}, m});
+  g_kvmaps.push_back({KeyKV{cache, D, ps, Hkv, n_pages, (int)swizzled}, m});
   *out = m;
   return true;
 }
 
 // ---- streaming variant for large batches -------------------------------------------------
 // A fixed number of blocks per SM, each walking a list of (token, head) items.  One warp feeds
-// a ring of shared-memory stages with the item's pages (TMA, one box per page and K/V), and
-// runs ahead of the four warps that consume them, across item boundaries, so a block never
-// waits for a round trip between items: at large batches the one-shot kernels are bound by
-// block lifetime times the number of blocks an SM holds, this one by bytes.  A group of D/8
-// lanes owns every NG-th key of a stage and keeps its own running maximum, sum and output
-// (no block-wide step per stage); the groups are merged once per item in group order.  The
-// token's own key and value come from the step's rows (or the cache) by plain loads after
-// the dependency wait and are folded in by group 0, which also writes them into the cache.
+// a ring of shared-memory stages (64 keys and their values each) with the item's pages by TMA,
+// in the 128-byte swizzle, and runs ahead of the four warps that consume them, across item
+// boundaries, so a block never waits for a round trip between items: at large batches the
+// one-shot kernels are bound by block lifetime times the number of blocks an SM holds, this
+// one by bytes.  The four warps share every stage through the warp-level tensor-core
+// instruction, the query being row 0 of a 16-row operand: each warp takes the scores of 16 of
+// the stage's keys, the scores meet in shared memory (one block barrier a stage), every warp
+// then does the same softmax step on all 64 and takes a quarter of the head's output columns.
+// (The same sums on the CUDA cores cost eight times the instructions, and the kernel was bound
+// by instruction issue.)  No merge at the end of an item: each warp holds the item's maximum
+// and sum and its own columns.  The token's own key and value come from the step's rows (or
+// the cache) by plain loads after the dependency wait, and are written into the cache here.
 // 2^x by the special-function unit (arguments here are <= 0 up to rounding; -inf gives 0)
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D[16x8] += A[16x16] B[16x8], bfloat16 operands, float accumulators; rows 8..15 of A are zero here
+__device__ __forceinline__ void mma_row0(float* d, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 
 struct StreamArgs {
   Args b;
   int n_items;        // tokens served x heads
-  int tile_pages;     // pages per stage
   int n_stages;
-  int nb_cap;         // most pages an item can span (sizes nothing; checked by the host)
 };
 constexpr int S_WARPS = 4;                  // consumer warps; warp S_WARPS produces
 constexpr int S_THREADS = (S_WARPS + 1) * 32;
 constexpr int S_MAX_STAGES = 8;
 constexpr int S_PMAX = 8;                   // page ids held per producer lane: 256 pages per item
+constexpr int S_TILE = 64;                  // keys per stage
 
 struct ItemGeom {
   int lo, first_page, k_base, n_rows, n_tiles, n_pages;
 };
-__device__ __forceinline__ ItemGeom item_geom(int pos, int window, int ps, int tile_keys) {
+__device__ __forceinline__ ItemGeom item_geom(int pos, int window, int ps) {
   ItemGeom g;
   g.lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   g.first_page = g.lo / ps;
   g.k_base = g.first_page * ps;
   g.n_rows = pos - g.k_base;                       // cached rows ahead of the token's own
-  g.n_tiles = (g.n_rows + tile_keys - 1) / tile_keys;
+  g.n_tiles = (g.n_rows + S_TILE - 1) / S_TILE;
   g.n_pages = (g.n_rows + ps - 1) / ps;
   return g;
 }
@@ -383,19 +409,23 @@ template <int D>
 __global__ void __launch_bounds__(S_THREADS)
 attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const StreamArgs sa) {
   const Args& a = sa.b;
-  extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int LPR = D / 8;                // lanes per key row
-  constexpr int KG = 32 / LPR;              // key groups per warp
-  constexpr int NG = S_WARPS * KG;          // key groups per block
-  constexpr int REC = D + 2;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // the 128-byte swizzle is a function of the address: stages start on 1024-byte boundaries
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int DH = D / 64;                // 128-byte column blocks of a row
+  constexpr int NT = D / 8;                 // 8-wide output tiles of the head
+  constexpr int NT_W = NT / S_WARPS;        // ... of one warp
+  constexpr int KS = D / 16;                // 16-deep steps over the head dimension
+  constexpr int LPR = D / 8;                // lanes that share the token's own row
+  constexpr int HALF_BYTES = S_TILE * 128;               // one column block of a K or V tile
+  constexpr int KV_BYTES = DH * HALF_BYTES;              // K (or V) of a stage
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;
   const int ps = a.page_size;
-  const int tile_keys = sa.tile_pages * ps;
+  const int tile_pages = S_TILE / ps;
   const int NS = sa.n_stages;
-  const size_t stage_elems = (size_t)2 * tile_keys * D;      // K rows, then V rows
-  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem);
-  float* merge = reinterpret_cast<float*>(smem + (size_t)NS * stage_elems * 2);   // [2][NG][REC]
   __shared__ __align__(8) uint64_t full[S_MAX_STAGES];
   __shared__ __align__(8) uint64_t empty[S_MAX_STAGES];
+  __shared__ float s_scores[2][S_TILE];     // a stage's scores, written by quarters, read by all
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -411,16 +441,16 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
   }
   __syncthreads();
   volatile int* af = &s_abort;
+  auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
 
   if (warp == S_WARPS) {
     // ---- producer: metadata and pages of EARLIER positions only, which the kernel ahead
     // cannot have written, so nothing here waits for it ----
-    auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
     auto pos_of = [&](int item) { return item < sa.n_items ? a.positions[token_of(item)] : 0; };
     auto load_ids = [&](int item, int pos, int* pid) {
       const int t = token_of(item);
       const int r = a.token_req ? a.token_req[t] : t;
-      const ItemGeom g = item_geom(pos, a.window, ps, tile_keys);
+      const ItemGeom g = item_geom(pos, a.window, ps);
       const int* bt = a.block_table + (size_t)r * a.bt_stride + g.first_page;
 #pragma unroll
       for (int k = 0; k < S_PMAX; k++) {
@@ -438,7 +468,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
       const int item_n = item + gridDim.x;
       if (item_n < sa.n_items) load_ids(item_n, pos_nxt, pid_nxt);
       const int pos_n2 = pos_of(item_n + gridDim.x);
-      const ItemGeom g = item_geom(pos_cur, a.window, ps, tile_keys);
+      const ItemGeom g = item_geom(pos_cur, a.window, ps);
       const int hk = (item % H) / G;
       for (int j = 0; j < g.n_tiles && ok; j++, it++) {
         const int s = it % NS;
@@ -448,21 +478,24 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
           ok = __shfl_sync(0xffffffffu, w, 0) != 0;
           if (!ok) break;
         }
-        const int pg0 = j * sa.tile_pages;
-        const int npg = min(sa.tile_pages, g.n_pages - pg0);
-        __nv_bfloat16* sk = stages + (size_t)s * stage_elems;
-        __nv_bfloat16* sv = sk + (size_t)tile_keys * D;
+        const int pg0 = j * tile_pages;
+        const int npg = min(tile_pages, g.n_pages - pg0);
+        uint8_t* sk = smem + (size_t)s * STAGE_BYTES;
+        uint8_t* sv = sk + KV_BYTES;
         if (lane == 0) mbar_expect_tx(&full[s], (uint32_t)npg * 2u * (uint32_t)ps * (uint32_t)D * 2u);
-        for (int p = 0; p < npg; p++) {
+        __syncwarp();
+        // the lane that holds a page's id issues its copies: the pages of a stage go out side by side
+        const int p = (lane - pg0) & 31;                 // this lane's page within the stage, if < npg
+        if (p < npg) {
           const int idx = pg0 + p;
-          int v = 0;
+          int page = 0;
 #pragma unroll
           for (int k = 0; k < S_PMAX; k++)
-            if (k == (idx >> 5)) v = pid_cur[k];
-          const int page = __shfl_sync(0xffffffffu, v, idx & 31);
-          if (lane == 0) {
-            tma_load_5d(sk + (size_t)p * ps * D, &map_kv, &full[s], 0, 0, hk, 0, page);
-            tma_load_5d(sv + (size_t)p * ps * D, &map_kv, &full[s], 0, 0, hk, 1, page);
+            if (k == (idx >> 5)) page = pid_cur[k];
+#pragma unroll
+          for (int hb = 0; hb < DH; hb++) {
+            tma_load_5d(sk + hb * HALF_BYTES + p * ps * 128, &map_kv, &full[s], hb * 64, 0, hk, 0, page);
+            tma_load_5d(sv + hb * HALF_BYTES + p * ps * 128, &map_kv, &full[s], hb * 64, 0, hk, 1, page);
           }
         }
       }
@@ -480,177 +513,207 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
   }
 
   // ---- consumers ----
-  const int kg = lane / LPR, dl = lane % LPR;
-  const int g_id = warp * KG + kg;
-  const int rows_per_group = tile_keys / NG;
-  const float qscale = a.scale * 1.4426950408889634f;      // scores in base-2 exponent units
+  const int gq = lane >> 2, tq = lane & 3;          // row group and column pair of the MMA fragments
+  const int dl = lane % LPR;
+  const float cexp = a.scale * 1.4426950408889634f; // scores in base-2 exponent units
   const size_t page_elems = (size_t)2 * a.Hkv * ps * D;
   const size_t v_off = (size_t)a.Hkv * ps * D;
   const bool fused = a.k_new != nullptr;
-  pdl_wait();       // queries and the step's own keys and values come from the kernel ahead
-  auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
-  // what an item needs from global memory is requested one item ahead
+  // what an item needs from global memory is requested one item ahead: the position (step
+  // metadata, readable at once), and the query as row 0 of the MMA's 16 x 16 operand (lanes
+  // 0..3 hold it, the others zeros), which the kernel ahead writes
   int item = blockIdx.x;
-  int t_nxt = 0, pos_nxt = 0;
-  uint4 q_nxt = make_uint4(0u, 0u, 0u, 0u);
-  if (item < sa.n_items) {
-    t_nxt = token_of(item);
-    pos_nxt = a.positions[t_nxt];
-    q_nxt = *reinterpret_cast<const uint4*>(a.q + (size_t)t_nxt * a.q_stride + (size_t)(item % H) * D + dl * 8);
-  }
+  int t_nxt = item < sa.n_items ? token_of(item) : 0;
+  int pos_nxt = item < sa.n_items ? a.positions[t_nxt] : 0;
+  uint32_t qa_nxt[KS][2];
+#pragma unroll
+  for (int ks = 0; ks < KS; ks++) qa_nxt[ks][0] = qa_nxt[ks][1] = 0u;
+  auto fetch_q = [&](int item_) {
+    if (gq == 0) {
+      const uint32_t* qp = reinterpret_cast<const uint32_t*>(a.q + (size_t)t_nxt * a.q_stride + (size_t)(item_ % H) * D);
+#pragma unroll
+      for (int ks = 0; ks < KS; ks++) {
+        qa_nxt[ks][0] = qp[8 * ks + tq];
+        qa_nxt[ks][1] = qp[8 * ks + 4 + tq];
+      }
+    }
+  };
+  pdl_wait();       // queries and the step's own keys and values come from the kernel ahead
+  if (item < sa.n_items) fetch_q(item);
   int it = 0;
-  bool ok = true;
-  for (int n = 0; item < sa.n_items; item += gridDim.x, n++) {
+  for (; item < sa.n_items; item += gridDim.x) {
     const int t = t_nxt, pos = pos_nxt, h = item % H, hk = h / G;
-    float qreg[8];
-    bf16x8_to_f32(q_nxt, qreg);
+    uint32_t qa[KS][2];
 #pragma unroll
-    for (int y = 0; y < 8; y++) qreg[y] *= qscale;
-    // the token's own key and value (group 0 folds them in at the end)
-    uint4 kn = make_uint4(0u, 0u, 0u, 0u), vn = kn;
+    for (int ks = 0; ks < KS; ks++) {
+      qa[ks][0] = qa_nxt[ks][0];
+      qa[ks][1] = qa_nxt[ks][1];
+    }
+    // the token's own key and value: every warp scores the key (lanes 0..LPR-1 hold 8 elements
+    // of the query and of the key each) and takes the value's elements of its own columns
+    const __nv_bfloat16* ksrc;
+    const __nv_bfloat16* vsrc;
     int slot = -1;
-    if (g_id == 0) {
-      const __nv_bfloat16* ksrc;
-      const __nv_bfloat16* vsrc;
-      if (fused) {
-        ksrc = a.k_new + (size_t)t * a.new_stride + (size_t)hk * D;
-        vsrc = a.v_new + (size_t)t * a.new_stride + (size_t)hk * D;
-        slot = a.slots[t];
-      } else {
-        const int r = a.token_req ? a.token_req[t] : t;
-        const int page = a.block_table[(size_t)r * a.bt_stride + pos / ps];
-        ksrc = a.cache + (size_t)page * page_elems + (size_t)hk * ps * D + (size_t)(pos % ps) * D;
-        vsrc = ksrc + v_off;
-      }
+    if (fused) {
+      ksrc = a.k_new + (size_t)t * a.new_stride + (size_t)hk * D;
+      vsrc = a.v_new + (size_t)t * a.new_stride + (size_t)hk * D;
+      if (warp == 0) slot = a.slots[t];
+    } else {
+      const int r = a.token_req ? a.token_req[t] : t;
+      const int page = a.block_table[(size_t)r * a.bt_stride + pos / ps];
+      ksrc = a.cache + (size_t)page * page_elems + (size_t)hk * ps * D + (size_t)(pos % ps) * D;
+      vsrc = ksrc + v_off;
+    }
+    uint4 kn = make_uint4(0u, 0u, 0u, 0u), qrow = kn, vn = kn;
+    if (lane < LPR) {
       kn = reinterpret_cast<const uint4*>(ksrc)[dl];
-      vn = reinterpret_cast<const uint4*>(vsrc)[dl];
+      qrow = reinterpret_cast<const uint4*>(a.q + (size_t)t * a.q_stride + (size_t)h * D)[dl];
+      if (warp == 0) vn = reinterpret_cast<const uint4*>(vsrc)[dl];
     }
-    {
-      const int item_n = item + gridDim.x;
-      if (item_n < sa.n_items) {
-        t_nxt = token_of(item_n);
-        pos_nxt = a.positions[t_nxt];
-        q_nxt = *reinterpret_cast<const uint4*>(a.q + (size_t)t_nxt * a.q_stride + (size_t)(item_n % H) * D + dl * 8);
-      }
-    }
-    const ItemGeom g = item_geom(pos, a.window, ps, tile_keys);
-    float m = -INFINITY, l = 0.0f, acc[8];
+    uint32_t v_own[NT_W];      // the value's elements 8 (NT_W warp + u) + 2 tq, +1 (lanes 0..3 use them)
 #pragma unroll
-    for (int y = 0; y < 8; y++) acc[y] = 0.0f;
+    for (int u = 0; u < NT_W; u++)
+      v_own[u] = reinterpret_cast<const uint32_t*>(vsrc)[4 * (NT_W * warp + u) + tq];
+    if (item + (int)gridDim.x < sa.n_items) {
+      t_nxt = token_of(item + gridDim.x);
+      pos_nxt = a.positions[t_nxt];
+      fetch_q(item + gridDim.x);
+    }
+    const ItemGeom g = item_geom(pos, a.window, ps);
+    float m_run = -INFINITY, l_run = 0.0f;      // l_run: this lane's share of the sum
+    float o[NT_W][4];
+#pragma unroll
+    for (int u = 0; u < NT_W; u++) o[u][0] = o[u][1] = o[u][2] = o[u][3] = 0.0f;
     for (int j = 0; j < g.n_tiles; j++, it++) {
       const int s = it % NS;
-      if (ok) ok = mbar_wait(&full[s], (it / NS) & 1, af);
+      bool ok = !*af && mbar_wait(&full[s], (it / NS) & 1, af);
+      ok = __all_sync(0xffffffffu, ok);
+      const uint32_t sk = smem_u32(smem + (size_t)s * STAGE_BYTES);
+      const uint32_t sv = sk + KV_BYTES;
+      const int key0 = g.k_base + j * S_TILE;
+      const bool whole = key0 >= g.lo && key0 + S_TILE <= pos;
+      float* sc_buf = s_scores[it & 1];
       if (ok) {
-        const __nv_bfloat16* sk = stages + (size_t)s * stage_elems;
-        const __nv_bfloat16* sv = sk + (size_t)tile_keys * D;
-        const int key0 = g.k_base + j * tile_keys;
-        // a stage in the middle of an item holds keys of the item only: no per-key test there
-        const bool whole = key0 >= g.lo && key0 + tile_keys <= pos;
-        for (int r0 = 0; r0 < rows_per_group; r0 += 4) {
-          float sc[4];
-          bool valid[4];
-          float mt = m;
+        if (!whole && lane < 16) {
+          // rows that hold no key of this item may hold anything: their values are zeroed (a
+          // zero weight times a non-number would still spoil the sum), their scores masked below
+          const int row = 16 * warp + lane, key = key0 + row;
+          if (key < g.lo || key >= pos) {
 #pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const int row = g_id + NG * (r0 + u);
-            const int key = key0 + row;
-            valid[u] = (r0 + u) < rows_per_group && (whole || (key >= g.lo && key < pos));
-            float sum = 0.0f;
-            if (valid[u]) {
-              uint4 kq = *reinterpret_cast<const uint4*>(sk + (size_t)row * D + dl * 8);
-              float f[8];
-              bf16x8_to_f32(kq, f);
-              float s0 = 0.0f, s1 = 0.0f;
+            for (int hb = 0; hb < DH; hb++)
 #pragma unroll
-              for (int y = 0; y < 8; y += 2) {
-                s0 = fmaf(qreg[y], f[y], s0);
-                s1 = fmaf(qreg[y + 1], f[y + 1], s1);
-              }
-              sum = s0 + s1;
-            }
-#pragma unroll
-            for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            sc[u] = sum;
-            if (valid[u]) mt = fmaxf(mt, sum);
+              for (int c = 0; c < 8; c++)
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(sv + hb * HALF_BYTES + row * 128 + c * 16), "r"(0u) : "memory");
           }
-          if (mt > -INFINITY) {
-            const float corr = ex2(m - mt);          // 0 at the first keys (m = -inf)
-            l *= corr;
+        }
+        // scores of this warp's 16 keys (two tiles of 8) against row 0
+        float sc[2][4];
 #pragma unroll
-            for (int y = 0; y < 8; y++) acc[y] *= corr;
+        for (int u = 0; u < 2; u++) sc[u][0] = sc[u][1] = sc[u][2] = sc[u][3] = 0.0f;
+        {
+          const int mi = lane >> 3, row = lane & 7;
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-              if (valid[u]) {
-                const int row = g_id + NG * (r0 + u);
-                const float pw = ex2(sc[u] - mt);
-                uint4 vq = *reinterpret_cast<const uint4*>(sv + (size_t)row * D + dl * 8);
-                float f[8];
-                bf16x8_to_f32(vq, f);
-                l += pw;
+          for (int kp = 0; kp < KS; kp += 2) {
+            const int c = 2 * kp + mi;                   // 16-byte column of the row
 #pragma unroll
-                for (int y = 0; y < 8; y++) acc[y] = fmaf(pw, f[y], acc[y]);
-              }
+            for (int u = 0; u < 2; u++) {
+              const int key = 16 * warp + 8 * u + row;
+              uint32_t b0, b1, b2, b3;
+              ldmatrix_x4(sk + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+              mma_row0(sc[u], qa[kp][0], qa[kp][1], b0, b1);
+              mma_row0(sc[u], qa[kp + 1][0], qa[kp + 1][1], b2, b3);
             }
-            m = mt;
+          }
+        }
+        if (gq == 0) {
+#pragma unroll
+          for (int u = 0; u < 2; u++)
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int i = 16 * warp + 8 * u + 2 * tq + e;
+              const int key = key0 + i;
+              sc_buf[i] = (whole || (key >= g.lo && key < pos)) ? sc[u][e] * cexp : -INFINITY;
+            }
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(S_WARPS * 32) : "memory");     // scores and zeroed rows are there for all
+      if (ok) {
+        const float s0 = sc_buf[lane], s1 = sc_buf[lane + 32];
+        const float m_new = fmaxf(m_run, warp_max(fmaxf(s0, s1)));
+        if (m_new > -INFINITY) {
+          const float corr = ex2(m_run - m_new);           // 0 at the first keys (m_run = -inf)
+          const float p0 = ex2(s0 - m_new), p1 = ex2(s1 - m_new);
+          m_run = m_new;
+          l_run = l_run * corr + (p0 + p1);
+#pragma unroll
+          for (int u = 0; u < NT_W; u++) {
+            o[u][0] *= corr;
+            o[u][1] *= corr;
+          }
+          // the weights as row 0 of the MMA's 16 x 16 operand, 16 keys a step: this lane needs
+          // keys 16 kk + 2 tq + {0, 1, 8, 9}; key i sits in lane i % 32 (p0 for i < 32, else p1)
+          uint32_t pa[4][2];
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++) {
+            const float pv = kk < 2 ? p0 : p1;
+            const int l0 = (16 * kk) % 32 + 2 * tq;
+            const float w0 = __shfl_sync(0xffffffffu, pv, l0), w1 = __shfl_sync(0xffffffffu, pv, l0 + 1);
+            const float w2 = __shfl_sync(0xffffffffu, pv, l0 + 8), w3 = __shfl_sync(0xffffffffu, pv, l0 + 9);
+            pa[kk][0] = pack_bf16x2(w0, w1);
+            pa[kk][1] = pack_bf16x2(w2, w3);
+          }
+          const int mi = lane >> 3, row = lane & 7;
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++) {
+            const int key = 16 * kk + (mi & 1) * 8 + row;
+#pragma unroll
+            for (int u = 0; u < NT_W; u += 2) {
+              const int c = NT_W * warp + u + (mi >> 1);
+              uint32_t b0, b1, b2, b3;
+              ldmatrix_x4_trans(sv + (c >> 3) * HALF_BYTES + key * 128 + (((c & 7) ^ (key & 7)) << 4), b0, b1, b2, b3);
+              mma_row0(o[u], pa[kk][0], pa[kk][1], b0, b1);
+              mma_row0(o[u + 1], pa[kk][0], pa[kk][1], b2, b3);
+            }
           }
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);       // the stage may be refilled
     }
-    if (g_id == 0) {
-      float f[8];
-      bf16x8_to_f32(kn, f);
+    // the token's own key and value, and the result
+    {
+      float fq[8], fk[8];
+      bf16x8_to_f32(qrow, fq);
+      bf16x8_to_f32(kn, fk);
       float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
       for (int y = 0; y < 8; y += 2) {
-        s0 = fmaf(qreg[y], f[y], s0);
-        s1 = fmaf(qreg[y + 1], f[y + 1], s1);
+        s0 = fmaf(fq[y], fk[y], s0);
+        s1 = fmaf(fq[y + 1], fk[y + 1], s1);
       }
-      float sum = s0 + s1;
+      const float s_own = warp_sum(s0 + s1) * cexp;          // lanes beyond the row hold zeros
+      const float m_fin = fmaxf(m_run, s_own);
+      const float corr = ex2(m_run - m_fin), pw = ex2(s_own - m_fin);
+      const float l_fin = warp_sum(l_run) * corr + pw;
+      if (gq == 0 && !*af) {
+        const float inv = 1.0f / l_fin;
+        __nv_bfloat16* op = a.out + (size_t)t * a.o_stride + (size_t)h * D;
 #pragma unroll
-      for (int o = 1; o < LPR; o <<= 1) sum += __shfl_xor_sync(0xffffffffu >> (32 - LPR), sum, o);
-      const float mt = fmaxf(m, sum);
-      const float corr = ex2(m - mt), pw = ex2(sum - mt);
-      bf16x8_to_f32(vn, f);
-      l = l * corr + pw;
-#pragma unroll
-      for (int y = 0; y < 8; y++) acc[y] = fmaf(pw, f[y], acc[y] * corr);
-      m = mt;
-      if (fused && slot >= 0 && h % G == 0) {
+        for (int u = 0; u < NT_W; u++) {
+          const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(&v_own[u]);
+          const float2 vf = __bfloat1622float2(vv);
+          const float y0 = (o[u][0] * corr + pw * vf.x) * inv, y1 = (o[u][1] * corr + pw * vf.y) * inv;
+          *reinterpret_cast<uint32_t*>(op + 8 * (NT_W * warp + u) + 2 * tq) = pack_bf16x2(y0, y1);
+        }
+      }
+      if (warp == 0 && lane < LPR && fused && slot >= 0 && h % G == 0) {
         __nv_bfloat16* kdst = a.cache + (size_t)(slot / ps) * page_elems + (size_t)hk * ps * D + (size_t)(slot % ps) * D;
         reinterpret_cast<uint4*>(kdst)[dl] = kn;
         reinterpret_cast<uint4*>(kdst + v_off)[dl] = vn;
       }
     }
-    // merge the groups in group order
-    float* mrec = merge + (size_t)(n & 1) * NG * REC;
-    float* mine = mrec + (size_t)g_id * REC;
-    if (dl == 0) {
-      mine[0] = m;
-      mine[1] = l;
-    }
-#pragma unroll
-    for (int y = 0; y < 8; y++) mine[2 + dl * 8 + y] = acc[y];
-    asm volatile("bar.sync 1, %0;" ::"n"(S_WARPS * 32) : "memory");
-    if (tid < D) {
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < NG; w++) M = fmaxf(M, mrec[w * REC]);
-      float L = 0.0f, o = 0.0f;
-#pragma unroll
-      for (int w = 0; w < NG; w++) {
-        const float lw = mrec[w * REC + 1];
-        if (lw > 0.0f) {
-          const float e = ex2(mrec[w * REC] - M);
-          L += lw * e;
-          o += mrec[w * REC + 2 + tid] * e;
-        }
-      }
-      if (ok) a.out[(size_t)t * a.o_stride + (size_t)h * D + tid] = __float2bfloat16_rn(o / L);
-    }
   }
-  if (!ok && tid == 0 && a.err) atomicExch(a.err, 1);
+  if (tid == 0 && *af && a.err) atomicExch(a.err, 1);
 }
 
 template <int D>
@@ -718,13 +781,12 @@ SGLC_API int sglc_attention_decode_tma(const void* q, int q_stride, void* cache,
   return launch<128>(mkv, a, T, stream);
 }
 
-// Whether the streaming kernel takes the case.
+// Whether the streaming kernel takes the case: head sizes 64 and 128, pages of 8, 16, 32 or 64
+// positions (a stage holds 64 keys in whole pages, each page box on a 1024-byte boundary), and
+// at most 256 pages per item.
 SGLC_API int sglc_attention_decode_stream_supports(int D, int page_size, int max_keys, int window) {
-  if (!(D == 64 || D == 128) || page_size < 4 || page_size > 128) return 0;
-  const int NG = 4 * (32 / (D / 8));
-  int tile_pages = page_size >= 64 ? 1 : 64 / page_size;
-  if (64 % page_size != 0 && page_size < 64) return 0;
-  if ((tile_pages * page_size) % NG != 0) return 0;
+  if (!(D == 64 || D == 128)) return 0;
+  if (!(page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64)) return 0;
   int eff = window > 0 && window < max_keys ? window : max_keys;
   if ((eff + page_size - 1) / page_size + 1 > 32 * S_PMAX) return 0;
   return 1;
@@ -749,7 +811,7 @@ SGLC_API int sglc_attention_decode_stream(const void* q, int q_stride, void* cac
   if ((page_size * D * 2) % 128 != 0) return SGLC_ERR_UNSUPPORTED;
   if ((long long)T * H > 0x7fffffffLL) return SGLC_ERR_UNSUPPORTED;
   CUtensorMap mkv;
-  if (!get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages)) return SGLC_ERR_UNSUPPORTED;
+  if (!get_kv_map(&mkv, cache, D, page_size, Hkv, n_pages, true)) return SGLC_ERR_UNSUPPORTED;
   StreamArgs sa;
   memset(&sa, 0, sizeof(sa));
   Args& a = sa.b;
@@ -765,17 +827,13 @@ SGLC_API int sglc_attention_decode_stream(const void* q, int q_stride, void* cac
   a.new_stride = new_stride; a.slots = slots;
   a.err = err;
   sa.n_items = T * H;
-  sa.tile_pages = page_size >= 64 ? 1 : 64 / page_size;
-  const int tile_keys = sa.tile_pages * page_size;
-  const size_t stage_bytes = (size_t)2 * tile_keys * D * 2;
-  const int NG = 4 * (32 / (D / 8));
-  const size_t fixed = (size_t)2 * NG * (D + 2) * 4;
-  // three blocks per SM, and as many stages as then fit (at least 3, at most 8)
-  int n_stages = (int)((72 * 1024 - fixed) / stage_bytes);
+  const size_t stage_bytes = (size_t)2 * S_TILE * D * 2;   // 64 keys and 64 values
+  // three blocks per SM (two at head size 128), and as many stages as then fit, three at least
+  int n_stages = (int)(((size_t)72 * 1024 - 1024) / stage_bytes);
   if (n_stages > S_MAX_STAGES) n_stages = S_MAX_STAGES;
   if (n_stages < 3) n_stages = 3;
   sa.n_stages = n_stages;
-  const size_t smem = (size_t)n_stages * stage_bytes + fixed;
+  const size_t smem = (size_t)n_stages * stage_bytes + 1024;
   if (smem > 200 * 1024) return SGLC_ERR_UNSUPPORTED;
   static int n_sm = 0;
   if (n_sm == 0) {

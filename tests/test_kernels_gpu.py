@@ -498,7 +498,7 @@ STREAM_CASES = [
     ([260, 90, 1], 2, 2, 128, 16, None),                   # head size 128
     ([200, 77], 2, 1, 128, 32, 33),
     ([500, 64, 63], 4, 4, 64, 64, None),                   # a page per stage
-    ([130, 9], 5, 5, 64, 4, 100),
+    ([130, 9], 5, 5, 64, 8, 100),
     (list(range(1, 61)), 12, 12, 64, 16, None),            # 720 items: blocks walk several items each
     ([1500] + [40] * 50, 10, 10, 64, 16, None),            # one long request among short ones
     ([1100] * 40, 12, 12, 64, 16, None),                   # several long items per block

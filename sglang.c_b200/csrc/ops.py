@@ -25,8 +25,27 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
 
 
+_PINNED_STREAM = None
+
+
 def _stream():
+    if _PINNED_STREAM is not None:
+        return _PINNED_STREAM
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class pinned_stream:
+    """Within the block every kernel goes to the stream that is current at entry, looked up
+    once (the lookup costs as much as a launch; a forward pass makes a hundred)."""
+
+    def __enter__(self):
+        global _PINNED_STREAM
+        self.before = _PINNED_STREAM
+        _PINNED_STREAM = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def __exit__(self, *exc):
+        global _PINNED_STREAM
+        _PINNED_STREAM = self.before
 
 
 def _dt(t, what):

@@ -374,9 +374,14 @@ class Engine:
             logits = self._forward_graphed(ctx)
         else:
             self.ws.reset()
-            logits = self.model.forward(ctx, self.cache, self._logits_buffer(nw))
+            logits = self._forward(ctx, self._logits_buffer(nw))
         self.steps_run += 1
         return logits
+
+    def _forward(self, ctx, out):
+        from ..csrc import ops
+        with ops.pinned_stream():        # one stream lookup for the pass's hundred launches
+            return self.model.forward(ctx, self.cache, out)
 
     def _graph_key(self, ctx):
         # The context bound sizes the shared memory of the decode attention of small batches
@@ -441,13 +446,13 @@ class Engine:
                 self._graph_seen.clear()
             self._graph_seen.add(key)
             self.ws.reset()
-            return self.model.forward(ctx, self.cache, out)
+            return self._forward(ctx, out)
         graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         before = ops.LAUNCHES
         with torch.cuda.graph(graph):
             self.ws.reset()
-            self.model.forward(ctx, self.cache, out)
+            self._forward(ctx, out)
         n_launches = ops.LAUNCHES - before
         ops.LAUNCHES = before
         while len(self._graphs) >= self.max_graphs:

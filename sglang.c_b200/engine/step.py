@@ -28,6 +28,10 @@ class GroupStep:
     page_size: int
 
 
+_ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.int32: 4, torch.uint8: 1, torch.float16: 2,
+                 torch.int64: 8}
+
+
 class Workspace:
     """A bump allocator over one device buffer, so that a step allocates
     nothing and the same step shape uses the same addresses."""
@@ -45,7 +49,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * _ELEMENT_SIZE[dtype]
         start = (self.off + 255) & ~255
         if start + nbytes > self.buf.numel():
             raise MemoryError(

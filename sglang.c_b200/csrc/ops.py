@@ -225,11 +225,12 @@ def gemm_tc_supported(a, w):
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
 
 
-def gemm_tc(a, w, bias, out=None, residual=None, act=None):
+def gemm_tc(a, w, bias, out=None, residual=None, act=None, supported=False):
     """out = act(a·wᵀ + bias) (bfloat16 or float32), or residual += a·wᵀ + bias, on the
-    tensor cores.  a [M,K] bfloat16 (row stride free), w [N,K] bfloat16 contiguous."""
+    tensor cores.  a [M,K] bfloat16 (row stride free), w [N,K] bfloat16 contiguous.
+    supported=True: the caller has just asked gemm_tc_supported(a, w)."""
     _need_cuda(a, w, bias, out, residual)
-    if not gemm_tc_supported(a, w):
+    if not supported and not gemm_tc_supported(a, w):
         raise KernelError(f"gemm_tc: operands a {tuple(a.shape)} stride {a.stride()} / w {tuple(w.shape)} "
                           "do not meet the 16-byte row rule of TMA (K and row stride multiples of 8)")
     M, K = a.shape

@@ -39,7 +39,7 @@ class Runtime:
     # -- kernel choice --------------------------------------------------------
     def gemm(self, a, w, bias, out=None, residual=None, act=None):
         if self.dtype == "bfloat16" and ops.gemm_tc_supported(a, w):
-            return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act)
+            return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act, supported=True)
         return ops.gemm_simt(a, w, bias, out=out, residual=residual, act=act)
 
     def attend(self, ctx, q, k, v, binding, grp, out, n_heads, n_kv_heads, head_dim, scale, window):

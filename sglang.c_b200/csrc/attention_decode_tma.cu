@@ -442,6 +442,13 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
   __syncthreads();
   volatile int* af = &s_abort;
   auto token_of = [&](int item) { int ti = item / H; return a.token_list ? a.token_list[ti] : ti; };
+  // A block's items: one of every run of gridDim.x, counted from the front in even runs and from
+  // the back in odd ones.  A caller that lists long tokens first thus gives every block long and
+  // short items alike.
+  auto after = [&](int item) {
+    const int k = item / (int)gridDim.x + 1;
+    return k * (int)gridDim.x + ((k & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
 
   if (warp == S_WARPS) {
     // ---- producer: metadata and pages of EARLIER positions only, which the kernel ahead
@@ -460,14 +467,14 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
     };
     int it = 0;
     int item = blockIdx.x;
-    int pos_cur = pos_of(item), pos_nxt = pos_of(item + gridDim.x);
+    int pos_cur = pos_of(item), pos_nxt = pos_of(after(item));
     int pid_cur[S_PMAX], pid_nxt[S_PMAX];
     if (item < sa.n_items) load_ids(item, pos_cur, pid_cur);
     bool ok = true;
     while (item < sa.n_items && ok) {
-      const int item_n = item + gridDim.x;
+      const int item_n = after(item);
       if (item_n < sa.n_items) load_ids(item_n, pos_nxt, pid_nxt);
-      const int pos_n2 = pos_of(item_n + gridDim.x);
+      const int pos_n2 = pos_of(after(item_n));
       const ItemGeom g = item_geom(pos_cur, a.window, ps);
       const int hk = (item % H) / G;
       for (int j = 0; j < g.n_tiles && ok; j++, it++) {
@@ -541,7 +548,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
   pdl_wait();       // queries and the step's own keys and values come from the kernel ahead
   if (item < sa.n_items) fetch_q(item);
   int it = 0;
-  for (; item < sa.n_items; item += gridDim.x) {
+  for (; item < sa.n_items; item = after(item)) {
     const int t = t_nxt, pos = pos_nxt, h = item % H, hk = h / G;
     uint32_t qa[KS][2];
 #pragma unroll
@@ -574,10 +581,10 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const
 #pragma unroll
     for (int u = 0; u < NT_W; u++)
       v_own[u] = reinterpret_cast<const uint32_t*>(vsrc)[4 * (NT_W * warp + u) + tq];
-    if (item + (int)gridDim.x < sa.n_items) {
-      t_nxt = token_of(item + gridDim.x);
+    if (after(item) < sa.n_items) {
+      t_nxt = token_of(after(item));
       pos_nxt = a.positions[t_nxt];
-      fetch_q(item + gridDim.x);
+      fetch_q(after(item));
     }
     const ItemGeom g = item_geom(pos, a.window, ps);
     float m_run = -INFINITY, l_run = 0.0f;      // l_run: this lane's share of the sum

@@ -269,6 +269,9 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
     blocks and merged in a fixed order.  With k_new/v_new/slots (the step's own keys and
     values, [T, n_kv_heads*head_dim] views, and their cache slots) the same launch also writes
     them into the cache; this is valid only when every request brings exactly one token.
+    `token_list` (int32, its first `n_tokens` entries) names the tokens to serve; a list of all
+    tokens is an order in which the streaming kernel takes them (long contexts first balance
+    its blocks).
     Three kernels serve it, chosen by the size of the launch (or named by `variant`, for tests
     and tuning: "stream", "tma", "register")."""
     _need_cuda(q, cache, block_table, token_req, positions, out, k_new, v_new, slots, token_list)
@@ -277,10 +280,15 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
     if token_req is not None:           # None: token t belongs to the step's t-th request
         _i32(token_req, "token_req")
     T = q.shape[0]
+    order_only = False
     if token_list is not None:          # serve only the listed tokens (the first n_tokens entries)
         _i32(token_list, "token_list")
         if token_req is None or k_new is not None:
-            raise KernelError("attention_decode: a token list needs token_req and no fused cache write")
+            # without a token -> request table, or with the cache write, the list can only be an
+            # order of all tokens (long ones first); the streaming kernel alone makes use of it
+            if int(n_tokens) != T:
+                raise KernelError("attention_decode: a list of some tokens needs token_req and no fused cache write")
+            order_only = True
         T = int(n_tokens)
     n_pages, two, Hkv, page_size, D = cache.shape
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -319,6 +327,8 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
         if variant == "stream":
             raise KernelError(f"attention_decode_stream does not take head_dim {D}, page size {page_size}, "
                               f"{max_keys} keys")
+    if order_only:
+        token_list = None
     if D in (64, 128) and splits <= 8 and (page_size * D * 2) % 128 == 0 and page_size <= 256 \
             and ((variant is None and USE_TMA_DECODE and T * n_heads * splits <= 1536) or variant == "tma"):
         # keys and values staged through shared memory by TMA (measured faster up to about a

@@ -15,6 +15,14 @@ from .runtime import Runtime
 from .step import GroupStep, StepBuffers, StepContext, StepEntry, Workspace
 
 
+_ORDER_SPREAD = 64      # keys (one stage of the streaming decode attention)
+
+
+def _spread(lens):
+    """Whether the contexts of a step differ enough for their order to matter."""
+    return len(lens) > 1 and max(lens) - min(lens) >= _ORDER_SPREAD
+
+
 class StepError(ValueError):
     """A step that cannot run as asked (bad ids, unknown request, too many tokens)."""
 
@@ -222,10 +230,16 @@ class Engine:
                 ctx.max_q_len = n
             t0 += n
         qs[R] = t0
+        if n_decode > 1:
+            # single tokens in the order of their contexts, longest first: the decode attention
+            # deals its blocks long and short ones alike
+            d = dtk[:n_decode].copy()
+            dtk[:n_decode] = d[np.argsort(-pos[d], kind="stable")]
         b.upload()
 
         ctx.T, ctx.R, ctx.n_want, ctx.max_keys = T, R, nw, max_keys
         ctx.n_decode = n_decode
+        ctx.decode_ordered = n_decode == T and _spread(ctx.h_kv_len)
         # a step of single tokens is likely to come again with the same requests: keep what
         # the next one can update in place
         self._rep = None
@@ -339,6 +353,7 @@ class Engine:
         ctx.repeating = True             # steady decoding: a new launch shape is captured at once
         ctx.T, ctx.R, ctx.n_want, ctx.n_decode = R, R, rep["nw"], R
         ctx.max_keys = int(o.max()) + 1
+        ctx.decode_ordered = int(o.max()) - int(o.min()) >= _ORDER_SPREAD
         ctx.max_q_len = 1
         ctx.h_q_len = [1] * R
         ctx.h_kv_len = (o + 1).tolist()
@@ -402,7 +417,7 @@ class Engine:
                 bound *= 2
         bound = min(bound, self.plan.max_positions)
         return (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
-                bound, ctx.n_decode), bound
+                bound, ctx.n_decode, ctx.decode_ordered), bound
 
     def _graph_lookup(self, ctx):
         """Replay the graph of this step's shape if there is one (and its output buffer still

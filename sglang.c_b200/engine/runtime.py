@@ -58,7 +58,9 @@ class Runtime:
             return ops.attention_decode(q, cache, grp.block_table, None, ctx.positions, out,
                                         n_heads, scale, window, ctx.max_keys,
                                         k_new=k if fuse else None, v_new=v if fuse else None,
-                                        slots=grp.slots if fuse else None)
+                                        slots=grp.slots if fuse else None,
+                                        token_list=ctx.decode_tokens if ctx.decode_ordered else None,
+                                        n_tokens=ctx.T)
         if binding.write:
             ops.kv_write(k, v, cache, grp.slots, n_kv_heads, head_dim)
         if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \

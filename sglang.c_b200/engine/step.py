@@ -84,7 +84,8 @@ class StepContext:
         self.max_q_len = 0
         self.repeating = False         # the step repeats the last one's shape (steady decoding)
         self.n_decode = 0              # tokens of requests that bring exactly one token
-        self.decode_tokens = None      # their indices (device int32), meaningful in mixed steps
+        self.decode_tokens = None      # their indices (device int32), longest context first
+        self.decode_ordered = False    # a step of single tokens whose contexts differ by a tile of keys or more
         self.groups: List[GroupStep] = []
         self.err_flag = None
 

@@ -547,6 +547,20 @@ def test_attention_decode_streaming_kernel(case_id):
                          scale, window, max(lens), k_new=k_new, v_new=v_new, slots=slots, variant="stream")
     assert torch.equal(out3, out)
     assert torch.equal(torch.nan_to_num(holed, nan=-7.0), torch.nan_to_num(cache, nan=-7.0))
+    # all tokens in an order (long contexts first, as the engine lists them): the same result
+    order = torch.tensor(sorted(range(T), key=lambda t: -lens[t]), dtype=torch.int32, device=DEV)
+    for fused in (False, True):
+        holed2 = cache.clone()
+        if fused:
+            for r, n in enumerate(lens):
+                holed2[int(c["bt"][r, (n - 1) // ps]), :, :, (n - 1) % ps] = float("nan")
+        out4 = torch.full((T, H * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attention_decode(c["q"], holed2, c["bt"], c["token_req"] if case_id % 2 else None, c["positions"], out4,
+                             H, scale, window, max(lens), k_new=k_new if fused else None,
+                             v_new=v_new if fused else None, slots=slots if fused else None,
+                             token_list=order, n_tokens=T, variant="stream")
+        assert torch.equal(out4, out), fused
+        assert torch.equal(torch.nan_to_num(holed2, nan=-7.0), torch.nan_to_num(cache, nan=-7.0))
     assert int(ops.tc_error_flag(out.device).item()) == 0
 
 

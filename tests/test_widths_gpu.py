@@ -57,3 +57,35 @@ def test_real_widths_whole_and_cut(width_dirs, tmp_path, name, dtype):
         err, where = traces.max_error(got, ref)
         assert err < TOL[dtype], f"{name} {mode}: max error {err} at {where}"
         eng.check_device_errors()
+
+
+def test_many_single_tokens_of_unequal_contexts(width_dirs, tmp_path):
+    """Sixteen requests of 12 heads decode together: enough (token, head) items for the streaming
+    decode attention, with contexts from 20 to 330 tokens, so that the step lists its tokens
+    longest first and the kernel's blocks take them in that order."""
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.engine.replay import replay
+    d = width_dirs("small", "bfloat16")
+    rng = np.random.default_rng(5)
+    lens = [int(n) for n in rng.permutation(np.linspace(20, 330, 16).astype(int))]
+    n_tail = 5
+    reqs = {f"r{i}": traces.random_tokens(40 + i, n + n_tail, 1031) for i, n in enumerate(lens)}
+    ref = {rid: plain_gpt2.forward_dir(d, toks) for rid, toks in reqs.items()}
+    steps = []
+    ids = list(reqs)
+    for g in range(0, 16, 4):                 # prompts, four requests a step
+        steps.append({"step": len(steps), "end": [],
+                      "entries": [{"id": rid, "tokens": reqs[rid][:lens[ids.index(rid)]],
+                                   "want": list(range(lens[ids.index(rid)]))} for rid in ids[g:g + 4]]})
+    for k in range(n_tail):                   # then all sixteen, one token each
+        steps.append({"step": len(steps), "end": ids if k == n_tail - 1 else [],
+                      "entries": [{"id": rid, "tokens": [reqs[rid][lens[i] + k]], "want": [0]}
+                                  for i, rid in enumerate(ids)]})
+    eng = Engine.from_dir(d, dtype="bfloat16", page_size=16, n_pages=traces.peak_tokens(steps) // 16,
+                          max_requests=16, max_step_tokens=1024)
+    out = str(tmp_path / "out")
+    replay(eng, traces.to_lines(steps), out)
+    got = traces.collect(steps, out, 1031)
+    err, where = traces.max_error(got, ref)
+    assert err < TOL["bfloat16"], f"max error {err} at {where}"
+    eng.check_device_errors()

@@ -1,12 +1,14 @@
 // Causal attention of prompt portions over the paged bfloat16 cache on the tensor cores.
 // One block per (request, head, tile of 128 queries).  For every tile of 128 keys that the
-// queries may see:  S = Q·K^T (tcgen05.mma into tensor memory), then the softmax warps (one
-// thread per query row) read S, apply the scale, the causal bound and the window, keep the
-// running maximum and sum of an online softmax in 32-bit, write P = exp(S - max) as bfloat16
-// to shared memory, O_tile = P·V (second MMA, V taken as it lies in the cache: keys by rows),
-// and the threads fold O_tile into their row's output with the usual rescaling.  Keys and
-// values come page by page through the block table (16-byte cp.async into the 128-byte
-// swizzle the MMA expects).  Lengths, positions and block tables are read on the device.
+// queries may see:  S = Q·K^T (tcgen05.mma into tensor memory), then the eight softmax warps
+// (16 query rows a warp, a row spread over a quad of threads as in the accumulator of the
+// warp-level MMA) read S, apply the scale, the causal bound and the window, keep the running
+// maximum and sum of an online softmax in 32-bit, write P = exp(S - max) as bfloat16 to shared
+// memory, O_tile = P·V (second MMA, V taken as it lies in the cache: keys by rows), and the
+// threads fold O_tile into their rows' output with the usual rescaling.  Keys and values come
+// page by page through the block table (one TMA box per page, or 16-byte cp.async where the
+// page size does not divide 128, into the 128-byte swizzle the MMA expects).  Lengths,
+// positions and block tables are read on the device.
 // The reference's prefill attention for this architecture is k_attn (scores of a whole row in
 // shared memory, src/cuda_backend.cu:1600-1651); its tiled form for other architectures is
 // k_attn_flash (:1838-1960, CUDA cores, warp-shuffle online softmax).
@@ -27,7 +29,9 @@ using namespace tc;
 
 constexpr int BQ = 128;          // queries per block = MMA M = TMEM lanes
 constexpr int BKV = 128;         // keys per tile = MMA N of S
-constexpr int THREADS = 256;     // warps 0-3 softmax, warp 4 MMA + TMEM, warps 5-7 loaders
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int MMA_WARP = SOFTMAX_THREADS / 32;
+constexpr int THREADS = SOFTMAX_THREADS + 128;     // warps 0-7 softmax, warp 8 MMA + TMEM, warps 9-11 loaders
 constexpr int N_LOADERS = 96;
 constexpr int KV_STAGES = 2;
 
@@ -104,7 +108,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ uint32_t sw128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, (D == 64 ? 2 : 1))
 attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_kv, const Args a) {
   constexpr int DB = D / 64;                       // 64-wide blocks of the head dimension
@@ -125,8 +129,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   // The launch is a list of clusters of two blocks per (request, head), heaviest first (blocks
   // are handed out x first, then y, so every request's heaviest work starts first).  A query
   // tile with split_min or more key tiles takes a whole cluster: rank 0 walks the first half
-  // of the key tiles and rank 1 the rest, and rank 1 hands its running maximum, sum and output
-  // rows over through distributed shared memory.  The lighter query tiles go two to a cluster,
+  // of the key tiles and rank 1 the rest, and rank 0 fetches rank 1's running maximum, sum and
+  // output rows through distributed shared memory.  The lighter query tiles go two to a cluster,
   // the heaviest of them with the lightest (an idle partner would hold its place on the SM
   // until the cluster ends).  Without the split the launch lasts as long as its longest tile
   // (the last query tile of the longest request) while most SMs have long finished.
@@ -189,7 +193,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
   int kt_first;
   const int n_all = key_tiles(qt, kt_first);
-  const int n_mine0 = split ? n_all / 2 : n_all;   // rank 0 also merges and stores: the smaller half
+  // rank 1's half ends with the masked tile at the diagonal, which costs about two plain ones,
+  // and it has its rows to send: rank 0 takes one tile more than half
+  const int n_mine0 = split ? (n_all + 2) / 2 : n_all;
   const int kt0 = (!split || rank == 0) ? kt_first : kt_first + n_mine0;
   const int n_tiles = (!split || rank == 0) ? n_mine0 : n_all - n_mine0;
   const int hk = h / (a.H / a.Hkv);
@@ -197,10 +203,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   if (threadIdx.x == 0) {
     mbar_init(&ctl.q_full, a.use_tma ? 1 : N_LOADERS);
     mbar_init(&ctl.s_full, 1);
-    mbar_init(&ctl.p_ready, 128);
+    mbar_init(&ctl.p_ready, SOFTMAX_THREADS);
     mbar_init(&ctl.o_full, 1);
-    mbar_init(&ctl.land_free, 1);
-    mbar_init(&ctl.land_full, 128);
+    mbar_init(&ctl.land_free, SOFTMAX_THREADS);
+    mbar_init(&ctl.land_full, SOFTMAX_THREADS);
     for (int s = 0; s < KV_STAGES; s++) {
       mbar_init(&ctl.kv_full[s], a.use_tma ? 1 : N_LOADERS);
       mbar_init(&ctl.kv_empty[s], 1);
@@ -208,7 +214,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     ctl.abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     tmem_alloc(&ctl.tmem_base, TMEM_COLS);
     tmem_relinquish();
   }
@@ -223,9 +229,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     cluster_wait();
   }
 
-  if (warp >= 5 && a.use_tma) {
+  if (warp > MMA_WARP && a.use_tma) {
     // ---- loader by TMA: one box per (page, K or V, 64-wide block of the head) ----
-    const int lt = threadIdx.x - 160;
+    const int lt = threadIdx.x - (MMA_WARP + 1) * 32;
     // rows of a tile that no page fills (beyond the last key, before the window) must hold
     // finite numbers: zero both stages once; later tiles leave finite data behind
     for (int c = lt; c < (2 * KV_STAGES * TILE_BYTES) / 16; c += N_LOADERS)
@@ -261,9 +267,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     }
-  } else if (warp >= 5) {
+  } else if (warp > MMA_WARP) {
     // ---- loaders by cp.async: Q once, then K and V tiles through the block table ----
-    const int lt = threadIdx.x - 160;
+    const int lt = threadIdx.x - (MMA_WARP + 1) * 32;
     {
       const __nv_bfloat16* qbase = a.q + (size_t)(t0 + qt * BQ) * a.q_stride + (size_t)h * D;
       const uint32_t dst = smem_u32(sQ);
@@ -319,7 +325,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_arrive(&ctl.kv_full[j % KV_STAGES]);
     }
     cp_async_wait<0>();
-  } else if (warp == 4) {
+  } else if (warp == MMA_WARP) {
     // ---- MMA issuer ----
     if (elect_one()) {
       constexpr uint32_t idesc_s = idesc_bf16_f32(BQ, BKV, 0, 0);       // Q, K both K-major
@@ -363,17 +369,26 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
   } else {
-    // ---- softmax and output: thread = query row ----
-    const int row = warp * 32 + lane;
-    const bool row_valid = row < rows;
-    const int pos = pos0 + row;
-    const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-    const uint32_t tS = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t tO = tS + 128;
-    float m = -INFINITY, l = 0.0f;
-    float o[D];
+    // ---- softmax and output: eight warps; a warp has 16 query rows, a quad of threads a row ----
+    // (the accumulators come out of tensor memory in the layout of the warp-level MMA's
+    // accumulator: a thread holds two rows, g and g + 8, and of every 8 columns the pair 2q, 2q+1;
+    // a row's maximum and sum are reduced over its quad by shuffles)
+    const int q4 = lane & 3;
+    const int lane0 = (warp & 3) * 32 + (warp >> 2) * 16;        // the warp's first lane of tensor memory
+    const int row_r[2] = {lane0 + (lane >> 2), lane0 + (lane >> 2) + 8};
+    const bool valid_r[2] = {row_r[0] < rows, row_r[1] < rows};
+    const int pos_r[2] = {pos0 + row_r[0], pos0 + row_r[1]};
+    int lo_r[2];
 #pragma unroll
-    for (int d = 0; d < D; d++) o[d] = 0.0f;
+    for (int x = 0; x < 2; x++) lo_r[x] = (a.window > 0 && pos_r[x] - a.window + 1 > 0) ? pos_r[x] - a.window + 1 : 0;
+    const uint32_t tS = tmem_base + ((uint32_t)lane0 << 16);
+    const uint32_t tO = tS + 128;
+    const int st = threadIdx.x;                                 // 0..SOFTMAX_THREADS-1
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};   // l: this thread's share of the row sums
+    // output: for every 32 columns 16 registers in the order they are loaded in (index & 2: row g + 8)
+    float o[D / 2];
+#pragma unroll
+    for (int d = 0; d < D / 2; d++) o[d] = 0.0f;
     bool ok = true;
     TL(0);
     for (int j = 0; j < n_tiles && ok; j++) {
@@ -387,59 +402,77 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       // of the rows; elsewhere every key is visible to every row of the tile
       const bool full_tile = (key0 + BKV - 1 <= pos0) && (rows == BQ) &&
                              (a.window <= 0 || key0 >= pos0 + BQ - a.window);
-      // pass 1: the row's maximum over the keys it may see
-      float mx = -INFINITY;
+      // On such a tile row x sees the keys vis_first[x] .. vis_first[x] + vis_span[x], counted
+      // from the tile's first key (a row that sees none: a first key beyond every tile).  With
+      // rel = key - first, "visible" is one unsigned comparison: rel <= span.
+      int rel0[2];                   // rel of this thread's first key of the tile (key 2 q4)
+      uint32_t vis_span[2];
+#pragma unroll
+      for (int x = 0; x < 2; x++) {
+        const int first = max(lo_r[x], key0), last = min(pos_r[x], key0 + BKV - 1);
+        const bool any = valid_r[x] && last >= first;
+        rel0[x] = any ? key0 + 2 * q4 - first : -(1 << 20);
+        vis_span[x] = any ? (uint32_t)(last - first) : 0u;
+      }
+      // pass 1: the rows' maxima over the keys they may see
+      float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll 1
       for (int c = 0; c < BKV; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c, v);
+        uint32_t v[16];
+        tmem_ld_16x256b_x4(tS + c, v);
         tmem_ld_wait();
         if (full_tile) {
 #pragma unroll
-          for (int x = 0; x < 32; x++) mx = fmaxf(mx, __uint_as_float(v[x]));
+          for (int i = 0; i < 16; i++) mx[(i >> 1) & 1] = fmaxf(mx[(i >> 1) & 1], __uint_as_float(v[i]));
         } else {
 #pragma unroll
-          for (int x = 0; x < 32; x++) {
-            int key = key0 + c + x;
-            if (row_valid && key <= pos && key >= lo) mx = fmaxf(mx, __uint_as_float(v[x]));
+          for (int i = 0; i < 16; i++) {
+            const int x = (i >> 1) & 1;
+            const bool vis = (uint32_t)(rel0[x] + c + 8 * (i >> 2) + (i & 1)) <= vis_span[x];
+            mx[x] = fmaxf(mx[x], vis ? __uint_as_float(v[i]) : -INFINITY);
           }
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a row with no key yet
-      const float alpha = exp2f((m - m_use) * a.scale_log2);     // m = -inf gives 0
-      const float neg_m = -m_use * a.scale_log2;
-      // pass 2: p = exp(s - max) = 2^(s*c - max*c) as bfloat16 into shared memory, and the row sum
-      float sum = 0.0f;
+      if (j == 2) TL(3);
+      float alpha[2], neg_m[2];
+#pragma unroll
+      for (int x = 0; x < 2; x++) {
+        mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
+        mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 2));
+        const float m_new = fmaxf(m[x], mx[x]);
+        const float m_use = m_new == -INFINITY ? 0.0f : m_new;     // a row with no key yet
+        alpha[x] = exp2f((m[x] - m_use) * a.scale_log2);           // m = -inf gives 0
+        neg_m[x] = -m_use * a.scale_log2;
+        m[x] = m_new;
+      }
+      // pass 2: p = exp(s - max) = 2^(s*c - max*c) as bfloat16 into shared memory, and the row sums
+      float sum[2] = {0.0f, 0.0f};
 #pragma unroll 1
       for (int c = 0; c < BKV; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c, v);
+        uint32_t v[16];
+        tmem_ld_16x256b_x4(tS + c, v);
         tmem_ld_wait();
-        uint32_t packed[16];
 #pragma unroll
-        for (int x = 0; x < 32; x += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(v[x]), a.scale_log2, neg_m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(v[x + 1]), a.scale_log2, neg_m));
-          if (!full_tile) {
-            int key = key0 + c + x;
-            if (!(row_valid && key <= pos && key >= lo)) p0 = 0.0f;
-            if (!(row_valid && key + 1 <= pos && key + 1 >= lo)) p1 = 0.0f;
+        for (int b = 0; b < 4; b++) {
+#pragma unroll
+          for (int x = 0; x < 2; x++) {
+            float p0 = ex2_approx(fmaf(__uint_as_float(v[4 * b + 2 * x]), a.scale_log2, neg_m[x]));
+            float p1 = ex2_approx(fmaf(__uint_as_float(v[4 * b + 2 * x + 1]), a.scale_log2, neg_m[x]));
+            if (!full_tile) {
+              const uint32_t rel = (uint32_t)(rel0[x] + c + 8 * b);
+              if (rel > vis_span[x]) p0 = 0.0f;
+              if (rel + 1u > vis_span[x]) p1 = 0.0f;
+            }
+            sum[x] += p0 + p1;
+            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            // keys c + 8b .. +7 are one 16-byte chunk of the row; this thread's pair is its q4-th word
+            *reinterpret_cast<uint32_t*>(sP + (c / 64) * (BQ * 128) + sw128(row_r[x], (c % 64) / 8 + b) + 4 * q4) =
+                *reinterpret_cast<uint32_t*>(&hh);
           }
-          sum += p0 + p1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          packed[x / 2] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        // 32 keys = 4 chunks of 16 bytes: key block (c/64), chunks (c%64)/8 ..
-#pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {
-          int ch = (c % 64) / 8 + q4;
-          uint4 val = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-          *reinterpret_cast<uint4*>(sP + (c / 64) * (BQ * 128) + sw128(row, ch)) = val;
         }
       }
-      l = l * alpha + sum;
-      m = m_new;
+#pragma unroll
+      for (int x = 0; x < 2; x++) l[x] = l[x] * alpha[x] + sum[x];
       tc_fence_before_sync();       // the loads of S are done before the next S may be written
       fence_async_proxy();          // P is visible to the tensor core
       mbar_arrive(&ctl.p_ready);
@@ -450,70 +483,93 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tO + c, v);
+        uint32_t v[16];
+        tmem_ld_16x256b_x4(tO + c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int x = 0; x < 32; x++) o[c + x] = o[c + x] * alpha + __uint_as_float(v[x]);
+        for (int i = 0; i < 16; i++)
+          o[c / 2 + i] = o[c / 2 + i] * alpha[(i >> 1) & 1] + __uint_as_float(v[i]);
       }
       tc_fence_before_sync();
       if (j == 2) TL(6);
     }
     TL(7);
     if (split) {
-      // The landing area is rank 0's K/V stages, free once its own tiles are done:
-      // [1 + D/4 pieces of 16 bytes][128 rows]: piece 0 = (max, sum), then the output row.
+      // Rank 1 leaves its rows in its own K/V stages (free once its last MMA is done, which its
+      // threads have waited for) and rank 0 fetches them through distributed shared memory when
+      // it is done with its own tiles.  The two blocks' threads hold the same rows and columns in
+      // the same registers, so thread t's registers cross as 16-byte pieces [piece][t]: piece 0 =
+      // (max, sum) of its two rows, then the output registers four at a time.
       float4* land = reinterpret_cast<float4*>(sK);
       if (rank == 1) {
-        if (ok) ok = mbar_wait_cluster(&ctl.land_free, 0, abort_flag);
-        const uint32_t dst = map_to_peer(land, 0u) + (uint32_t)row * 16u;
-        st_peer_v4(dst, __float_as_uint(m), __float_as_uint(ok ? l : 0.0f), 0u, 0u);
+        land[st] = make_float4(m[0], ok ? l[0] : 0.0f, m[1], ok ? l[1] : 0.0f);
 #pragma unroll
-        for (int c = 0; c < D / 4; c++)
-          st_peer_v4(dst + (uint32_t)(c + 1) * (BQ * 16u), __float_as_uint(o[4 * c]), __float_as_uint(o[4 * c + 1]),
-                     __float_as_uint(o[4 * c + 2]), __float_as_uint(o[4 * c + 3]));
+        for (int c = 0; c < D / 8; c++)
+          land[(c + 1) * SOFTMAX_THREADS + st] = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
         mbar_arrive_peer(map_to_peer(&ctl.land_full, 0u));
-        ok = false;                                   // rank 0 stores the rows
+        mbar_wait_cluster(&ctl.land_free, 0, abort_flag);     // stay until rank 0 has read them
+        ok = false;                                           // rank 0 stores the rows
       } else {
-        asm volatile("bar.sync 1, 128;" ::: "memory");    // every row of this block is done with K and V
-        if (threadIdx.x == 0) mbar_arrive_peer(map_to_peer(&ctl.land_free, 1u));
         TL(8);
-        if (!mbar_wait_cluster(&ctl.land_full, 0, abort_flag)) ok = false;
+        const bool there = mbar_wait_cluster(&ctl.land_full, 0, abort_flag);
         TL(9);
-        const float4 ml = land[row];
-        const float m2 = ml.x, l2 = ml.y;
-        const float mm = fmaxf(m, m2);
-        const float m_use = mm == -INFINITY ? 0.0f : mm;
-        const float a1 = exp2f((m - m_use) * a.scale_log2), a2 = exp2f((m2 - m_use) * a.scale_log2);
-        l = l * a1 + l2 * a2;
+        if (there) {
+          const uint32_t src = map_to_peer(land, 1u) + (uint32_t)st * 16u;
+          const uint4 ml = ld_peer_v4(src);
+          uint4 v[D / 8];
 #pragma unroll
-        for (int c = 0; c < D / 4; c++) {
-          const float4 v = land[(c + 1) * BQ + row];
-          o[4 * c] = o[4 * c] * a1 + v.x * a2;
-          o[4 * c + 1] = o[4 * c + 1] * a1 + v.y * a2;
-          o[4 * c + 2] = o[4 * c + 2] * a1 + v.z * a2;
-          o[4 * c + 3] = o[4 * c + 3] * a1 + v.w * a2;
+          for (int c = 0; c < D / 8; c++) v[c] = ld_peer_v4(src + (uint32_t)(c + 1) * (SOFTMAX_THREADS * 16u));
+          const float m2[2] = {__uint_as_float(ml.x), __uint_as_float(ml.z)};
+          const float l2[2] = {__uint_as_float(ml.y), __uint_as_float(ml.w)};
+          float a1[2], a2[2];
+#pragma unroll
+          for (int x = 0; x < 2; x++) {
+            const float mm = fmaxf(m[x], m2[x]);
+            const float m_use = mm == -INFINITY ? 0.0f : mm;
+            a1[x] = exp2f((m[x] - m_use) * a.scale_log2);
+            a2[x] = exp2f((m2[x] - m_use) * a.scale_log2);
+            l[x] = l[x] * a1[x] + l2[x] * a2[x];
+          }
+#pragma unroll
+          for (int c = 0; c < D / 8; c++) {
+            o[4 * c] = o[4 * c] * a1[0] + __uint_as_float(v[c].x) * a2[0];
+            o[4 * c + 1] = o[4 * c + 1] * a1[0] + __uint_as_float(v[c].y) * a2[0];
+            o[4 * c + 2] = o[4 * c + 2] * a1[1] + __uint_as_float(v[c].z) * a2[1];
+            o[4 * c + 3] = o[4 * c + 3] * a1[1] + __uint_as_float(v[c].w) * a2[1];
+          }
+        } else {
+          ok = false;
+        }
+        mbar_arrive_peer(map_to_peer(&ctl.land_free, 1u));    // read (or given up): rank 1 may go
+      }
+    }
+    TL(10);
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+      l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
+      l[x] += __shfl_xor_sync(0xffffffffu, l[x], 2);
+    }
+    if (ok) {
+#pragma unroll
+      for (int x = 0; x < 2; x++) {
+        if (!valid_r[x]) continue;
+        const float inv = 1.0f / l[x];
+        __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row_r[x]) * a.o_stride + (size_t)h * D + 2 * q4;
+#pragma unroll
+        for (int i = 0; i < D / 8; i++) {          // the row's i-th block of 8 columns
+          __nv_bfloat162 hh = __floats2bfloat162_rn(o[4 * i + 2 * x] * inv, o[4 * i + 2 * x + 1] * inv);
+          *reinterpret_cast<__nv_bfloat162*>(op + 8 * i) = hh;
         }
       }
     }
-    if (ok && row_valid) {
-      const float inv = 1.0f / l;
-      __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row) * a.o_stride + (size_t)h * D;
-#pragma unroll
-      for (int d = 0; d < D; d += 8) {
-        __align__(16) __nv_bfloat162 hh[4];
-#pragma unroll
-        for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(o[d + 2 * x] * inv, o[d + 2 * x + 1] * inv);
-        *reinterpret_cast<uint4*>(op + d) = *reinterpret_cast<uint4*>(hh);
-      }
-    }
+    TL(11);
   }
 
   tc_fence_before_sync();
   __syncthreads();
   TLB(1);
   if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }

@@ -350,6 +350,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = mbar_wait(&ctl.p_ready, j & 1, abort_flag);
         if (!ok) break;
         tc_fence_after_sync();
+        // the next tile's scores go ahead of this tile's P.V: the softmax warps find them when
+        // they come back from sending P, and this P.V runs under their first pass
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(&ctl.kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s((j + 1) % KV_STAGES);
+        }
         const uint32_t p0 = smem_u32(sP), v0 = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < BKV / 16; k++) {
@@ -360,12 +368,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mma_commit(&ctl.o_full);
         mma_commit(&ctl.kv_empty[s]);
-        if (j + 1 < n_tiles) {
-          ok = mbar_wait(&ctl.kv_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_s((j + 1) % KV_STAGES);
-        }
       }
     }
   } else {
@@ -389,6 +391,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     float o[D / 2];
 #pragma unroll
     for (int d = 0; d < D / 2; d++) o[d] = 0.0f;
+    float alpha[2] = {0.0f, 0.0f};     // of the last tile seen: what its maximum made of the sums before it
+    // o = o * alpha + (the tile's P.V, from tensor memory)
+    auto fold = [&](const float (&al)[2]) {
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[16];
+        tmem_ld_16x256b_x4(tO + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; i++) o[c / 2 + i] = o[c / 2 + i] * al[(i >> 1) & 1] + __uint_as_float(v[i]);
+      }
+      tc_fence_before_sync();
+    };
     bool ok = true;
     TL(0);
     for (int j = 0; j < n_tiles && ok; j++) {
@@ -434,7 +449,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       if (j == 2) TL(3);
-      float alpha[2], neg_m[2];
+      if (j > 0) {
+        // the tile before: its P.V ran under this pass; fold it in (its P may then be overwritten)
+        ok = mbar_wait(&ctl.o_full, (j - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        fold(alpha);
+      }
+      float neg_m[2];
 #pragma unroll
       for (int x = 0; x < 2; x++) {
         mx[x] = fmaxf(mx[x], __shfl_xor_sync(0xffffffffu, mx[x], 1));
@@ -477,21 +499,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       fence_async_proxy();          // P is visible to the tensor core
       mbar_arrive(&ctl.p_ready);
       if (j == 2) TL(4);
-      ok = mbar_wait(&ctl.o_full, j & 1, abort_flag);
-      if (!ok) break;
-      if (j == 2) TL(5);
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[16];
-        tmem_ld_16x256b_x4(tO + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; i++)
-          o[c / 2 + i] = o[c / 2 + i] * alpha[(i >> 1) & 1] + __uint_as_float(v[i]);
+    }
+    if (ok && n_tiles > 0) {
+      ok = mbar_wait(&ctl.o_full, (n_tiles - 1) & 1, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        fold(alpha);
       }
-      tc_fence_before_sync();
-      if (j == 2) TL(6);
     }
     TL(7);
     if (split) {

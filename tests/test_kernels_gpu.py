@@ -403,6 +403,9 @@ PREFILL_TC_CASES = [
     ([500, 70], [300, 70], 2, 2, 64, 16, 100),                     # a window that ends inside a tile
     ([400], [400], 1, 1, 128, 32, 129),
     ([700, 3, 130], [2, 3, 130], 12, 12, 64, 16, None),
+    ([900], [900], 2, 1, 128, 16, None),                           # head size 128, query tiles shared by two blocks
+    ([1100], [1100], 1, 1, 64, 16, 800),                           # shared tiles whose first key tile meets the window
+    ([1500, 40], [700, 40], 2, 2, 64, 32, None),                   # a portion after 800 cached keys: 7 to 12 key tiles
 ]
 
 

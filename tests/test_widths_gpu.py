@@ -89,3 +89,31 @@ def test_many_single_tokens_of_unequal_contexts(width_dirs, tmp_path):
     err, where = traces.max_error(got, ref)
     assert err < TOL["bfloat16"], f"max error {err} at {where}"
     eng.check_device_errors()
+
+
+def test_scheduler_decodes_unequal_contexts_at_small_width(width_dirs):
+    """Greedy generation through the scheduler for sixteen prompts of 20 to 330 tokens at 12
+    heads: steady decoding runs ahead of the host, on the streaming decode attention with the
+    tokens listed longest context first.  A token other than the plain implementation's is
+    accepted only at a near tie of the plain logits."""
+    from sglang_c_b200.engine import generate, sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    d = width_dirs("small", "bfloat16")
+    rng = np.random.default_rng(11)
+    lens = [int(n) for n in rng.permutation(np.linspace(20, 330, 16).astype(int))]
+    prompts = [traces.random_tokens(300 + i, n, 1031) for i, n in enumerate(lens)]
+    s = sched_new(d, dtype="bfloat16", page_size=16, max_tokens=16 * 384, max_requests=16,
+                  max_step_tokens=1024)
+    got = generate(s, prompts, SamplingParams(temperature=0.0), max_new=8)
+    cfg, w = plain_gpt2.read_model_dir(d)
+    for p, g in zip(prompts, got):
+        assert len(g) == 8
+        seq = list(p)
+        for t in g:
+            lg = plain_gpt2.forward(cfg, w, seq)[-1]
+            best = int(np.argmax(lg))
+            assert t == best or lg[best] - lg[t] < TOL["bfloat16"], (t, best, float(lg[best] - lg[t]))
+            seq.append(t)
+    st = s.get_stats()
+    assert st.n_finished == 16 and st.pool_free == st.pool_pages
+    s.engine.check_device_errors()

@@ -305,24 +305,33 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       cp_async_commit();
     };
-    // tile j+1 is requested before tile j is waited for, so a tile is announced as soon as it
-    // has landed while the next one is already on its way
+    // Both stages are free at the start, so tiles 0 and 1 are requested at once.  Afterwards a
+    // tile is announced as soon as it has landed and BEFORE this thread waits for a stage to
+    // come free: the MMA warp issues the scores of tile j+1 ahead of P.V of tile j, so the
+    // stage of tile j is not given back until tile j+1 has been announced.
+    static_assert(KV_STAGES == 2, "the loader's order of waits assumes two stages");
     bool ok = true;
     issue_tile(0);
+    if (n_tiles > 1) {
+      issue_tile(1);
+      cp_async_wait<1>();             // all but the newest group: Q and tile 0 have landed
+    } else {
+      cp_async_wait<0>();
+    }
+    fence_async_proxy();
+    mbar_arrive(&ctl.q_full);
+    mbar_arrive(&ctl.kv_full[0]);
     for (int j = 0; j < n_tiles && ok; j++) {
-      const bool more = j + 1 < n_tiles;
-      if (more) {
-        if (j + 1 >= KV_STAGES)
-          ok = mbar_wait(&ctl.kv_empty[(j + 1) % KV_STAGES], (((j + 1) / KV_STAGES) - 1) & 1, abort_flag);
-        if (!ok) break;
-        issue_tile(j + 1);
-        cp_async_wait<1>();           // all but the newest group: tile j (and Q) have landed
-      } else {
-        cp_async_wait<0>();
+      if (j + 1 < n_tiles) {
+        cp_async_wait<0>();           // tile j+1, the only one on its way, has landed
+        fence_async_proxy();
+        mbar_arrive(&ctl.kv_full[(j + 1) % KV_STAGES]);
       }
-      fence_async_proxy();
-      if (j == 0) mbar_arrive(&ctl.q_full);
-      mbar_arrive(&ctl.kv_full[j % KV_STAGES]);
+      if (j + 2 < n_tiles) {
+        ok = mbar_wait(&ctl.kv_empty[j % KV_STAGES], (j / KV_STAGES) & 1, abort_flag);   // P.V of tile j is done
+        if (!ok) break;
+        issue_tile(j + 2);
+      }
     }
     cp_async_wait<0>();
   } else if (warp == MMA_WARP) {

@@ -406,6 +406,8 @@ PREFILL_TC_CASES = [
     ([900], [900], 2, 1, 128, 16, None),                           # head size 128, query tiles shared by two blocks
     ([1100], [1100], 1, 1, 64, 16, 800),                           # shared tiles whose first key tile meets the window
     ([1500, 40], [700, 40], 2, 2, 64, 32, None),                   # a portion after 800 cached keys: 7 to 12 key tiles
+    ([300, 129, 900], [300, 20, 900], 2, 2, 64, 48, None),         # pages that do not divide a tile: loads by cp.async
+    ([200], [200], 1, 1, 128, 24, 150),
 ]
 
 

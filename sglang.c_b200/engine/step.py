@@ -41,23 +41,36 @@ class Workspace:
         self.buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
         self.off = 0
         self.peak = 0
+        self._views = {}      # (start, dtype, shape) -> view: every layer asks for the same ones
 
     def reset(self):
         self.off = 0
 
     def alloc(self, shape, dtype):
+        start = (self.off + 255) & ~255
+        key = (start, dtype, shape if type(shape) is tuple else tuple(shape))
+        hit = self._views.get(key)
+        if hit is not None:
+            view, end = hit
+            self.off = end
+            if end > self.peak:
+                self.peak = end
+            return view
         n = 1
         for s in shape:
             n *= int(s)
         nbytes = n * _ELEMENT_SIZE[dtype]
-        start = (self.off + 255) & ~255
         if start + nbytes > self.buf.numel():
             raise MemoryError(
                 f"step workspace of {self.buf.numel()} bytes is too small for {nbytes} more bytes; "
                 "raise max_step_tokens or workspace_bytes")
         self.off = start + nbytes
         self.peak = max(self.peak, self.off)
-        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+        view = self.buf[start:start + nbytes].view(dtype).view(*shape)
+        if len(self._views) >= 4096:
+            self._views.clear()
+        self._views[key] = (view, self.off)
+        return view
 
 
 class StepContext:

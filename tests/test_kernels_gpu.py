@@ -310,6 +310,7 @@ GEMM_TC_SHAPES = [
     (33, 1000, 96), (100, 320, 96), (128, 50257, 64), (3, 96, 320), (5, 777, 128), (128, 128, 128),
     (129, 768, 768), (300, 2304, 768), (2048, 768, 3072), (1000, 1000, 200), (257, 96, 320),
     (512, 50257 // 8, 96), (130, 72, 8), (2, 8, 8),
+    (200, 128, 2048), (400, 200, 3000),      # few tiles and a long K; a K that ends inside a block of 64
 ]
 
 

@@ -129,8 +129,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   // The launch is a list of clusters of two blocks per (request, head), heaviest first (blocks
   // are handed out x first, then y, so every request's heaviest work starts first).  A query
   // tile with split_min or more key tiles takes a whole cluster: rank 0 walks the first half
-  // of the key tiles and rank 1 the rest, and rank 0 fetches rank 1's running maximum, sum and
-  // output rows through distributed shared memory.  The lighter query tiles go two to a cluster,
+  // of the key tiles and rank 1 the rest; each then fetches the other's running maximum and sum
+  // and half of its output columns through distributed shared memory and finishes that half.  The lighter query tiles go two to a cluster,
   // the heaviest of them with the lightest (an idle partner would hold its place on the SM
   // until the cluster ends).  Without the split the launch lasts as long as its longest tile
   // (the last query tile of the longest request) while most SMs have long finished.
@@ -193,9 +193,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   if (a.window > 0 && pos0 - a.window + 1 > 0) first_key = pos0 - a.window + 1;
   int kt_first;
   const int n_all = key_tiles(qt, kt_first);
-  // rank 1's half ends with the masked tile at the diagonal, which costs about two plain ones,
-  // and it has its rows to send: rank 0 takes one tile more than half
-  const int n_mine0 = split ? (n_all + 2) / 2 : n_all;
+  // rank 1's half ends with the masked tile at the diagonal, which costs more than a plain one:
+  // of an odd number rank 0 takes the larger half
+  const int n_mine0 = split ? (n_all + 1) / 2 : n_all;
   const int kt0 = (!split || rank == 0) ? kt_first : kt_first + n_mine0;
   const int n_tiles = (!split || rank == 0) ? n_mine0 : n_all - n_mine0;
   const int hk = h / (a.H / a.Hkv);
@@ -517,54 +517,64 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     }
     TL(7);
+    // A shared tile is finished by both blocks, each for half of the head's columns: a block
+    // leaves its (maximum, sum) and the other half's output registers in its own K/V stages
+    // (free once its last MMA is done, which its threads have waited for), tells its partner and
+    // fetches the partner's through distributed shared memory.  The two blocks' threads hold the
+    // same rows and columns in the same registers, so thread t's registers cross as 16-byte
+    // pieces [piece][t]: piece 0 = (max, sum) of its two rows, then output registers by fours.
+    constexpr int HP = D / 16;                       // pieces (8-column blocks) of half a head
+    const int keep0 = (split && rank == 1) ? HP : 0; // first 8-column block this block finishes
+    const int n_keep = split ? HP : D / 8;
     if (split) {
-      // Rank 1 leaves its rows in its own K/V stages (free once its last MMA is done, which its
-      // threads have waited for) and rank 0 fetches them through distributed shared memory when
-      // it is done with its own tiles.  The two blocks' threads hold the same rows and columns in
-      // the same registers, so thread t's registers cross as 16-byte pieces [piece][t]: piece 0 =
-      // (max, sum) of its two rows, then the output registers four at a time.
       float4* land = reinterpret_cast<float4*>(sK);
-      if (rank == 1) {
-        land[st] = make_float4(m[0], ok ? l[0] : 0.0f, m[1], ok ? l[1] : 0.0f);
+      const int give0 = HP - keep0;
+      land[st] = make_float4(m[0], ok ? l[0] : 0.0f, m[1], ok ? l[1] : 0.0f);
 #pragma unroll
-        for (int c = 0; c < D / 8; c++)
-          land[(c + 1) * SOFTMAX_THREADS + st] = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
-        mbar_arrive_peer(map_to_peer(&ctl.land_full, 0u));
-        mbar_wait_cluster(&ctl.land_free, 0, abort_flag);     // stay until rank 0 has read them
-        ok = false;                                           // rank 0 stores the rows
-      } else {
-        TL(8);
-        const bool there = mbar_wait_cluster(&ctl.land_full, 0, abort_flag);
-        TL(9);
-        if (there) {
-          const uint32_t src = map_to_peer(land, 1u) + (uint32_t)st * 16u;
-          const uint4 ml = ld_peer_v4(src);
-          uint4 v[D / 8];
-#pragma unroll
-          for (int c = 0; c < D / 8; c++) v[c] = ld_peer_v4(src + (uint32_t)(c + 1) * (SOFTMAX_THREADS * 16u));
-          const float m2[2] = {__uint_as_float(ml.x), __uint_as_float(ml.z)};
-          const float l2[2] = {__uint_as_float(ml.y), __uint_as_float(ml.w)};
-          float a1[2], a2[2];
-#pragma unroll
-          for (int x = 0; x < 2; x++) {
-            const float mm = fmaxf(m[x], m2[x]);
-            const float m_use = mm == -INFINITY ? 0.0f : mm;
-            a1[x] = exp2f((m[x] - m_use) * a.scale_log2);
-            a2[x] = exp2f((m2[x] - m_use) * a.scale_log2);
-            l[x] = l[x] * a1[x] + l2[x] * a2[x];
-          }
-#pragma unroll
-          for (int c = 0; c < D / 8; c++) {
-            o[4 * c] = o[4 * c] * a1[0] + __uint_as_float(v[c].x) * a2[0];
-            o[4 * c + 1] = o[4 * c + 1] * a1[0] + __uint_as_float(v[c].y) * a2[0];
-            o[4 * c + 2] = o[4 * c + 2] * a1[1] + __uint_as_float(v[c].z) * a2[1];
-            o[4 * c + 3] = o[4 * c + 3] * a1[1] + __uint_as_float(v[c].w) * a2[1];
-          }
-        } else {
-          ok = false;
-        }
-        mbar_arrive_peer(map_to_peer(&ctl.land_free, 1u));    // read (or given up): rank 1 may go
+      for (int c = 0; c < HP; c++) {
+        // (constant register indices: both halves are written out, one is stored)
+        const float4 lo4 = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+        const float4 hi4 = make_float4(o[4 * (HP + c)], o[4 * (HP + c) + 1], o[4 * (HP + c) + 2], o[4 * (HP + c) + 3]);
+        land[(c + 1) * SOFTMAX_THREADS + st] = give0 == 0 ? lo4 : hi4;
       }
+      mbar_arrive_peer(map_to_peer(&ctl.land_full, (uint32_t)(rank ^ 1)));
+      TL(8);
+      const bool there = mbar_wait_cluster(&ctl.land_full, 0, abort_flag);
+      TL(9);
+      if (there) {
+        const uint32_t src = map_to_peer(land, (uint32_t)(rank ^ 1)) + (uint32_t)st * 16u;
+        const uint4 ml = ld_peer_v4(src);
+        uint4 v[HP];
+#pragma unroll
+        for (int c = 0; c < HP; c++) v[c] = ld_peer_v4(src + (uint32_t)(c + 1) * (SOFTMAX_THREADS * 16u));
+        const float m2[2] = {__uint_as_float(ml.x), __uint_as_float(ml.z)};
+        const float l2[2] = {__uint_as_float(ml.y), __uint_as_float(ml.w)};
+        float a1[2], a2[2];
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+          const float mm = fmaxf(m[x], m2[x]);
+          const float m_use = mm == -INFINITY ? 0.0f : mm;
+          a1[x] = exp2f((m[x] - m_use) * a.scale_log2);
+          a2[x] = exp2f((m2[x] - m_use) * a.scale_log2);
+          l[x] = l[x] * a1[x] + l2[x] * a2[x];
+        }
+#pragma unroll
+        for (int c = 0; c < HP; c++) {
+          // the kept half, again with constant register indices
+#pragma unroll
+          for (int half = 0; half < 2; half++) {
+            if (half * HP != keep0) continue;
+            const int b = 4 * (half * HP + c);
+            o[b] = o[b] * a1[0] + __uint_as_float(v[c].x) * a2[0];
+            o[b + 1] = o[b + 1] * a1[0] + __uint_as_float(v[c].y) * a2[0];
+            o[b + 2] = o[b + 2] * a1[1] + __uint_as_float(v[c].z) * a2[1];
+            o[b + 3] = o[b + 3] * a1[1] + __uint_as_float(v[c].w) * a2[1];
+          }
+        }
+      } else {
+        ok = false;
+      }
+      mbar_arrive_peer(map_to_peer(&ctl.land_free, (uint32_t)(rank ^ 1)));    // read (or given up)
     }
     TL(10);
 #pragma unroll
@@ -580,12 +590,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         __nv_bfloat16* op = a.out + (size_t)(t0 + qt * BQ + row_r[x]) * a.o_stride + (size_t)h * D + 2 * q4;
 #pragma unroll
         for (int i = 0; i < D / 8; i++) {          // the row's i-th block of 8 columns
+          if (i < keep0 || i >= keep0 + n_keep) continue;
           __nv_bfloat162 hh = __floats2bfloat162_rn(o[4 * i + 2 * x] * inv, o[4 * i + 2 * x + 1] * inv);
           *reinterpret_cast<__nv_bfloat162*>(op + 8 * i) = hh;
         }
       }
     }
     TL(11);
+    // the partner reads this block's shared memory: stay until it has
+    if (split) mbar_wait_cluster(&ctl.land_free, 0, abort_flag);
   }
 
   tc_fence_before_sync();

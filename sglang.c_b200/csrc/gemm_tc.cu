@@ -838,10 +838,16 @@ static int g_stream_kernel = 1;
 SGLC_API void sglc_gemm_tc_set_stream_kernel(int on) { g_stream_kernel = on; }
 
 // Orientation, tile width and K split for a problem size.
+// From 65 tokens on, a product over a short K goes to the many-token kernel although its one row
+// of tiles is half empty: the few-token orientation would split K over a cluster and pass
+// 128 x 128 partial sums, 64 KB a block, through distributed shared memory (measured at 96 and
+// 128 tokens: a decode step 15-17 % shorter; at 64 tokens and fewer the split wins or ties).
+static int g_direct_min_m = 65, g_direct_max_kb = 32;
+SGLC_API void sglc_gemm_tc_set_direct(int min_m, int max_kb) { g_direct_min_m = min_m; g_direct_max_kb = max_kb; }
 static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split,
                  int* tiles_p, int* tiles_q) {
   int kb_total = (K + BK - 1) / BK;
-  if (M <= 128) {
+  if (M <= 128 && !(M >= g_direct_min_m && kb_total <= g_direct_max_kb)) {
     *swap = 1;
     *bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     *tiles_p = (N + BM - 1) / BM;

@@ -15,10 +15,12 @@ step of 2,048 prompt tokens (2 x 1,024); `roofline` is the decode step's bytes
 measured copy bandwidth; `points` has decode at batch 1 and 64.
 """
 import argparse
+import atexit
 import json
 import os
 import statistics
 import subprocess
+import shutil
 import sys
 import tempfile
 import threading
@@ -309,6 +311,7 @@ def main():
     n_layer = args.layers or base["n_layer"]
     cfg_d = dict(base, n_layer=n_layer)
     tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+    atexit.register(shutil.rmtree, tmp, True)       # the random model is up to 3 GB
     model_dir = make_model(tmp, base, n_layer)
     if args.workload == "mixed":
         r = run_mixed(model_dir, cfg_d)

@@ -2,8 +2,10 @@
 (apps/sglc.c:264-312,486-514): same option names and defaults where it has
 them.  There is no tokenizer here, so the prompt is given as token ids."""
 import argparse
+import atexit
 import json
 import os
+import shutil
 import sys
 import tempfile
 import time
@@ -62,7 +64,10 @@ def main(argv=None):
             d = json.load(f)
         arch = resolve_architecture(d)
         cfg = arch.config_class.from_dict(d)
-        model_dir = args.save_model or tempfile.mkdtemp(prefix="sglc_random_")
+        model_dir = args.save_model
+        if not model_dir:
+            model_dir = tempfile.mkdtemp(prefix="sglc_random_")
+            atexit.register(shutil.rmtree, model_dir, True)
         write_random_model(model_dir, arch, cfg, args.random_weights, scheme=args.init)
         print(f"[sglc] wrote random weights (seed {args.random_weights}) to {model_dir}", file=sys.stderr)
     if not model_dir:

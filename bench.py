@@ -18,9 +18,9 @@ import argparse
 import atexit
 import json
 import os
+import shutil
 import statistics
 import subprocess
-import shutil
 import sys
 import tempfile
 import threading

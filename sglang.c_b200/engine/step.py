@@ -42,6 +42,7 @@ class Workspace:
         self.off = 0
         self.peak = 0
         self._views = {}      # (start, dtype, shape) -> view: every layer asks for the same ones
+        self._cols = {}       # (id of a view, first column, end) -> its column range
 
     def reset(self):
         self.off = 0
@@ -69,8 +70,19 @@ class Workspace:
         view = self.buf[start:start + nbytes].view(dtype).view(*shape)
         if len(self._views) >= 4096:
             self._views.clear()
+            self._cols.clear()
         self._views[key] = (view, self.off)
         return view
+
+    def columns(self, t, first, end):
+        """t[:, first:end] of a view that alloc() gave out, made once (alloc hands the same
+        object out again, so its identity is a key for as long as the view is kept)."""
+        key = (id(t), first, end)
+        hit = self._cols.get(key)
+        if hit is None or hit[0] is not t:
+            hit = (t, t[:, first:end])
+            self._cols[key] = hit
+        return hit[1]
 
 
 class StepContext:
@@ -107,6 +119,9 @@ class StepContext:
 
     def alloc(self, shape, dtype):
         return self.ws.alloc(shape, dtype)
+
+    def columns(self, t, first, end):
+        return self.ws.columns(t, first, end)
 
     def mark(self):
         return self.ws.off

@@ -42,9 +42,9 @@ class CausalAttention(Part):
         T = h.shape[0]
         qkv = ctx.alloc((T, (H + 2 * Hkv) * D), self.rt.act_dtype)
         self.qkv.forward(ctx, h, out=qkv)
-        q = qkv[:, :H * D]
-        k = qkv[:, H * D:(H + Hkv) * D]
-        v = qkv[:, (H + Hkv) * D:]
+        q = ctx.columns(qkv, 0, H * D)
+        k = ctx.columns(qkv, H * D, (H + Hkv) * D)
+        v = ctx.columns(qkv, (H + Hkv) * D, (H + 2 * Hkv) * D)
         if position is not None:
             position.rotate(ctx, q, k)
         grp = ctx.group(cache.group)

@@ -86,22 +86,6 @@ __device__ __forceinline__ void tl_mark(const GemmArgs& a, int slot) {
 #define TL(slot)
 #endif
 
-// The tanh form of GELU as u * sigmoid(2k(u + 0.044715 u^3)), which is the same function
-// (0.5 (1 + tanh x) = sigmoid 2x) without the cancellation of 1 + tanh for negative inputs, by
-// one exponential and one division of the fast kind (2 ulp each): a few instructions where
-// tanhf takes twenty, and an epilogue of 128 x 128 values a tile is made of them.
-__device__ __forceinline__ float gelu_tanh_sigmoid(float u) {
-  const float z = 1.5957691216057308f * (u + 0.044715f * u * u * u);
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * 1.4426950408889634f));
-  return __fdividef(u, 1.0f + e);
-}
-__device__ __forceinline__ float act_tc(float u, int act) {
-  if (act == SGLC_ACT_GELU_TANH) return gelu_tanh_sigmoid(u);
-  if (act == SGLC_ACT_GELU_ERF) return gelu_erf_f32(u);
-  return u;
-}
-
 struct SharedCtl {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];

@@ -257,6 +257,39 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None, supported=False):
     _check(lib, code, f"gemm_tc M={M} N={N} K={K}")
 
 
+FEW_MAX_TOKENS = 2           # products of so few tokens go to gemm_few ...
+FEW_MAX_WEIGHT = 3 << 20     # ... if the weight matrix has no more elements than this
+
+
+def gemm_few(a, w, bias, out=None, residual=None, act=None):
+    """The same product as gemm_tc for up to 8 tokens: 8 output features a block over the whole
+    of K, operands from global memory straight into the registers of the warp-level
+    tensor-core instruction, no block waiting for another."""
+    _need_cuda(a, w, bias, out, residual)
+    M, K = a.shape
+    N = w.shape[0]
+    lib = build.load("gemm_few")
+    if w.shape[1] != K or not gemm_tc_supported(a, w) or not lib.sglc_gemm_few_supports(M, N, K, a.stride(0)):
+        raise KernelError(f"gemm_few: a {tuple(a.shape)} stride {a.stride()} / w {tuple(w.shape)}: up to 8 "
+                          "tokens, K and the row stride multiples of 8, 16-byte aligned operands")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("gemm_few: bias must be a float32 vector of N")
+    dst = residual if residual is not None else out
+    if dst is None or dst.shape[0] < M or dst.shape[1] != N or dst.stride(1) != 1:
+        raise KernelError("gemm_few: output does not match [M,N]")
+    if residual is not None:
+        if residual.dtype != torch.float32:
+            raise KernelError("gemm_few: the residual stream is float32")
+        if act not in (None, "none"):
+            raise KernelError("gemm_few: no activation when adding into the residual stream")
+    elif dst.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("gemm_few: output must be float32 or bfloat16")
+    code = lib.sglc_gemm_few(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), M, N, K,
+                             a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
+                             ACT[act], _stream())
+    _check(lib, code, f"gemm_few M={M} N={N} K={K}")
+
+
 # ---------------------------------------------------------------------------
 STREAM_MIN_ITEMS = 160     # (token, head) items from which the streaming decode kernel is used
 USE_TMA_DECODE = True      # tests switch it off to reach the register-staged kernel at head size 64/128

@@ -26,6 +26,7 @@ class Linear:
     def from_refs(cls, store, weight_ref, bias_ref, layout):
         w = store.matrix(weight_ref, transpose=(layout == "conv1d"))
         b = store.vector(bias_ref) if bias_ref is not None else None
+        store.rt.note_layer_matrix(w)
         return cls(w, b)
 
     def forward(self, ctx, a, out=None, act=None, residual=None):

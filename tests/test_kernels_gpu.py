@@ -350,6 +350,57 @@ def test_gemm_tc(M, N, K):
     assert int(ops.tc_error_flag(a.device).item()) == 0
 
 
+GEMM_FEW_SHAPES = [(1, 8, 8), (3, 13, 40), (8, 100, 72), (1, 768, 768), (2, 30, 1600), (5, 2304, 768),
+                   (2, 768, 3072), (2, 65, 3080), (4, 17, 6400), (7, 1031, 96)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_FEW_SHAPES)
+def test_gemm_few(M, N, K):
+    """The few-token product (weights and tokens from global memory into the registers of the
+    warp-level tensor-core instruction) against a float64 product of the same operands."""
+    ops = _ops()
+    a, w, bias = _rand(M, K, dtype=torch.bfloat16, seed=30), _rand(N, K, dtype=torch.bfloat16, seed=31, scale=0.1), _rand(N, seed=32)
+    ref = a.double() @ w.double().t() + bias.double()
+    tol32 = 2e-5 * math.sqrt(K) + 1e-5
+    out = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_few(a, w, bias, out=out)
+    assert float((out.double() - ref).abs().max()) < tol32
+    outb = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_few(a, w, bias, out=outb, act="gelu_tanh")
+    want = torch.nn.functional.gelu(ref, approximate="tanh")
+    assert float((outb.double() - want).abs().max()) < tol32 + 8e-3 * float(want.abs().max())
+    ops.gemm_few(a, w, None, out=outb, act="gelu_erf")
+    want = torch.nn.functional.gelu(ref - bias.double())
+    assert float((outb.double() - want).abs().max()) < tol32 + 8e-3 * float(want.abs().max())
+    res = _rand(M, N, seed=33)
+    res0 = res.clone()
+    ops.gemm_few(a, w, bias, residual=res)
+    assert float((res.double() - (res0.double() + ref)).abs().max()) < tol32
+    out2 = torch.empty(M, N, device=DEV)
+    ops.gemm_few(a, w, bias, out=out2)
+    assert torch.equal(out, out2)
+    # strided input rows and a wider output buffer; rows of the buffer beyond M stay as they are
+    wide = _rand(M, K + 16, dtype=torch.bfloat16, seed=34)
+    big = torch.zeros(M + 2, N + 5, device=DEV)
+    ops.gemm_few(wide[:, 8:8 + K], w, None, out=big[:, :N])
+    assert float((big[:M, :N].double() - wide[:, 8:8 + K].double() @ w.double().t()).abs().max()) < tol32
+    assert float(big[:, N:].abs().max()) == 0.0 and float(big[M:].abs().max()) == 0.0
+    # the same product through the tcgen05 kernel agrees to rounding of the sum's order
+    out3 = torch.empty(M, N, device=DEV)
+    ops.gemm_tc(a, w, bias, out=out3)
+    assert float((out3 - out).abs().max()) < tol32
+
+
+def test_gemm_few_refuses_what_it_cannot_take():
+    ops = _ops()
+    w = _rand(6, 64, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_few(_rand(9, 64, dtype=torch.bfloat16), w, None, out=torch.empty(9, 6, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_few(_rand(4, 100, dtype=torch.bfloat16), _rand(6, 100, dtype=torch.bfloat16), None,
+                     out=torch.empty(4, 6, device=DEV))
+
+
 def test_gemm_tc_refuses_rows_that_tma_cannot_load():
     ops = _ops()
     a, w = _rand(4, 100, dtype=torch.bfloat16), _rand(6, 100, dtype=torch.bfloat16)

@@ -98,14 +98,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_bytes_flops(cfg, batch, context, elem=2):
+def model_bytes_flops(cfg, batch, context, elem=2, kv_elem=None):
     """Bytes a decode step has to read (every weight it uses once, the cache of
     the live requests) and the flops of a prefill of T tokens as n prompts."""
     E, I, L, V, H = cfg["n_embd"], cfg["n_inner"], cfg["n_layer"], cfg["vocab_size"], cfg["n_head"]
     mats = L * (E * 3 * E + E * E + E * I + I * E)
     vecs = L * (3 * E + E + I + E + 4 * E) + 2 * E
     weights = (mats + V * E) * elem + vecs * 4 + batch * E * elem      # + the position rows used
-    kv = batch * context * L * 2 * E * elem
+    kv = batch * context * L * 2 * E * (kv_elem or elem)
     return weights + kv
 
 
@@ -278,6 +278,59 @@ def run_mixed(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
             "n_preempt": st.n_preempt, "graph_replays": s.engine.graph_replays}
 
 
+def reference_main(args):
+    """The reference arm: the unmodified reference's own GPU path on the same workload
+    (baseline/reference_arm.py compiles it into baseline/_ref and drives its C API)."""
+    if args.gpus != 1:
+        print(f"bench.py: the reference runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm
+    try:
+        reference_arm.build()
+    except (reference_arm.Unavailable, subprocess.CalledProcessError, OSError) as e:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"the reference could not be compiled here: {str(e).splitlines()[0][:200]}"}))
+        return 0
+    pk = peaks()
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+    cfg = SMALL
+    try:
+        r = reference_arm.run(cfg, BATCH, CONTEXT, steps, warmup, PREFILL_TOKENS, pk,
+                              prefill_flops(cfg, 2, PREFILL_TOKENS // 2),
+                              lambda elem: model_bytes_flops(cfg, BATCH, CONTEXT + steps // 2, elem, kv_elem=4),
+                              clock_sampler=ClockSampler())
+    except reference_arm.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)[:200]}))
+        return 0
+    out = {
+        "impl": "reference",
+        "metric": "decode tok/s at batch 8, context 512 (GPT-2 small layer sizes, random weights)",
+        "value": r["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp32", "data": "synthetic: seeded random weights and uniform random token ids",
+        "config": {"model": "gpt2-small layer sizes, random weights", "n_layer": cfg["n_layer"],
+                   "n_layer_full": cfg["n_layer"], "n_embd": cfg["n_embd"], "n_head": cfg["n_head"],
+                   "n_inner": cfg["n_inner"], "vocab_size": cfg["vocab_size"], "n_positions": cfg["n_positions"],
+                   "global_batch": BATCH, "seq_len": CONTEXT, "parallelism": "none (1 GPU)",
+                   "prefill_tokens": PREFILL_TOKENS, "prefill_shape": "2 prompts x 1024, one forward each",
+                   "decode": "one single-token forward per request per step (its GPT-2 decode)",
+                   "same_config": "layer sizes and workload equal; its default is float32 weights and cache, "
+                                  "fp16_weights is its SGL_CUDA_FP16=1 switch",
+                   "timing": "wall clock around its API calls (each ends in its own stream sync)",
+                   "peaks": pk["source"]},
+        # its API is host tokens in, host logits out, host sampling: the end-to-end number is the number
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 4 * BATCH,
+                "d2h_bytes_per_step": 4 * cfg["vocab_size"] * BATCH},
+        "prefill": dict(r["prefill"], of=pk["source"]),
+        "roofline": dict(r["roofline"], of=pk["source"]),
+        "points": r["points"], "fp16_weights": r["fp16_weights"], "clocks": r["clocks"],
+    }
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -293,10 +346,7 @@ def main():
                          "tokens and 128 generated tokens each through the scheduler")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "integemjack/sglang.c is a C/CMake project without a Python package: "
-                          "pip install of its source tree finds no setup.py or pyproject.toml"}))
-        return 0
+        return reference_main(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

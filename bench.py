@@ -6,13 +6,16 @@ The default run has the layer sizes of GPT-2 small (n_layer 12, n_embd 768,
 n_head 12, n_inner 3072, vocab 50257, positions 1024) with random weights in
 bfloat16, a batch of 8 requests decoding at a context of 512 tokens, pages of
 16.  A "step" is one decode step of the whole batch.  One JSON line is printed:
-`value` is decoded tokens a second with the steps timed on the device (one pair
-of CUDA events around all K steps, each step's sampled ids feeding the next; a
-step reads more than L2 holds, so nothing is flushed); `e2e` is the same through
-the Python entry point (scheduler, host token ids in and out); `prefill` is one
-step of 2,048 prompt tokens (2 x 1,024); `roofline` is the decode step's bytes
-(every weight once, the cache of the live requests) over its time, against the
-measured copy bandwidth; `points` has decode at batch 1 and 64.
+`value` is decoded tokens a second with the steps timed on the device (CUDA events
+around chunks of K steps, each step's sampled ids feeding the next; the median of
+five regions of at least 50 ms each; a step reads more than L2 holds, so nothing
+is flushed); `e2e` is the same through the Python entry point (scheduler, host
+token ids in and out); `prefill` is one step of 2,048 prompt tokens (2 x 1,024);
+`roofline` is the decode step's bytes (every weight once, the cache of the live
+requests) over its time, against the measured copy bandwidth; `points` has decode
+at batch 1 and 64 and the true 32-bit path; `kernels` says where a decode and a
+prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
+sizes and the mixed workload to `points`.
 """
 import argparse
 import atexit
@@ -130,23 +133,29 @@ def make_model(tmp, cfg_d, n_layer=None):
                               store_dtype="bfloat16")
 
 
-def time_decode(eng, batch, context, steps, warmup, flush):
-    """Device time of `steps` decode steps in a row of `batch` requests that hold `context`
-    tokens each, one pair of CUDA events around all of them; returns (ms per step list,
-    launches in the timed region).  The steps are real decoding (each step's sampled ids are the
-    next step's input) and are queued one ahead, as the scheduler does.  L2 is not flushed in
-    between: a step reads more than L2 holds (weights and cache of the live requests)."""
+REGION_MS = 50.0       # a timed region lasts at least this long
+N_REGIONS = 5          # a point is the median of this many regions
+
+
+def time_decode(eng, batch, context, steps, warmup):
+    """Decode steps of `batch` requests that hold `context` tokens each, timed on the device.
+    A chunk is `steps` steps in a row between one pair of CUDA events, real decoding (each step's
+    sampled ids are the next step's input, on the device) queued one ahead as the scheduler does;
+    after a chunk the requests are rewound to `context` (host bookkeeping only, untimed) and one
+    untimed step re-primes the repeat path.  A region is as many chunks as it takes to reach
+    REGION_MS of device time; the result is the median region's ms per step over N_REGIONS, with
+    the launches of one chunk.  L2 is not flushed: a step reads more than L2 holds (every weight
+    and the cache of the live requests)."""
     import numpy as np
     import torch
     from sglang_c_b200.csrc import ops
     from sglang_c_b200.engine import StepEntry
-    from sglang_c_b200.sampling import Sampler, SamplingParams
+    from sglang_c_b200.sampling import Sampler
     V = eng.plan.vocab_size
     rng = np.random.default_rng(batch)
     reqs = [f"b{batch}_{i}" for i in range(batch)]
     for r in reqs:
         eng.add_request(r)
-    # fill the context in portions
     todo = {r: [int(t) for t in rng.integers(0, V, size=context)] for r in reqs}
     done = 0
     while done < context:
@@ -155,11 +164,8 @@ def time_decode(eng, batch, context, steps, warmup, flush):
         done += n
     sampler = Sampler(eng.rt.device, max(batch, 1))
     toks = [int(t) for t in rng.integers(0, V, size=batch)]
-    launches = 0
 
     def one_step(first):
-        # the step's ids come from the sampler's output of the step before, on the device; its
-        # host side (cache growth, packed arrays) is prepared while the device runs that step
         if first or not eng.prepare_repeat(reqs):
             logits = eng.step([StepEntry(r, [t], [0]) for r, t in zip(reqs, toks)])
         else:
@@ -167,80 +173,171 @@ def time_decode(eng, batch, context, steps, warmup, flush):
         ops.sample(logits, sampler.d_params[:batch], sampler.d_hist_tok, sampler.d_hist_cnt,
                    sampler.d_out[:batch])
 
-    one_step(True)
-    for it in range(warmup):
-        one_step(False)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    l0 = ops.LAUNCHES
-    e0.record()
-    for it in range(steps):
-        one_step(False)
-    e1.record()
-    torch.cuda.synchronize()
-    launches = ops.LAUNCHES - l0
-    times = [e0.elapsed_time(e1) / steps] * steps
+    def chunk(n):
+        for r in reqs:
+            eng.truncate(r, context)
+        one_step(True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = ops.LAUNCHES
+        e0.record()
+        for _ in range(n):
+            one_step(False)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1), ops.LAUNCHES - l0
+
+    chunk(max(warmup, 3))
+    regions, launches = [], 0
+    for _ in range(N_REGIONS):
+        ms, n = 0.0, 0
+        while ms < REGION_MS:
+            t, launches = chunk(steps)
+            ms += t
+            n += steps
+        regions.append(ms / n)
     for r in reqs:
         eng.end_request(r)
-    return times, launches
+    return statistics.median(regions), launches, regions
 
 
-def time_prefill(eng, n_prompts, prompt_len, reps, warmup, flush):
+def time_prefill(eng, n_prompts, prompt_len, warmup):
+    """One step of n_prompts whole prompts; the median of N_REGIONS regions of at least REGION_MS
+    of device time each (a region is steps in a row, each on fresh requests)."""
     import numpy as np
     import torch
     from sglang_c_b200.engine import StepEntry
     V = eng.plan.vocab_size
     rng = np.random.default_rng(99)
-    times = []
-    for it in range(warmup + reps):
-        reqs = [f"p{it}_{i}" for i in range(n_prompts)]
+    it = [0]
+
+    def once():
+        it[0] += 1
+        reqs = [f"p{it[0]}_{i}" for i in range(n_prompts)]
         for r in reqs:
             eng.add_request(r)
         entries = [StepEntry(r, [int(t) for t in rng.integers(0, V, size=prompt_len)], [prompt_len - 1])
                    for r in reqs]
-        if flush is not None:
-            flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         eng.step(entries)
         e1.record()
         torch.cuda.synchronize()
-        if it >= warmup:
-            times.append(e0.elapsed_time(e1))
         for r in reqs:
             eng.end_request(r)
-    return times
+        return e0.elapsed_time(e1)
+
+    for _ in range(max(warmup, 3)):
+        once()
+    regions = []
+    for _ in range(N_REGIONS):
+        ms, n = 0.0, 0
+        while ms < REGION_MS:
+            ms += once()
+            n += 1
+        regions.append(ms / n)
+    return statistics.median(regions)
 
 
-def time_e2e(model_dir, batch, context, steps, warmup):
-    """The same decode through the Python entry point: token ids on the host in,
-    token ids on the host out, every step."""
+def kernel_table(eng, batch, context, prompt_len):
+    """Where a step's time goes, kernel by kernel: a decode step of `batch` requests at `context`
+    and a prefill step of two prompts, each run once operation by operation (no graph) with a pair
+    of CUDA events around every launch, queued behind a few milliseconds of device sleep so that
+    the host's launch cost does not fall between the events; the cost of an empty pair of events
+    is measured in the same queue and taken off every launch.  Kernels are kept from overlapping
+    by the events, so the figures are each kernel's own time, not its share of an overlapped step."""
+    import numpy as np
+    import torch
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.engine import StepEntry
+    V = eng.plan.vocab_size
+    rng = np.random.default_rng(7)
+    graphs, eng.use_graphs = eng.use_graphs, False
+    out = {}
+    try:
+        reqs = [f"k{i}" for i in range(batch)]
+        for r in reqs:
+            eng.add_request(r)
+        done = 0
+        while done < context:
+            n = min(eng.max_step_tokens // batch, context - done)
+            eng.step([StepEntry(r, [int(t) for t in rng.integers(0, V, size=n)], []) for r in reqs])
+            done += n
+        for name, make in (("decode", lambda: [StepEntry(r, [1], [0]) for r in reqs]), ("prefill", None)):
+            if make is None:
+                for r in reqs:
+                    eng.end_request(r)
+                reqs = ["kp0", "kp1"]
+                for r in reqs:
+                    eng.add_request(r)
+                make = lambda: [StepEntry(r, [int(t) for t in rng.integers(0, V, size=prompt_len)],
+                                          [prompt_len - 1]) for r in reqs]
+            entries = make()
+            if name == "decode":
+                eng.step(entries)                      # the kernels' first call is not what is timed
+                for r in reqs:
+                    eng.truncate(r, context)
+            torch.cuda.synchronize()
+            torch.cuda._sleep(20_000_000)              # about 10 ms: the step is queued whole behind it
+            empty = []
+            for _ in range(16):                        # what a pair of events costs with nothing between
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                b.record()
+                empty.append((a, b))
+            ops.profile_begin()
+            eng.step(entries)
+            rows = ops.profile_end()
+            pair_us = statistics.median(a.elapsed_time(b) for a, b in empty) * 1e3
+            out[name] = {k: {"launches": n, "us": round(max(us - n * pair_us, 0.0), 1)}
+                         for k, (n, us) in sorted(rows.items())}
+            out[name]["event_pair_us"] = round(pair_us, 2)
+        for r in reqs:
+            eng.end_request(r)
+    finally:
+        eng.use_graphs = graphs
+    return out
+
+
+def time_e2e(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
+    """The same decode through the Python entry point: token ids on the host in, token ids on
+    the host out, every step; wall clock.  A region is fresh requests with prompts of `context`
+    tokens, run until all decode, `warmup` steps, then enough steps for REGION_MS (at least
+    `steps`; the context grows by that many); the median of N_REGIONS regions."""
     import numpy as np
     import torch
     from sglang_c_b200.engine import sched_new
     from sglang_c_b200.sampling import SamplingParams
-    s = sched_new(model_dir, seed=0, dtype="bfloat16", page_size=PAGE,
-                  max_tokens=batch * (context + steps + warmup + 64), max_requests=max(batch, 1),
+    n_timed = max(steps, 100)
+    s = sched_new(model_dir, seed=0, dtype=dtype, page_size=PAGE,
+                  max_tokens=batch * (context + n_timed + warmup + 64), max_requests=max(batch, 1),
                   max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
     V = s.engine.plan.vocab_size
     rng = np.random.default_rng(5)
     sp = SamplingParams(temperature=0.0, ignore_eos=True)
-    for _ in range(batch):
-        s.submit_ids([int(t) for t in rng.integers(0, V, size=context)], warmup + steps + 32, sp)
-    while s.waiting or any(r.n_computed < len(r.prompt) for r in s.running):
-        s.step()                                   # prompts done; every request decodes from here
-    for _ in range(warmup):
-        s.step()
-    torch.cuda.synchronize()
-    n0 = s.stats.decode_tokens
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        s.step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    regions = []
+    for _ in range(N_REGIONS):
+        ids = [s.submit_ids([int(t) for t in rng.integers(0, V, size=context)], warmup + n_timed + 32, sp)
+               for _ in range(batch)]
+        while s.waiting or any(r.n_computed < len(r.prompt) for r in s.running):
+            s.step()                               # prompts done; every request decodes from here
+        for _ in range(warmup):
+            s.step()
+        torch.cuda.synchronize()
+        n0 = s.stats.decode_tokens
+        t0 = time.perf_counter()
+        for _ in range(n_timed):
+            s.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        regions.append((s.stats.decode_tokens - n0) / dt)
+        for i in ids:
+            s.abort(i)
+        while s.poll() is not None:
+            pass
     h2d = s.engine.bufs.total * 4 + batch * 40      # the packed step data and the sampling records
     d2h = batch * 4                                 # the sampled token ids
-    return (s.stats.decode_tokens - n0) / dt, h2d, d2h
+    return statistics.median(regions), h2d, d2h
 
 
 def run_mixed(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
@@ -331,19 +428,66 @@ def reference_main(args):
     return 0
 
 
+def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=True, kernels=True):
+    """Every figure of one model size: decode at batch 8 (device-timed and end to end), prefill,
+    the points, the 32-bit path and the kernel table."""
+    import torch
+    from sglang_c_b200.engine import Engine
+    cfg_d = dict(base, n_layer=n_layer)
+    tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+    atexit.register(shutil.rmtree, tmp, True)       # the random model is up to 3 GB
+    model_dir = make_model(tmp, base, n_layer)
+    eng = Engine.from_dir(model_dir, dtype="bfloat16", page_size=PAGE,
+                          max_tokens=64 * (CONTEXT + 256), max_requests=64, max_step_tokens=PREFILL_TOKENS)
+    time_decode(eng, BATCH, 32, 2, 3)               # every path once (compiles on a fresh checkout)
+    r = {}
+    ms, launches, regions = time_decode(eng, BATCH, CONTEXT, steps, warmup)
+    r.update(ms=ms, launches=launches, regions=regions, value=BATCH / (ms / 1e3))
+    r["bytes"] = model_bytes_flops(cfg_d, BATCH, CONTEXT + steps // 2)
+    pms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3)
+    pflops = prefill_flops(cfg_d, 2, PREFILL_TOKENS // 2)
+    r["prefill"] = {"value": PREFILL_TOKENS / (pms / 1e3), "tokens": PREFILL_TOKENS, "ms": pms,
+                    "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"]}
+    r["points"] = {}
+    for b in points:
+        t, _, _ = time_decode(eng, b, CONTEXT, steps, warmup)
+        r["points"][f"decode_b{b}"] = b / (t / 1e3)
+        nb = model_bytes_flops(cfg_d, b, CONTEXT + steps // 2)
+        r["points"][f"decode_b{b}_roofline_frac"] = nb / (t / 1e3) / 1e9 / pk["hbm_gbs"]
+    if kernels:
+        r["kernels"] = kernel_table(eng, BATCH, CONTEXT, PREFILL_TOKENS // 2)
+    del eng
+    torch.cuda.empty_cache()
+    r["e2e"] = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
+    if fp32:
+        # the true 32-bit path (plain FFMA products, 32-bit cache): same step function and scheduler
+        eng = Engine.from_dir(model_dir, dtype="float32", page_size=PAGE, max_tokens=BATCH * (CONTEXT + 256) + 4096,
+                              max_requests=BATCH, max_step_tokens=PREFILL_TOKENS)
+        t, _, _ = time_decode(eng, BATCH, CONTEXT, steps, warmup)
+        r["points"]["fp32_decode_b8"] = BATCH / (t / 1e3)
+        pm32 = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3)
+        r["points"]["fp32_prefill_tok_s"] = PREFILL_TOKENS / (pm32 / 1e3)
+        del eng
+        torch.cuda.empty_cache()
+    r["model_dir"] = model_dir
+    return r
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--model", default="small", choices=sorted(MODELS),
-                    help="layer sizes: GPT-2 small (the default and the headline), medium or xl")
+                    help="layer sizes of the headline line: GPT-2 small (the default), medium or xl")
+    ap.add_argument("--full", action="store_true",
+                    help="also medium and XL layer sizes (decode at batch 8, prefill) and the mixed workload "
+                         "(64 requests, prompts of 16..1024 tokens, 128 generated each) under `points`")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
-                    help="decode: the contract's line; mixed: 64 requests with prompts of 16..1024 "
-                         "tokens and 128 generated tokens each through the scheduler")
+                    help="decode: the contract's line; mixed: only the mixed workload through the scheduler")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_main(args)
@@ -353,57 +497,46 @@ def main():
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 
-    import torch
-    from sglang_c_b200.csrc import ops
-    from sglang_c_b200.engine import Engine
     pk = peaks()
     base = MODELS[args.model]
     n_layer = args.layers or base["n_layer"]
-    cfg_d = dict(base, n_layer=n_layer)
-    tmp = tempfile.mkdtemp(prefix="sglc_bench_")
-    atexit.register(shutil.rmtree, tmp, True)       # the random model is up to 3 GB
-    model_dir = make_model(tmp, base, n_layer)
     if args.workload == "mixed":
-        r = run_mixed(model_dir, cfg_d)
+        tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+        atexit.register(shutil.rmtree, tmp, True)
+        r = run_mixed(make_model(tmp, base, n_layer), dict(base, n_layer=n_layer))
         print(json.dumps({"metric": "mixed workload: generated tok/s through the scheduler", "value":
                           r["generated_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
                           "data": "synthetic: seeded random weights and uniform random token ids",
                           "config": {"model": f"gpt2-{args.model} layer sizes, random weights",
                                      "n_layer": n_layer, "n_layer_full": base["n_layer"]}, "mixed": r}))
         return 0
-    eng = Engine.from_dir(model_dir, dtype="bfloat16", page_size=PAGE,
-                          max_tokens=64 * (CONTEXT + 256), max_requests=64, max_step_tokens=PREFILL_TOKENS)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")     # larger than the 126 MB L2
-
-    # warm every path once (compiles on a fresh checkout) before the clocks are watched
-    time_decode(eng, BATCH, 32, 2, 3, None)
     clocks = ClockSampler()
     clocks.start()
-    times, launches = time_decode(eng, BATCH, CONTEXT, steps, warmup, flush)
-    ms = sum(times) / len(times)
-    value = BATCH / (ms / 1e3)
-    nbytes = model_bytes_flops(cfg_d, BATCH, CONTEXT + steps // 2)
-    achieved = nbytes / (ms / 1e3) / 1e9
-
-    pt = time_prefill(eng, 2, PREFILL_TOKENS // 2, 5, 3, flush)
-    pms = sum(pt) / len(pt)
-    pflops = prefill_flops(cfg_d, 2, PREFILL_TOKENS // 2)
-    prefill = {"value": PREFILL_TOKENS / (pms / 1e3), "tokens": PREFILL_TOKENS, "ms": pms,
-               "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"]}
-
-    points = {}
-    if not args.skip_points:
-        for b in (1, 64):
-            t, _ = time_decode(eng, b, CONTEXT, min(steps, 32), warmup, flush)
-            points[f"decode_b{b}"] = b / (sum(t) / len(t) / 1e3)
-    del eng
-    torch.cuda.empty_cache()
-    e2e_value, h2d, d2h = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
+    r = measure_model(args.model, base, n_layer, steps, warmup, pk, points=() if args.skip_points else (1, 64))
+    points = r["points"]
+    if args.full:
+        points["mixed_small_generated_tok_s"] = run_mixed(r["model_dir"], dict(base, n_layer=n_layer))["generated_tok_s"]
+        for other in ("medium", "xl"):
+            if other == args.model:
+                continue
+            o = measure_model(other, MODELS[other], MODELS[other]["n_layer"], steps, warmup, pk, points=(1, 64),
+                              fp32=(other == "xl"), kernels=False)
+            points[f"{other}_decode_b8"] = o["value"]
+            points[f"{other}_decode_b8_roofline_frac"] = o["bytes"] / (o["ms"] / 1e3) / 1e9 / pk["hbm_gbs"]
+            points[f"{other}_prefill_tok_s"] = o["prefill"]["value"]
+            points[f"{other}_prefill_frac"] = o["prefill"]["frac"]
+            for k, v in o["points"].items():
+                points[f"{other}_{k}"] = v
+            if other == "xl":
+                points["mixed_xl_generated_tok_s"] = run_mixed(o["model_dir"], MODELS[other])["generated_tok_s"]
+            shutil.rmtree(os.path.dirname(o["model_dir"]), True)
     clk = clocks.stop()              # sampled over all the timed regions above
-
+    ms, nbytes = r["ms"], r["bytes"]
+    achieved = nbytes / (ms / 1e3) / 1e9
+    e2e_value, h2d, d2h = r["e2e"]
     out = {
         "metric": f"decode tok/s at batch 8, context 512 (GPT-2 {args.model} layer sizes, random weights)",
-        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "value": r["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
         "config": {"model": f"gpt2-{args.model} layer sizes, random weights", "n_layer": n_layer,
@@ -412,14 +545,17 @@ def main():
                    "n_positions": base["n_positions"], "global_batch": BATCH, "seq_len": CONTEXT,
                    "page_size": PAGE, "parallelism": "none (1 GPU)", "prefill_tokens": PREFILL_TOKENS,
                    "prefill_shape": "2 prompts x 1024", "l2": "a step reads more than L2 holds (no flush)",
-                   "timing": "CUDA events around all steps", "cuda_graph": "decode step replays a graph",
+                   "timing": f"CUDA events; median of {N_REGIONS} regions of >= {REGION_MS:.0f} ms, each chunks of "
+                             f"--steps steps", "cuda_graph": "decode step replays a graph",
                    "peaks": pk["source"]},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches,
-        "prefill": prefill,
+        "gpu_launches": r["launches"],
+        "prefill": r["prefill"],
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"], "of": pk["source"], "bytes_per_step": nbytes},
         "points": points,
+        "region_ms_per_step": [round(x, 5) for x in r["regions"]],
+        "kernels": r.get("kernels"),
         "clocks": clk,
     }
     print(json.dumps(out))

@@ -214,6 +214,34 @@ class CacheManager:
                     if g.need.kind == "paged_kv":
                         g.pool.unref(g.tables[req].pop())
 
+    def truncate(self, req, new_len):
+        """Shorten a request to new_len positions: what lies beyond is forgotten and the pages it
+        filled alone go back to the pool.  (What a step that failed half-way had taken is undone
+        with it; a benchmark rewinds a request with it.)  A group with a window cannot go back
+        past pages it has already released."""
+        if req not in self._slot:
+            raise CacheError(f"request {req!r} is not live")
+        if not (0 <= new_len <= self._len[req]):
+            raise CacheError(f"request {req!r} holds {self._len[req]} positions; cannot truncate to {new_len}")
+        keep = self._blocks_for(new_len)
+        for g in self.groups:
+            if g.need.kind != "paged_kv":
+                continue
+            table = g.tables[req]
+            first = self._first_needed_block(g, new_len)
+            if any(table[b] < 0 for b in range(first, min(keep, len(table)))):
+                raise CacheError(f"request {req!r}: a page that {new_len} positions still need was released "
+                                 "when the window passed it")
+        for g in self.groups:
+            if g.need.kind != "paged_kv":
+                continue
+            table = g.tables[req]
+            while len(table) > keep:
+                p = table.pop()
+                if p >= 0:
+                    g.pool.unref(p)
+        self._len[req] = new_len
+
     def free_request(self, req):
         """Return every page and the state slot of a request."""
         if req not in self._slot:

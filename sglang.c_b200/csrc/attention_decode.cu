@@ -348,7 +348,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // the ranges of one (token, head) are the blocks of a cluster.  Blocks 1.. send their
     // (m, l, o) to block 0's shared memory and signal its barrier; block 0 waits for all of
     // them (with a limit) and merges in range order.  Nothing remote is touched by a block
-    // after its signal, and block 0 outlives every store into it.
+    // after its signal, and block 0 outlives every store into it (when its wait runs out,
+    // through the cluster's hardware barrier: see there).
     __syncwarp();
     cluster_wait();                  // pairs with the arrive at the top: block 0's barrier exists
     float* dst_local = recs + (size_t)sp * rec;
@@ -363,6 +364,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       TL(4);
       if (!mbar_wait_cluster(&merge_bar, 0)) {
         if (tid == 0 && err) atomicExch(err, 1);
+        // a peer that has not signalled may still be storing into this block's shared memory:
+        // the cluster's hardware barrier completes when every block of it has arrived or
+        // exited, and the peers exit right after their stores, so this block leaves last
+        cluster_arrive();
+        cluster_wait();
         return;
       }
       TL(5);

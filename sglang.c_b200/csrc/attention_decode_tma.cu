@@ -252,7 +252,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Ar
   }
   // Blocks 1.. send their (m, l, o) to block 0's shared memory and signal its barrier; block 0
   // waits for all of them (with a limit) and merges in range order.  Nothing remote is touched by
-  // a block after its signal, and block 0 outlives every store into it.
+  // a block after its signal, and block 0 outlives every store into it (when its wait runs out,
+  // through the cluster's hardware barrier: see there).
   constexpr int rec = D + 2;
   __syncwarp();
   cluster_wait();                    // pairs with the arrive at the top: block 0's barrier exists
@@ -289,6 +290,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const Ar
     volatile int* af = &s_abort;
     if (!mbar_wait_cluster(&merge_bar, 0, af) || !ok) {
       if (tid == 0 && a.err) atomicExch(a.err, 1);
+      // a peer that has not signalled may still be storing into this block's shared memory: the
+      // cluster's hardware barrier completes when every block of it has arrived or exited, and
+      // the peers exit right after their stores, so this block leaves after the last of them
+      cluster_arrive();
+      cluster_wait();
       return;
     }
   }

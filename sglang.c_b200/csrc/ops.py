@@ -28,10 +28,42 @@ def _ptr(t):
 _PINNED_STREAM = None
 
 
+# Set by profile_begin(): a list of (label, start event, end event), one per launch.  Every
+# binding below evaluates _stream() just before its launch and _check() just after, so the two
+# bracket the kernel.
+_PROFILE = None
+_PROFILE_START = None
+
+
 def _stream():
+    global _PROFILE_START
+    if _PROFILE is not None:
+        _PROFILE_START = torch.cuda.Event(enable_timing=True)
+        _PROFILE_START.record()
     if _PINNED_STREAM is not None:
         return _PINNED_STREAM
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def profile_begin():
+    """From here on every kernel launch of this package is bracketed by a pair of CUDA events
+    (which also keeps a kernel from starting under the one ahead: the times are the kernels'
+    own, not their share of an overlapped step).  Queue the work behind something long, so that
+    the host's launch cost does not show between the events."""
+    global _PROFILE
+    _PROFILE = []
+
+
+def profile_end():
+    """{kernel label: (launches, microseconds)} since profile_begin(); synchronises."""
+    global _PROFILE
+    rows, _PROFILE = _PROFILE, None
+    torch.cuda.synchronize()
+    out = {}
+    for label, e0, e1 in rows or []:
+        n, us = out.get(label, (0, 0.0))
+        out[label] = (n + 1, us + e0.elapsed_time(e1) * 1e3)
+    return out
 
 
 class pinned_stream:
@@ -65,6 +97,10 @@ def _need_cuda(*tensors):
 def _check(lib, code, what, n_kernels=1):
     global LAUNCHES
     LAUNCHES += n_kernels
+    if _PROFILE is not None and _PROFILE_START is not None:
+        end = torch.cuda.Event(enable_timing=True)
+        end.record()
+        _PROFILE.append((what.split(" ")[0], _PROFILE_START, end))
     if code != 0:
         msg = lib.sglc_error_string(code).decode()
         raise KernelError(f"{what}: {msg} (code {code})")
@@ -216,6 +252,20 @@ def _tc_buffers(device):
 
 def tc_error_flag(device):
     return _tc_buffers(device)[2]
+
+
+def wait_probe(device, polls=300, peer_cycles=200000):
+    """Makes a bounded wait run out, on purpose and harmlessly: two tiny kernels (csrc/wait_probe.cu)
+    wait, with a limit of `polls`, on barriers that nobody arrives on, give up, tear down as the
+    tensor-core kernels do and set the error word those kernels share.  Returns the kernels' trace
+    [waiter, its block's other warps, cluster waiter, peer left, waiter left] (2 = ran out,
+    1 = happened); the error word is left set for the caller to find."""
+    lib = build.load("wait_probe")
+    err = _tc_buffers(torch.device(device))[2]
+    trace = torch.zeros(5, dtype=torch.int32, device=device)
+    code = lib.sglc_wait_probe(_ptr(err), _ptr(trace), ctypes.c_uint(int(polls)), int(peer_cycles), _stream())
+    _check(lib, code, "wait_probe", n_kernels=2)
+    return trace.tolist()
 
 
 def gemm_tc_supported(a, w):

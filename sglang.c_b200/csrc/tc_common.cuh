@@ -58,9 +58,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // A wait with an iteration limit.  Returns false if the limit ran out or another
 // role of the block already gave up (*abort_flag != 0); in the first case it
 // sets the flag itself.
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+// The limit is a constant of the library (about a second of polling by default); a library's
+// set_wait_limit() changes it, which the run-out test does for the probe kernels only.
+__constant__ uint32_t c_wait_limit = 1u << 22;
+inline int set_wait_limit(uint32_t polls) {
+  return (int)cudaMemcpyToSymbol(c_wait_limit, &polls, sizeof(polls));
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  const uint32_t limit = c_wait_limit;
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
@@ -104,7 +110,8 @@ __device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {
 }
 // bounded wait on a barrier of this block that other blocks arrive on
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  const uint32_t limit = c_wait_limit;
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

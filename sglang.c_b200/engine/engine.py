@@ -52,14 +52,16 @@ class Engine:
         self.b_cap = (plan.max_positions + self.page_size - 1) // self.page_size
         self._paged = self.cache.paged_groups()
         self._any_window = any(self.cache.groups[gi].need.window is not None for gi in self._paged)
-        self._max_heads = max([int(lp.mixer.params.get("n_heads", 1)) for lp in plan.layers] + [1])
         self._rep = None                  # what a repeated step of single tokens updates in place
+        self._poisoned = set()            # requests a failed step left with positions never computed
         self._prepared = None             # prepare_repeat's mark: indices of requests that took a page
         self.bufs = StepBuffers(runtime.device, self.max_step_tokens, self.max_requests, self.b_cap,
                                 len(self.cache.groups))
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=runtime.device)
         self.ws = Workspace(runtime.device, self._workspace_bytes())
         self.logits = None
+        from ..csrc import ops as _ops
+        self._few_max_weight = _ops.FEW_MAX_WEIGHT
         self.max_graphs = 48
         self.steps_run = 0
         # steps whose launch shapes repeat replay a CUDA graph (see _forward_graphed)
@@ -79,15 +81,9 @@ class Engine:
         return eng
 
     def _workspace_bytes(self):
-        widths = [self.plan.hidden_size]
-        for lp in self.plan.layers:
-            for spec in (lp.mixer, lp.ffn):
-                p = spec.params
-                widths.append(int(p.get("inner_size", 0)))
-                if "n_heads" in p:
-                    widths.append((p["n_heads"] + 2 * p.get("n_kv_heads", p["n_heads"])) * p["head_dim"])
-        per_token = 4 * (3 * self.plan.hidden_size + 2 * max(widths) + 2 * sum(sorted(widths)[-2:]))
-        return per_token * self.max_step_tokens + (8 << 20)
+        # what the parts say they take per token, rounded up for the 256-byte alignment of each
+        # of a layer's handful of buffers, plus room for a few rows of odds and ends
+        return int(self.model.workspace_per_token() * 1.02) * self.max_step_tokens + (8 << 20)
 
     def _logits_buffer(self, n):
         if self.logits is None or self.logits.shape[0] < n:
@@ -108,7 +104,15 @@ class Engine:
     def end_request(self, req):
         self.cancel_prepared()
         self._rep = None
+        self._poisoned.discard(req)
         self.cache.free_request(req)
+
+    def truncate(self, req, new_len):
+        """Forget what the request holds beyond new_len positions (pages filled by that alone go
+        back to the pool); the next step for it continues from there."""
+        self.cancel_prepared()
+        self._rep = None
+        self.cache.truncate(req, new_len)
 
     def has_request(self, req):
         return self.cache.has_request(req)
@@ -127,6 +131,9 @@ class Engine:
             seen.add(e.req)
             if not self.cache.has_request(e.req):
                 raise StepError(f"request {e.req!r} is not live (add_request first)")
+            if e.req in self._poisoned:
+                raise StepError(f"request {e.req!r} was left half-grown by a step that failed and could not be "
+                                "rolled back (its window had released pages); end it")
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.req!r} brings no tokens")
@@ -166,7 +173,7 @@ class Engine:
         if self._rep is not None:
             ctx = self._step_repeat(entries, self._rep)
             if ctx is not None:
-                return self._run(ctx)
+                return self._run_or_roll_back(ctx, ctx.h_reqs, [n - 1 for n in ctx.h_kv_len])
             self.cancel_prepared()           # prepared for another step than this one
         T = self._validate(entries)
         wants = [(e.req, self.cache.length(e.req) + len(e.tokens)) for e in entries]
@@ -246,7 +253,22 @@ class Engine:
         if n_decode == R and not self._any_window:
             self._rep = dict(reqs=[e.req for e in entries], want=[list(e.want) for e in entries],
                              lens=np.asarray(ctx.h_kv_len, dtype=np.int64), slots=list(ctx.h_state_slots), nw=nw)
-        return self._run(ctx)
+        return self._run_or_roll_back(ctx, [e.req for e in entries], old_len)
+
+    def _run_or_roll_back(self, ctx, reqs, old_len):
+        """_run; if it raises (a shape a kernel refuses, a failed launch), the requests were grown
+        for tokens whose keys and values were never written: the growth is taken back, so that no
+        later step attends to what happens to lie in those pages."""
+        try:
+            return self._run(ctx)
+        except Exception:
+            self._rep = None
+            for req, o in zip(reqs, old_len):
+                try:
+                    self.cache.truncate(req, int(o))
+                except Exception:
+                    self._poisoned.add(req)
+            raise
 
     def _step_repeat(self, entries, rep):
         """The step after a step of single tokens, for the same requests in the same order with
@@ -323,12 +345,13 @@ class Engine:
                 raise StepError("run_prepared: device_tokens must be an int32 device tensor of one id per request")
             ctx = self._finish_prepared(None)
             self.bufs.dview("tokens", R).copy_(device_tokens[:R], non_blocking=True)
-            return self._run(ctx)
+            return self._run_or_roll_back(ctx, ctx.h_reqs, [n - 1 for n in ctx.h_kv_len])
         toks = np.asarray(tokens, dtype=np.int64)
         if toks.shape != (R,) or toks.min() < 0 or toks.max() >= self.plan.vocab_size:
             self.cancel_prepared()
             raise StepError("run_prepared: one token id inside the vocabulary for each request")
-        return self._run(self._finish_prepared(toks))
+        ctx = self._finish_prepared(toks)
+        return self._run_or_roll_back(ctx, ctx.h_reqs, [n - 1 for n in ctx.h_kv_len])
 
     def cancel_prepared(self):
         """Undo prepare_repeat: the requests shrink back by one position, pages taken for them
@@ -378,6 +401,7 @@ class Engine:
         ctx.q_start, ctx.kv_len = b.dview("q_start", R + 1), b.dview("kv_len", R)
         ctx.state_slots = b.dview("state_slots", R)
         ctx.err_flag = self.err_flag
+        ctx.few_token_ok = 0 < self.model.largest_layer_matrix <= self._few_max_weight
         ctx.groups = []
         for gi in range(len(self.cache.groups)):
             if gi in self._paged:
@@ -399,23 +423,7 @@ class Engine:
             return self.model.forward(ctx, self.cache, out)
 
     def _graph_key(self, ctx):
-        # The context bound sizes the shared memory of the decode attention of small batches
-        # (a block stages its whole key range), and what a block holds of an SM decides whether
-        # it can start, and prefetch, while the kernels ahead still run: there the bound moves in
-        # steps of 128 keys up to 1024 and of about an eighth of the length beyond (a capture
-        # every 128 steps costs less than the tighter bound wins).  Other steps take the next
-        # power of two, so a graph serves until the contexts double.
-        from ..csrc import ops
-        if ctx.n_decode == ctx.T and ctx.T * self._max_heads < ops.STREAM_MIN_ITEMS:
-            g = 128
-            while g * 8 < ctx.max_keys:
-                g *= 2
-            bound = ((ctx.max_keys + g - 1) // g) * g
-        else:
-            bound = 128
-            while bound < ctx.max_keys:
-                bound *= 2
-        bound = min(bound, self.plan.max_positions)
+        bound = self.model.graph_bound(ctx)
         return (ctx.T, ctx.R, ctx.n_want, (ctx.max_q_len + 127) // 128 if ctx.max_q_len > 1 else 0,
                 bound, ctx.n_decode, ctx.decode_ordered), bound
 

@@ -23,11 +23,15 @@ class Runtime:
             raise RuntimeError("this engine runs on a CUDA device only (no CPU path)")
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device is available; this engine has no CPU path")
+        if self.device.index is not None and self.device.index >= torch.cuda.device_count():
+            raise RuntimeError(f"device {device}: this machine has {torch.cuda.device_count()} CUDA device(s)")
+        # the kernels are launched through ctypes on the current device's current stream: make
+        # the runtime's device the current one (for this thread), or launches and tensors part ways
+        torch.cuda.set_device(self.device)
         t = torch.float32 if self.dtype == "float32" else torch.bfloat16
         self.matrix_dtype = t
         self.act_dtype = t
         self.cache_dtype = t
-        self.largest_layer_matrix = 0      # elements of the largest matrix a layer's Linear holds
 
     @property
     def cache_dtype_name(self):
@@ -37,17 +41,14 @@ class Runtime:
         dt = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}[dtype_name]
         return torch.zeros(shape, dtype=dt, device=self.device)
 
-    def note_layer_matrix(self, w):
-        self.largest_layer_matrix = max(self.largest_layer_matrix, w.numel())
-
     # -- kernel choice --------------------------------------------------------
-    def gemm(self, a, w, bias, out=None, residual=None, act=None):
+    def gemm(self, a, w, bias, out=None, residual=None, act=None, few_ok=False):
         if self.dtype == "bfloat16" and ops.gemm_tc_supported(a, w):
-            # one or two tokens, and every matrix of the layers small: the kernel without any
-            # exchange between blocks.  (Its blocks are heavy; beside the lighter kernels that
-            # wider matrices need it lengthens the step, so the choice is made for the model.)
-            if a.shape[0] <= ops.FEW_MAX_TOKENS and self.largest_layer_matrix <= ops.FEW_MAX_WEIGHT \
-                    and w.numel() <= ops.FEW_MAX_WEIGHT:
+            # one or two tokens, and every matrix of the model's layers small (few_ok: the step
+            # context says so for the model it runs): the kernel without any exchange between
+            # blocks.  (Its blocks are heavy; beside the lighter kernels that wider matrices need
+            # it lengthens the step, so the choice is made for the model, not for the product.)
+            if few_ok and a.shape[0] <= ops.FEW_MAX_TOKENS and w.numel() <= ops.FEW_MAX_WEIGHT:
                 return ops.gemm_few(a, w, bias, out=out, residual=residual, act=act)
             return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act, supported=True)
         return ops.gemm_simt(a, w, bias, out=out, residual=residual, act=act)

@@ -23,6 +23,7 @@ where the engine allows more:
     positions is refused at submit (the reference: src/scheduler.c:818-825).
 """
 import time
+from collections import deque
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -31,6 +32,7 @@ from .engine import Engine, OutOfPages
 from .step import StepEntry
 
 WAITING, RUNNING, DONE = "waiting", "running", "done"
+KEEP_TAKEN = 256       # taken requests whose record is kept for questions after poll()
 
 
 @dataclass
@@ -86,7 +88,11 @@ class Scheduler:
         self.requests = {}
         self.waiting: List[Request] = []     # FIFO, preempted requests re-enter by arrival order
         self.running: List[Request] = []     # in order of arrival
-        self.done: List[Request] = []
+        # finished and not yet taken by poll(); a taken request stays in `requests` (for its
+        # log-probabilities and finish reason) until KEEP_TAKEN later ones have been taken
+        # (the reference frees a taken request at once, src/scheduler.c:577-615)
+        self.done = deque()
+        self._taken = deque()
         self.next_id = 1
         self.stats = SchedStats(prefill_chunk=self.prefill_chunk, pool_pages=engine.cache.n_pages)
         # any object with Sampler.sample's signature; the default samples on the device
@@ -127,11 +133,14 @@ class Scheduler:
 
     def poll(self):
         """One finished request not yet taken: (id, generated ids, n_prompt), or None."""
-        for r in self.done:
-            if not r.taken:
-                r.taken = True
-                return r.id, list(r.gen), len(r.prompt)
-        return None
+        if not self.done:
+            return None
+        r = self.done.popleft()
+        r.taken = True
+        self._taken.append(r.id)
+        while len(self._taken) > KEEP_TAKEN:
+            self.requests.pop(self._taken.popleft(), None)
+        return r.id, list(r.gen), len(r.prompt)
 
     def poll_logprobs(self, req_id):
         r = self.requests.get(req_id)

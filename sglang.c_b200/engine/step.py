@@ -63,8 +63,8 @@ class Workspace:
         nbytes = n * _ELEMENT_SIZE[dtype]
         if start + nbytes > self.buf.numel():
             raise MemoryError(
-                f"step workspace of {self.buf.numel()} bytes is too small for {nbytes} more bytes; "
-                "raise max_step_tokens or workspace_bytes")
+                f"step workspace of {self.buf.numel()} bytes is too small for {nbytes} more bytes: a part "
+                "asks ctx.alloc for more than its workspace_per_token() declared")
         self.off = start + nbytes
         self.peak = max(self.peak, self.off)
         view = self.buf[start:start + nbytes].view(dtype).view(*shape)
@@ -113,6 +113,7 @@ class StepContext:
         self.decode_ordered = False    # a step of single tokens whose contexts differ by a tile of keys or more
         self.groups: List[GroupStep] = []
         self.err_flag = None
+        self.few_token_ok = False      # every matrix of the model's layers is small (see Runtime.gemm)
 
     def group(self, i):
         return self.groups[i]

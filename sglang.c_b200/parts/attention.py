@@ -36,6 +36,24 @@ class CausalAttention(Part):
         p = self.params
         return CacheNeed.paged_kv(p["n_kv_heads"], p["head_dim"], p.get("window"))
 
+    def workspace_per_token(self):
+        p = self.params
+        return (4 if self.rt.dtype == "float32" else 2) * (2 * p["n_heads"] + 2 * p["n_kv_heads"]) * p["head_dim"]
+
+    def graph_bound(self, ctx):
+        # A step of single tokens in few (token, head) items goes to the decode attention that
+        # stages a block's whole key range in shared memory sized by the bound, and what a block
+        # holds of an SM decides whether it can start, and prefetch, while the kernels ahead still
+        # run: there the bound moves in steps of 128 keys up to 1024 and of about an eighth of the
+        # length beyond (a capture every 128 steps costs less than the tighter bound wins).
+        from ..csrc import ops
+        if ctx.n_decode == ctx.T and ctx.T * self.params["n_heads"] < ops.STREAM_MIN_ITEMS:
+            g = 128
+            while g * 8 < ctx.max_keys:
+                g *= 2
+            return ((ctx.max_keys + g - 1) // g) * g
+        return None
+
     def forward(self, ctx, h, residual, cache, position=None):
         p = self.params
         H, Hkv, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]

@@ -51,3 +51,14 @@ class Part:
 
     def cache_need(self):
         return None
+
+    def workspace_per_token(self, *args):
+        """Bytes per token of the step that this part takes from ctx.alloc while it runs (a
+        block gets its built layer as argument and answers for the whole layer).  The engine
+        sizes the step workspace from the answers."""
+        return 0
+
+    def graph_bound(self, ctx):
+        """Mixers only: an upper bound of the context length for this step's launches, if the
+        mixer's kernels want another than the next power of two (None: no wish)."""
+        return None

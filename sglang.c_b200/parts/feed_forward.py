@@ -25,6 +25,9 @@ class MLP(Part):
         self.up = Linear.from_refs(store, tensors["up_weight"], tensors.get("up_bias"), lay)
         self.down = Linear.from_refs(store, tensors["down_weight"], tensors.get("down_bias"), lay)
 
+    def workspace_per_token(self):
+        return (4 if self.rt.dtype == "float32" else 2) * self.params["inner_size"]
+
     def forward(self, ctx, h, residual):
         T = h.shape[0]
         u = ctx.alloc((T, self.params["inner_size"]), self.rt.act_dtype)

@@ -26,10 +26,9 @@ class Linear:
     def from_refs(cls, store, weight_ref, bias_ref, layout):
         w = store.matrix(weight_ref, transpose=(layout == "conv1d"))
         b = store.vector(bias_ref) if bias_ref is not None else None
-        store.rt.note_layer_matrix(w)
         return cls(w, b)
 
     def forward(self, ctx, a, out=None, act=None, residual=None):
         """out = act(a·Wᵀ + b)  or  residual += a·Wᵀ + b (32-bit, in place)."""
-        ctx.rt.gemm(a, self.weight, self.bias, out=out, residual=residual, act=act)
+        ctx.rt.gemm(a, self.weight, self.bias, out=out, residual=residual, act=act, few_ok=ctx.few_token_ok)
         return residual if residual is not None else out

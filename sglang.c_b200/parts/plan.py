@@ -30,14 +30,50 @@ class PartSpec:
     weights: Dict[str, str] = field(default_factory=dict)   # role -> tensor name
 
 
-@dataclass
+# the category of a layer's sub-part when only its role is given
+_ROLE_CATEGORY = {"norm1": "norm", "norm2": "norm", "norm": "norm", "mixer": "mixer", "ffn": "feed_forward"}
+
+
 class LayerPlan:
-    name: str
-    block: PartSpec            # the arrangement of the four parts below
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    """A layer: a `block` (the arrangement) and the sub-parts it arranges, by role.  The roles are
+    the block's business: the pre-norm block asks for norm1, mixer, norm2, ffn; another block may
+    ask for one norm beside a mixer and a feed-forward, or for a pair of norms behind them.
+    `parts` maps role -> (category, PartSpec); the four usual roles can also be given (and later
+    replaced) as attributes.  A layer has at most one sub-part of category "mixer": its cache
+    need is the layer's."""
+
+    def __init__(self, name, block, norm1=None, mixer=None, norm2=None, ffn=None, parts=None):
+        object.__setattr__(self, "name", name)
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", {})
+        for role, spec in (("norm1", norm1), ("mixer", mixer), ("norm2", norm2), ("ffn", ffn)):
+            if spec is not None:
+                self.parts[role] = (_ROLE_CATEGORY[role], spec)
+        for role, v in (parts or {}).items():
+            setattr(self, role, v)
+
+    def __getattr__(self, role):
+        parts = object.__getattribute__(self, "parts")
+        if role in parts:
+            return parts[role][1]
+        raise AttributeError(f"layer '{self.name}' has no sub-part '{role}'")
+
+    def __setattr__(self, role, value):
+        if role in ("name", "block"):
+            object.__setattr__(self, role, value)
+        elif isinstance(value, tuple):
+            self.parts[role] = (value[0], value[1])
+        else:
+            cat = self.parts[role][0] if role in self.parts else _ROLE_CATEGORY.get(role)
+            if cat is None:
+                raise ValueError(f"sub-part '{role}': give (category, PartSpec), the role alone does not say which")
+            self.parts[role] = (cat, value)
+
+    def mixer_role(self):
+        roles = [r for r, (cat, _) in self.parts.items() if cat == "mixer"]
+        if len(roles) > 1:
+            raise ValueError(f"layer '{self.name}' has {len(roles)} mixers; a layer keeps one cache")
+        return roles[0] if roles else None
 
 
 @dataclass(frozen=True)
@@ -70,9 +106,7 @@ class ModelPlan:
         yield self.embedding
         yield self.position
         for layer in self.layers:
-            yield layer.norm1
-            yield layer.mixer
-            yield layer.norm2
-            yield layer.ffn
+            for _, spec in layer.parts.values():
+                yield spec
         yield self.final_norm
         yield self.head

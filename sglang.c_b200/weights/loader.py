@@ -58,12 +58,9 @@ def _category_of(plan, spec):
     if spec is plan.head:
         return "head"
     for layer in plan.layers:
-        if spec is layer.norm1 or spec is layer.norm2:
-            return "norm"
-        if spec is layer.mixer:
-            return "mixer"
-        if spec is layer.ffn:
-            return "feed_forward"
+        for cat, s in layer.parts.values():
+            if spec is s:
+                return cat
     raise WeightError("part spec does not belong to the plan")
 
 
@@ -139,6 +136,8 @@ class DeviceStore:
         self.rt = runtime
         self._cache = {}
         self.bytes = 0
+        self.in_layer = False              # set by the model while a layer's parts load
+        self.largest_layer_matrix = 0      # elements of the largest matrix a layer's part took
 
     def _put(self, key, make):
         t = self._cache.get(key)
@@ -156,7 +155,10 @@ class DeviceStore:
             if transpose:
                 t = t.t()
             return t.to(self.rt.matrix_dtype).contiguous().to(self.rt.device)
-        return self._put((ref.name, "matrix", transpose), make)
+        t = self._put((ref.name, "matrix", transpose), make)
+        if self.in_layer:
+            self.largest_layer_matrix = max(self.largest_layer_matrix, t.numel())
+        return t
 
     def vector(self, ref):
         return self._put((ref.name, "vector"),

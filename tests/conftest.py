@@ -54,3 +54,52 @@ def model_dirs(tmp_path_factory):
         return cache[key]
 
     return get
+
+
+SHARP = 6.0     # factor on the query and key projections of a "sharp" model
+
+
+def make_sharp_dir(tmp, name, store_dtype="float32", factor=SHARP):
+    """The tiny model `name` with the query and key columns of every c_attn (weights and biases)
+    multiplied by `factor`: scores grow by its square, the softmax stops being nearly uniform
+    (with N(0, 0.02) weights it is), and every single key carries weight: a key dropped, misplaced
+    or read from a stale page moves logits by far more than rounding does."""
+    import json
+    import numpy as np
+    import torch
+    import plain_gpt2
+    from sglang_c_b200.weights.safetensors_io import write_safetensors
+    base = make_model_dir(tmp, name, "float32")
+    out = os.path.join(str(tmp), f"sharp_{name}_{store_dtype}")
+    if os.path.exists(os.path.join(out, "model.safetensors")):
+        return out
+    cfg, w = plain_gpt2.read_model_dir(base)
+    E = cfg["n_embd"]
+    tensors = {}
+    for k, v in w.items():
+        a = np.array(v, dtype=np.float32)
+        if k.endswith("attn.c_attn.weight"):
+            a[:, :2 * E] *= factor
+        elif k.endswith("attn.c_attn.bias"):
+            a[:2 * E] *= factor
+        t = torch.from_numpy(a)
+        tensors[k] = t.to(torch.bfloat16) if (store_dtype == "bfloat16" and t.dim() >= 2) else t
+    os.makedirs(out, exist_ok=True)
+    with open(os.path.join(out, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(out, "model.safetensors"), tensors)
+    return out
+
+
+@pytest.fixture(scope="session")
+def sharp_dirs(tmp_path_factory):
+    base = tmp_path_factory.mktemp("sharp")
+    cache = {}
+
+    def get(name, store_dtype="float32"):
+        key = (name, store_dtype)
+        if key not in cache:
+            cache[key] = make_sharp_dir(base, name, store_dtype)
+        return cache[key]
+
+    return get

@@ -160,24 +160,38 @@ def attention_scale(st, layer_idx):
     return s
 
 
-def attention_block(x, w, l, st):
+def _same(a):
+    return a
+
+
+def bf16_round(a):
+    """The nearest bfloat16 (8 bits of mantissa, ties to even) of every element, as float64."""
+    f = np.ascontiguousarray(a, dtype=np.float32)
+    bits = f.view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).astype(np.float64).reshape(f.shape)
+
+
+def attention_block(x, w, l, st, r=_same):
     """ln_1 → c_attn → split q|k|v → attention → c_proj → residual
-    (src/gpt2.c:220-278)."""
+    (src/gpt2.c:220-278).  `r` rounds what an engine keeps in reduced precision: the normalised
+    rows, the projected queries/keys/values (as they lie in the cache) and the attention output;
+    the residual stream stays as it is."""
     E = st["E"]
     p = f"h.{l}."
-    h = layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], st["eps"])
-    qkv = conv1d(h, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"])
+    h = r(layer_norm(x, w[p + "ln_1.weight"], w[p + "ln_1.bias"], st["eps"]))
+    qkv = r(conv1d(h, w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"]))
     q, k, v = qkv[:, :E], qkv[:, E:2 * E], qkv[:, 2 * E:]
-    a = causal_attention(q, k, v, st["H"], attention_scale(st, l))
+    a = r(causal_attention(q, k, v, st["H"], attention_scale(st, l)))
     return x + conv1d(a, w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"])
 
 
-def mlp_block(x, w, l, st):
+def mlp_block(x, w, l, st, r=_same):
     """ln_2 → c_fc → activation → c_proj → residual  (src/gpt2.c:281-292)."""
     p = f"h.{l}."
-    h = layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], st["eps"])
+    h = r(layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], st["eps"]))
     u = conv1d(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"])
-    g = ACTIVATIONS[st["act"]](u)
+    g = r(ACTIVATIONS[st["act"]](u))
     return x + conv1d(g, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
 
 
@@ -187,24 +201,32 @@ def lm_head(hf, wte):
     return hf @ wte.T
 
 
-def forward(cfg, w, tokens, dtype=np.float64):
+def forward(cfg, w, tokens, dtype=np.float64, rounded=False):
     """Logits at every position of one whole sequence, [T, V]
-    (the order of src/gpt2.c:210-297; the reference returns the last row only)."""
+    (the order of src/gpt2.c:210-297; the reference returns the last row only).
+    rounded=True rounds to bfloat16 what a bfloat16 engine keeps in bfloat16 (matrices and tables,
+    normalised rows, projections, cached keys and values, attention and activation outputs) and
+    keeps every sum, statistic and the residual stream in float64: against it an engine's
+    bfloat16 run differs by the order of its additions only, not by the rounding itself."""
     st = settings(cfg)
     w = {k: v.astype(dtype) for k, v in w.items()}
+    r = _same
+    if rounded:
+        r = bf16_round
+        w = {k: (bf16_round(v) if v.ndim >= 2 else v.astype(np.float64)) for k, v in w.items()}
     if len(tokens) > st["P"]:
         raise ValueError("sequence longer than n_positions")
     x = embedding(tokens, w["wte.weight"], w["wpe.weight"])
     for l in range(st["L"]):
-        x = attention_block(x, w, l, st)
-        x = mlp_block(x, w, l, st)
-    hf = layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], st["eps"])
+        x = attention_block(x, w, l, st, r)
+        x = mlp_block(x, w, l, st, r)
+    hf = r(layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], st["eps"]))
     return lm_head(hf, w["wte.weight"])
 
 
-def forward_dir(model_dir, tokens, dtype=np.float64):
+def forward_dir(model_dir, tokens, dtype=np.float64, rounded=False):
     cfg, w = read_model_dir(model_dir)
-    return forward(cfg, w, tokens, dtype)
+    return forward(cfg, w, tokens, dtype, rounded)
 
 
 # --------------------------------------------------------------------------

@@ -39,7 +39,33 @@ def test_plain_matches_reference_cpu_code(tmp_path, golden):
     # the reference computes in float32 (with some double accumulators)
     assert np.abs(got - ref).max() < 2e-6
     assert [int(r.argmax()) for r in logits] == golden["argmax"]
-    assert golden["decode_batch_vs_prefill_max_abs"] == 0.0
+
+
+@pytest.mark.parametrize("case", ["inverse_layer_idx", "no_scale"])
+def test_plain_options_match_reference_on_changed_weights(tmp_path, case):
+    """n_inner other than 4*n_embd, scale_attn_by_inverse_layer_idx and scale_attn_weights=false:
+    the reference ran an equal function on changed weights (tests/golden/make_golden_b.py); the
+    plain implementation runs the options themselves on the original weights."""
+    import math
+    from sglang_c_b200.config import resolve_architecture
+    from sglang_c_b200.weights import write_random_model
+    with open(os.path.join(HERE, "golden", "gpt2_options_reference.json")) as f:
+        g = json.load(f)
+    c = g["cases"][case]
+    arch = resolve_architecture(c["config"])
+    d = str(tmp_path / case)
+    write_random_model(d, arch, arch.config_class.from_dict(c["config"]), g["seed"], scheme=g["scheme"],
+                       store_dtype="float32")
+    with open(os.path.join(d, "model.safetensors"), "rb") as f:
+        assert hashlib.sha256(f.read()).hexdigest() == c["weights_sha256"], \
+            "the random-weight generator changed: regenerate tests/golden"
+    logits = plain_gpt2.forward_dir(d, c["tokens"])
+    for n, row in zip(c["prefix_lengths"], c["logits"]):
+        got = logits[n - 1, c["columns"]]
+        assert np.abs(got - np.array(row)).max() < 3e-6, (case, n)
+    # the exact GELU, which no change of weights expresses, against the C library's erf
+    u = np.linspace(-6, 6, 49)
+    assert np.abs(plain_gpt2.gelu_erf(u) - np.array([0.5 * x * (1 + math.erf(x / math.sqrt(2))) for x in u])).max() < 1e-15
 
 
 def test_plain_float32_close_to_float64(tmp_path, golden):

@@ -14,11 +14,20 @@ from conftest import PAGE_SIZE, ROOT, TINY
 
 pytestmark = pytest.mark.gpu
 
-# Fixed before the first run.  32-bit: the engine and the float64 oracle differ by
-# float32 rounding only (logits are below 1 in size).  bfloat16: activations and
-# products are rounded to 8 bits of mantissa; a fault of the cache or of a kernel
-# moves logits by several 1e-2 at least.
-TOL = {"float32": 2e-5, "bfloat16": 1e-2}
+# 32-bit: the engine and the float64 oracle differ by float32 rounding only (logits are below 1
+# in size).  bfloat16: the oracle rounds to bfloat16 wherever the engine does (weights, normalised
+# rows, projections, cached keys and values, attention and activation outputs), so what is left
+# is the engine's 32-bit order of additions and, through it, the rare value that falls on the
+# other side of a rounding step: one such flip of a normalised value near 2 is 2^-7 and moves a
+# logit by up to 5e-4, a handful of them over a long sequence were measured at 1.1e-3 to 3.4e-3
+# on these models (every stage alone agrees with the oracle bit for bit).  The bound is twice
+# that; against an oracle without the rounding the same runs lie at 2e-3 to 3e-3, which is why
+# the bound cannot go lower by much.  A single key lost among hundreds moves logits by less than
+# this when the weights are N(0, 0.02): the 32-bit runs (same step function, cache and block
+# tables, bound 2e-5), the kernels' own tests with a key made to stand out, and the sharp model
+# below are what catches that.
+TOL = {"float32": 2e-5, "bfloat16": 6e-3}
+TOL_SHARP = {"float32": 1e-4, "bfloat16": 8e-3}
 STORE = {"float32": "float32", "bfloat16": "bfloat16"}
 
 # C has head size 64 and 1024 positions: in bfloat16 it runs the tensor-core attention kernels
@@ -33,12 +42,14 @@ def requests_for(name):
 _ref_cache = {}
 
 
-def reference(model_dir, requests):
+def reference(model_dir, requests, dtype="float32"):
+    """The plain implementation's logits; for a bfloat16 run, with rounding to bfloat16 where the
+    engine rounds (weights, activations, cached keys and values), every sum in float64."""
     out = {}
     for rid, toks in requests.items():
-        key = (model_dir, tuple(toks))
+        key = (model_dir, tuple(toks), dtype == "bfloat16")
         if key not in _ref_cache:
-            _ref_cache[key] = plain_gpt2.forward_dir(model_dir, toks)
+            _ref_cache[key] = plain_gpt2.forward_dir(model_dir, toks, rounded=(dtype == "bfloat16"))
         out[rid] = _ref_cache[key]
     return out
 
@@ -68,7 +79,7 @@ def test_each_request_alone(model_dirs, tmp_path, name, dtype, mode):
     reqs = requests_for(name)
     steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions}[mode](reqs)
     got, _ = run_trace(d, dtype, name, steps, tmp_path, max_step_tokens=1024)
-    err, where = traces.max_error(got, reference(d, reqs))
+    err, where = traces.max_error(got, reference(d, reqs, dtype))
     assert err < TOL[dtype], f"{mode}: max error {err} at {where}"
 
 
@@ -88,8 +99,36 @@ def test_mixed_batches_with_pages_used_again(model_dirs, tmp_path, name, dtype):
     total = sum((n + 63) // 64 * 64 for n in lens)
     assert peak < total, "the pool must be smaller than all requests together"
     got, eng = run_trace(d, dtype, name, steps, tmp_path, max_tokens=peak)
-    err, where = traces.max_error(got, reference(d, reqs))
+    err, where = traces.max_error(got, reference(d, reqs, dtype))
     assert err < TOL[dtype], f"mixed: max error {err} at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sharp_attention_in_every_cut(sharp_dirs, tmp_path, dtype):
+    """Model C with its query and key projections times 6: scores 36 times larger, a softmax that
+    singles keys out (an early token changed moves the last logits by 0.1 and more where the
+    plain model moves them by 1e-3).  Whole, last tokens one by one (steady decoding replays a
+    captured graph), changing portions, and mixed with pages used again."""
+    name = "C"
+    d = sharp_dirs(name, STORE[dtype])
+    reqs = requests_for(name)
+    ref = reference(d, reqs, dtype)
+    toks = reqs["r1"]
+    changed = list(toks)
+    changed[3] = (changed[3] + 1) % TINY[name]["vocab_size"]
+    moved = np.abs(plain_gpt2.forward_dir(d, changed, rounded=(dtype == "bfloat16"))[-1] - ref["r1"][-1]).max()
+    assert moved > 10 * TOL_SHARP[dtype], "the sharp model has lost its teeth"
+    prompt_len = {rid: max(1, len(t) - 24) for rid, t in reqs.items()}
+    mixed = traces.mixed(reqs, prompt_len, seed=5)
+    for mode, steps, kw in (("whole", traces.whole(reqs), dict(max_step_tokens=1024)),
+                            ("tail", traces.tail_decoded(reqs), dict(max_step_tokens=1024)),
+                            ("portions", traces.portions(reqs), dict(max_step_tokens=1024)),
+                            ("mixed", mixed, dict(max_tokens=traces.peak_tokens(mixed)))):
+        got, eng = run_trace(d, dtype, name, steps, tmp_path / mode, **kw)
+        err, where = traces.max_error(got, ref)
+        assert err < TOL_SHARP[dtype], f"sharp {mode}: max error {err} at {where}"
+        if mode == "tail" and dtype == "bfloat16":
+            assert eng.graph_replays > 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -123,7 +162,7 @@ def test_long_decoding(model_dirs, tmp_path, dtype):
     reqs = {"long": toks}
     steps = traces.tail_decoded(reqs, n_tail=P - 24)
     got, _ = run_trace(d, dtype, name, steps, tmp_path, max_step_tokens=64)
-    err, where = traces.max_error(got, reference(d, reqs))
+    err, where = traces.max_error(got, reference(d, reqs, dtype))
     assert err < TOL[dtype], f"long decoding: max error {err} at {where}"
 
 
@@ -136,7 +175,7 @@ def test_first_tokens_of_a_sequence(model_dirs, tmp_path, name, dtype):
     reqs = {"s": traces.random_tokens(5, 6, V), "t": traces.random_tokens(6, 2, V)}
     steps = traces.tail_decoded(reqs, n_tail=64)
     got, _ = run_trace(d, dtype, name, steps, tmp_path)
-    err, where = traces.max_error(got, reference(d, reqs))
+    err, where = traces.max_error(got, reference(d, reqs, dtype))
     assert err < TOL[dtype], f"first tokens: max error {err} at {where}"
 
 
@@ -184,5 +223,5 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
     proc.stdin.close()
     assert proc.wait(timeout=120) == 0
     got = traces.collect(steps, out, V)
-    err, where = traces.max_error(got, reference(d, reqs))
+    err, where = traces.max_error(got, reference(d, reqs, dtype))
     assert err < TOL[dtype], f"trace_run: max error {err} at {where}"

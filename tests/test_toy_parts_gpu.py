@@ -2,8 +2,10 @@
 without a change to its files: a mixer with per-request state of its own (in slots, not
 pages), a running order that names a layer twice, a call that reads the cache another call
 wrote, a layer with a window beside layers without, a feed-forward that routes each token to
-experts (in some layers only), and a position encoding that turns queries and keys instead of
-adding a table.  Each toy model is compared with a
+experts (in some layers only), a position encoding that turns queries and keys instead of
+adding a table, a gated feed-forward with two up-projections that takes its buffers from the step
+workspace (and says how much), and a block of another shape: one norm feeding mixer and
+feed-forward side by side.  Each toy model is compared with a
 plain restatement written here from the plain implementation's parts.  These are toys, not
 models of anyone's."""
 import dataclasses
@@ -23,6 +25,7 @@ TOL = {"float32": 3e-5, "bfloat16": 1.5e-2}
 DECAY = 0.75
 N_EXPERTS = 3
 ROTARY_BASE = 100.0
+GATED_INNER = 136          # no multiple of the hidden size, nor a power of two
 
 
 def _register():
@@ -115,6 +118,70 @@ def _register():
                 xv[..., :half] = na.to(x.dtype)
                 xv[..., half:] = nb.to(x.dtype)
 
+    @register_part("feed_forward", "toy_gated")
+    class GatedFeedForward(Part):
+        """residual += (silu(h·Wgᵀ) * (h·Wuᵀ))·Wdᵀ: two up-projections into buffers of the step
+        workspace, whose size per token the part declares."""
+        graph_safe = False
+
+        @classmethod
+        def declare_weights(cls, params):
+            return {"gate": WeightDecl((params["inner_size"], params["size"]), "matrix"),
+                    "up": WeightDecl((params["inner_size"], params["size"]), "matrix"),
+                    "down": WeightDecl((params["size"], params["inner_size"]), "residual_matrix")}
+
+        def load(self, tensors, store):
+            self.gate, self.up, self.down = (store.matrix(tensors[k]) for k in ("gate", "up", "down"))
+
+        def workspace_per_token(self):
+            return 2 * self.params["inner_size"] * (4 if self.rt.dtype == "float32" else 2)
+
+        def forward(self, ctx, h, residual):
+            T, inner = h.shape[0], self.params["inner_size"]
+            g = ctx.alloc((T, inner), self.rt.act_dtype)
+            u = ctx.alloc((T, inner), self.rt.act_dtype)
+            ctx.rt.gemm(h, self.gate, None, out=g)
+            ctx.rt.gemm(h, self.up, None, out=u)
+            g.copy_((torch.nn.functional.silu(g.float()) * u.float()).to(g.dtype))
+            ctx.rt.gemm(g, self.down, None, residual=residual)
+            return residual
+
+    @register_part("block", "toy_parallel")
+    class ParallelBlock(Part):
+        """x += mixer(norm(x)) + ffn(norm(x)): one norm, read by both."""
+
+        def workspace_per_token(self, layer):
+            act = 4 if self.rt.dtype == "float32" else 2
+            return act * layer.norm.params["size"] + max(layer.mixer.workspace_per_token(),
+                                                         layer.ffn.workspace_per_token())
+
+        def forward(self, ctx, x, layer, cache, position=None):
+            mark = ctx.mark()
+            h = ctx.alloc((x.shape[0], x.shape[1]), self.rt.act_dtype)
+            layer.norm.forward(ctx, x, h)
+            inner = ctx.mark()
+            layer.mixer.forward(ctx, h, residual=x, cache=cache, position=position)
+            ctx.release(inner)
+            layer.ffn.forward(ctx, h, residual=x)
+            ctx.release(mark)
+            return x
+
+    def plan_gated(cfg):
+        plan = build_plan(cfg)
+        for l, layer in enumerate(plan.layers):
+            layer.ffn = PartSpec("toy_gated", {"size": cfg.n_embd, "inner_size": GATED_INNER},
+                                 {"gate": f"h.{l}.toy.gate.weight", "up": f"h.{l}.toy.up.weight",
+                                  "down": f"h.{l}.toy.down.weight"})
+        return plan
+
+    def plan_parallel(cfg):
+        from sglang_c_b200.parts import LayerPlan
+        plan = build_plan(cfg)
+        plan.layers = [LayerPlan(lp.name, PartSpec("toy_parallel"),
+                                 parts={"norm": lp.norm1, "mixer": lp.mixer, "ffn": lp.ffn})
+                       for lp in plan.layers]
+        return plan
+
     def plan_routed(top_k):
         def make(cfg):
             plan = build_plan(cfg)
@@ -154,6 +221,8 @@ def _register():
     register_architecture("ToyRoutedForTest", GPT2Config, plan_routed(1))
     register_architecture("ToyMixtureForTest", GPT2Config, plan_routed(N_EXPERTS))
     register_architecture("ToyRotaryForTest", GPT2Config, plan_rotary)
+    register_architecture("ToyGatedForTest", GPT2Config, plan_gated)
+    register_architecture("ToyParallelForTest", GPT2Config, plan_parallel)
 
 
 @pytest.fixture(scope="module")
@@ -292,7 +361,32 @@ def plain_rotary(cfg, w, toks):
     return _finish(x, w, st)
 
 
-PLAIN = {"ToyStateForTest": plain_state, "ToyOrderForTest": plain_order, "ToyWindowForTest": plain_window,
+def plain_gated(cfg, w, toks):
+    st = plain_gpt2.settings(cfg)
+    x = plain_gpt2.embedding(toks, w["wte.weight"], w["wpe.weight"])
+    for l in range(st["L"]):
+        x = plain_gpt2.attention_block(x, w, l, st)
+        p = f"h.{l}."
+        h = plain_gpt2.layer_norm(x, w[p + "ln_2.weight"], w[p + "ln_2.bias"], st["eps"])
+        g, u = h @ w[p + "toy.gate.weight"].T, h @ w[p + "toy.up.weight"].T
+        x = x + (g / (1.0 + np.exp(-g)) * u) @ w[p + "toy.down.weight"].T
+    return _finish(x, w, st)
+
+
+def plain_parallel(cfg, w, toks):
+    st = plain_gpt2.settings(cfg)
+    x = plain_gpt2.embedding(toks, w["wte.weight"], w["wpe.weight"])
+    act = plain_gpt2.ACTIVATIONS[st["act"]]
+    for l in range(st["L"]):
+        p = f"h.{l}."
+        h, q, k, v = _qkv(x, w, l, st)
+        a = plain_gpt2.causal_attention(q, k, v, st["H"], plain_gpt2.attention_scale(st, l))
+        u = act(plain_gpt2.conv1d(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"]))
+        x = _attn_out(x, a, w, l) + plain_gpt2.conv1d(u, w[p + "mlp.c_proj.weight"], w[p + "mlp.c_proj.bias"])
+    return _finish(x, w, st)
+
+
+PLAIN = {"ToyGatedForTest": plain_gated, "ToyParallelForTest": plain_parallel, "ToyStateForTest": plain_state, "ToyOrderForTest": plain_order, "ToyWindowForTest": plain_window,
          "ToyRoutedForTest": plain_routed(1), "ToyMixtureForTest": plain_routed(N_EXPERTS),
          "ToyRotaryForTest": plain_rotary}
 
@@ -310,7 +404,8 @@ def run(model_dir, dtype, steps, tmp_path, n_pages, page_size=8):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("arch", ["ToyStateForTest", "ToyOrderForTest", "ToyWindowForTest", "ToyRoutedForTest",
-                                  "ToyMixtureForTest", "ToyRotaryForTest"])
+                                  "ToyMixtureForTest", "ToyRotaryForTest", "ToyGatedForTest",
+                                  "ToyParallelForTest"])
 @pytest.mark.parametrize("tiny", ["A", "B"])
 def test_toy_models_in_every_cut(toy_dirs, tmp_path, arch, tiny, dtype):
     if arch == "ToyRoutedForTest" and dtype == "bfloat16":

@@ -129,14 +129,16 @@ def collect(steps, out_dir, vocab):
     return got
 
 
-def max_error(got, reference):
+def max_error(got, reference, all_positions=True):
     """Largest absolute difference over all collected rows; also checks that
-    every position of every request was produced."""
+    every position of every request was produced (all_positions=False: that
+    some were, and compares those)."""
     worst, where = 0.0, None
     for rid, ref in reference.items():
         assert rid in got, f"no logits for request {rid}"
-        assert sorted(got[rid]) == list(range(len(ref))), f"request {rid}: positions missing"
-        for p in range(len(ref)):
+        if all_positions:
+            assert sorted(got[rid]) == list(range(len(ref))), f"request {rid}: positions missing"
+        for p in sorted(got[rid]):
             d = float(np.abs(got[rid][p].astype(np.float64) - ref[p]).max())
             if not np.isfinite(d):
                 return float("inf"), (rid, p)

@@ -26,19 +26,6 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& u, float* f) {
   }
 }
 
-// Optional timeline for tuning (compile with -DSGLC_TIMELINE): block (0,0,0), thread 0 stores
-// the nanosecond timer at a few points into tl_out[slot].
-#ifdef SGLC_TIMELINE
-__device__ unsigned long long g_tl[16];
-#define TL(slot)                                                                      \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {    \
-    unsigned long long t_;                                                            \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                            \
-    g_tl[slot] = t_;                                                                  \
-  }
-#else
-#define TL(slot)
-#endif
 
 // the shared::cluster address of `local` as it lies in the block of rank `cta_rank`
 __device__ __forceinline__ uint32_t map_to_peer(const void* local, int cta_rank) {
@@ -110,7 +97,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   int* spage = reinterpret_cast<int*>(sc + chunk_cap);   // the request's page ids, nb_max of them
   float* recs = reinterpret_cast<float*>(spage + nb_max);   // merge records (block 0 of a cluster)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  TL(0);
   pdl_launch_dependents();
   if (use_cluster) {
     // block 0's merge barrier exists before any block may signal it: arrive now, wait later
@@ -142,7 +128,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int n = pos - lo + 1;
   int chunk = (n + n_splits - 1) / n_splits;
-  if (chunk > chunk_cap) chunk = chunk_cap;          // cannot happen when the host sized chunk_cap
+  // The launcher sized the score array and the page list from max_keys; a position beyond it (a
+  // caller's max_keys smaller than some positions[t] + 1) would index past both.  Such a token
+  // gets zeros and the error word instead; every block of the token takes this way out alike.
+  if (pos < 0 || pos / page_size >= nb_max || chunk > chunk_cap) {
+    if (sp == 0) {
+      __nv_bfloat16* bad = out + (size_t)t * o_stride + (size_t)h * D;
+      for (int d = tid; d < D; d += THREADS) bad[d] = __float2bfloat16_rn(0.0f);
+      if (tid == 0 && err) atomicExch(err, 1);
+    }
+    return;
+  }
   const int k0 = lo + sp * chunk;
   int k1 = k0 + chunk;
   if (k1 > pos + 1) k1 = pos + 1;
@@ -155,7 +151,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
   const bool fused = k_new != nullptr;
   const __nv_bfloat16* kn = fused ? k_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
   const __nv_bfloat16* vn = fused ? v_new + (size_t)t * new_stride + (size_t)hk * D : nullptr;
-  TL(1);
 
   // LPR lanes share one key's row (16 bytes each), so a warp reads KG whole rows per load and
   // consecutive keys of a page are one contiguous stretch.  Key index of (round j, this lane)
@@ -274,7 +269,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       }
     }
   }
-  TL(2);
   const float m = block_max(lmax, red);
   float lsum = 0.0f;
   for (int i = tid; i < nk; i += THREADS) {
@@ -330,7 +324,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     for (int y = 0; y < 8; y++) part[(warp * KG + kg) * D + dl * 8 + y] = acc[y];
   }
   __syncthreads();
-  TL(3);
   const int n_part = WARPS * KG;
 
   __nv_bfloat16* op = out + (size_t)t * o_stride + (size_t)h * D;
@@ -361,7 +354,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
       }
       if (tid == 0) { dst_local[0] = m; dst_local[1] = l; }
       __syncthreads();
-      TL(4);
       if (!mbar_wait_cluster(&merge_bar, 0)) {
         if (tid == 0 && err) atomicExch(err, 1);
         // a peer that has not signalled may still be storing into this block's shared memory:
@@ -371,7 +363,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         cluster_wait();
         return;
       }
-      TL(5);
     } else {
       const uint32_t dst = map_to_peer(dst_local, 0);
       for (int d = tid; d < D; d += THREADS) {
@@ -398,7 +389,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         if (recs[s * rec + 1] > 0.0f) o += recs[s * rec + 2 + d] * expf(recs[s * rec] - M);
       op[d] = __float2bfloat16_rn(o * inv);
     }
-    TL(6);
     return;
   }
   // more ranges than a cluster holds: (m, l, o) of this range go to a workspace in global
@@ -455,11 +445,6 @@ SGLC_API int sglc_attention_decode_scratch(int T, int H, int D, int n_splits, lo
 }
 
 // How many key ranges the launcher would use for T tokens of H heads with up to max_keys keys.
-#ifdef SGLC_TIMELINE
-SGLC_API int sglc_attention_decode_timeline(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16);
-}
-#endif
 
 SGLC_API int sglc_attention_decode_splits(int T, int H, int max_keys) {
   long long blocks = (long long)T * H;
@@ -528,13 +513,17 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
 #include "attention_decode_noalloc.h"
 
 // [SGLC_NOALLOC_MAX_WS_FLOATS floats of (m, l, o) records][SGLC_NOALLOC_MAX_COUNTERS ints]
+// [one int: set by a launch that met a position beyond its max_keys][padding]
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SGLC_NOALLOC_SCRATCH_BYTES];
 
 namespace {
 constexpr int NOALLOC_MAX_DEVICES = 64;
 // In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address;
 // the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+// (Filled without a lock: two host threads that make a device's first call at once both look the
+// address up and both store the same value.)
 void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+constexpr size_t NOALLOC_STATUS_OFFSET = (size_t)SGLC_NOALLOC_MAX_WS_FLOATS * 4 + (size_t)SGLC_NOALLOC_MAX_COUNTERS * 4;
 
 int noalloc_scratch(void** out) {
   int dev = -1;
@@ -559,7 +548,25 @@ SGLC_API const char* sglc_attention_decode_noalloc_error(int code) {
            "(T*H*n_splits*(D+2) floats <= 1048576 and T*H <= 16384)";
   if (code == SGLC_NOALLOC_ERR_SETUP)
     return "the address of the built-in scratch could not be looked up on this device";
+  if (code == SGLC_NOALLOC_ERR_POSITION)
+    return "a token's position lies beyond max_keys - 1 (its output was set to zero): pass a max_keys "
+           "that covers every positions[t] + 1";
   return sglc_error_string(code);
+}
+
+SGLC_API int sglc_attention_decode_noalloc_check(cudaStream_t stream) {
+  void* base = nullptr;
+  int rc = noalloc_scratch(&base);
+  if (rc != SGLC_OK) return rc;
+  int word = 0;
+  int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + NOALLOC_STATUS_OFFSET);
+  cudaError_t e = cudaMemcpyAsync(&word, status, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return (int)e;
+  if (word == 0) return SGLC_OK;
+  e = cudaMemsetAsync(status, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  return SGLC_NOALLOC_ERR_POSITION;
 }
 
 SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const void* cache,
@@ -606,6 +613,8 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
       bt_stride, token_req, positions, (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale,
       window, n_splits, chunk_cap, /*use_cluster=*/0, ws, counters,
       /*k_new=*/(const __nv_bfloat16*)nullptr, /*v_new=*/(const __nv_bfloat16*)nullptr, 0,
-      /*slots=*/(const int*)nullptr, nb_max, /*err=*/(int*)nullptr, /*token_list=*/(const int*)nullptr);
+      /*slots=*/(const int*)nullptr, nb_max,
+      /*err=*/reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + NOALLOC_STATUS_OFFSET),
+      /*token_list=*/(const int*)nullptr);
   return sglc_launch_status();
 }

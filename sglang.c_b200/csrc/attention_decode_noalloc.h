@@ -9,7 +9,7 @@
  * ranges.  Here that scratch is a fixed array inside the library itself.
  *
  * What to know before calling it:
- *   - The scratch is a file-scope device array of SGLC_NOALLOC_SCRATCH_BYTES (about 4 MB).
+ *   - The scratch is a file-scope device array of SGLC_NOALLOC_SCRATCH_BYTES (4,260,096 bytes).
  *     Every GPU on which the library is loaded holds it until the process exits.
  *   - Sizes must fit: T*H*n_splits*(D+2) floats <= SGLC_NOALLOC_MAX_WS_FLOATS and
  *     T*H <= SGLC_NOALLOC_MAX_COUNTERS; otherwise the call returns
@@ -20,6 +20,13 @@
  *     must start at zero (the arrival counters) is cleared on the caller's stream at the
  *     start of every call.  Two calls that overlap on the GPU (different streams, or two
  *     host threads) race on the scratch and give wrong results: serialise them.
+ *   - max_keys must cover every token: positions[t] + 1 <= max_keys.  The launch sizes its
+ *     shared memory from it; a token beyond it is not computed: its output rows are zeros and
+ *     a status word inside the scratch is set.  sglc_attention_decode_noalloc_check(stream)
+ *     waits for the stream, returns SGLC_NOALLOC_ERR_POSITION if the word was set since the
+ *     last check (and clears it), 0 otherwise; it allocates nothing either.
+ *   - The table of looked-up addresses is filled without a lock; two host threads making a
+ *     device's first call at the same moment both store the same value, which is harmless.
  *   - It calls no cudaMalloc, cudaFree or other allocating routine.
  * Arguments are those of sglc_attention_decode without the scratch pointers:
  *   q, out: bfloat16 rows [T][stride], heads side by side; cache: one layer's bfloat16 pages
@@ -40,15 +47,18 @@ extern "C" {
 
 #define SGLC_NOALLOC_MAX_WS_FLOATS (1 << 20)
 #define SGLC_NOALLOC_MAX_COUNTERS (1 << 14)
-#define SGLC_NOALLOC_SCRATCH_BYTES (SGLC_NOALLOC_MAX_WS_FLOATS * 4 + SGLC_NOALLOC_MAX_COUNTERS * 4)
+#define SGLC_NOALLOC_SCRATCH_BYTES (SGLC_NOALLOC_MAX_WS_FLOATS * 4 + SGLC_NOALLOC_MAX_COUNTERS * 4 + 256)
 #define SGLC_NOALLOC_ERR_TOO_LARGE (-10)
 #define SGLC_NOALLOC_ERR_SETUP (-11)
+#define SGLC_NOALLOC_ERR_POSITION (-12)
 
 int sglc_attention_decode_noalloc(const void* q, int q_stride, const void* cache,
                                   const int* block_table, int bt_stride, const int* token_req,
                                   const int* positions, void* out, int o_stride, int T, int H,
                                   int Hkv, int D, int page_size, float scale, int window,
                                   int max_keys, int n_splits, cudaStream_t stream);
+
+int sglc_attention_decode_noalloc_check(cudaStream_t stream);
 
 const char* sglc_attention_decode_noalloc_error(int code);
 

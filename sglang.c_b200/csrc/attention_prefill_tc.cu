@@ -35,30 +35,6 @@ constexpr int THREADS = SOFTMAX_THREADS + 128;     // warps 0-7 softmax, warp 8 
 constexpr int N_LOADERS = 96;
 constexpr int KV_STAGES = 2;
 
-// Optional timeline for tuning (compile with -DSGLC_TIMELINE): the last query tile of the first
-// (request, head) stores the nanosecond timer at points of its softmax thread 0.
-#ifdef SGLC_TIMELINE
-__device__ unsigned long long g_tl[64];
-#define TL(slot)                                                                            \
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {                \
-    unsigned long long t_;                                                                  \
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                  \
-    g_tl[slot] = t_;                                                                        \
-  }
-__device__ unsigned long long g_tl_blocks[2 * 2048];     // per block: start and end
-#define TLB(slot)                                                                           \
-  if (threadIdx.x == 0) {                                                                   \
-    const unsigned b_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;     \
-    if (b_ < 2048) {                                                                        \
-      unsigned long long t_;                                                                \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                \
-      g_tl_blocks[2 * b_ + slot] = t_;                                                      \
-    }                                                                                       \
-  }
-#else
-#define TL(slot)
-#define TLB(slot)
-#endif
 
 struct Ctl {
   uint64_t q_full, s_full, p_ready, o_full;
@@ -136,8 +112,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   // (the last query tile of the longest request) while most SMs have long finished.
   const int r = blockIdx.x / a.H, h = blockIdx.x % a.H, rank = blockIdx.z, cl = blockIdx.y;
   pdl_launch_dependents();
-  TLB(0);
-  TLB(1);
   pdl_wait();
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
@@ -414,12 +388,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_before_sync();
     };
     bool ok = true;
-    TL(0);
     for (int j = 0; j < n_tiles && ok; j++) {
-      if (j == 2) TL(1);
       ok = mbar_wait(&ctl.s_full, j & 1, abort_flag);
       if (!ok) break;
-      if (j == 2) TL(2);
       tc_fence_after_sync();
       const int key0 = (kt0 + j) * BKV;
       // a tile needs the mask only where it meets the diagonal, the window's edge or the end
@@ -457,7 +428,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
           }
         }
       }
-      if (j == 2) TL(3);
       if (j > 0) {
         // the tile before: its P.V ran under this pass; fold it in (its P may then be overwritten)
         ok = mbar_wait(&ctl.o_full, (j - 1) & 1, abort_flag);
@@ -507,7 +477,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       tc_fence_before_sync();       // the loads of S are done before the next S may be written
       fence_async_proxy();          // P is visible to the tensor core
       mbar_arrive(&ctl.p_ready);
-      if (j == 2) TL(4);
     }
     if (ok && n_tiles > 0) {
       ok = mbar_wait(&ctl.o_full, (n_tiles - 1) & 1, abort_flag);
@@ -516,7 +485,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         fold(alpha);
       }
     }
-    TL(7);
     // A shared tile is finished by both blocks, each for half of the head's columns: a block
     // leaves its (maximum, sum) and the other half's output registers in its own K/V stages
     // (free once its last MMA is done, which its threads have waited for), tells its partner and
@@ -538,9 +506,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         land[(c + 1) * SOFTMAX_THREADS + st] = give0 == 0 ? lo4 : hi4;
       }
       mbar_arrive_peer(map_to_peer(&ctl.land_full, (uint32_t)(rank ^ 1)));
-      TL(8);
       const bool there = mbar_wait_cluster(&ctl.land_full, 0, abort_flag);
-      TL(9);
       if (there) {
         const uint32_t src = map_to_peer(land, (uint32_t)(rank ^ 1)) + (uint32_t)st * 16u;
         const uint4 ml = ld_peer_v4(src);
@@ -576,7 +542,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       mbar_arrive_peer(map_to_peer(&ctl.land_free, (uint32_t)(rank ^ 1)));    // read (or given up)
     }
-    TL(10);
 #pragma unroll
     for (int x = 0; x < 2; x++) {
       l[x] += __shfl_xor_sync(0xffffffffu, l[x], 1);
@@ -596,14 +561,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     }
-    TL(11);
     // the partner reads this block's shared memory: stay until it has
     if (split) mbar_wait_cluster(&ctl.land_free, 0, abort_flag);
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  TLB(1);
   if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
   if (warp == MMA_WARP) {
     tc_fence_after_sync();
@@ -680,14 +643,6 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const Args& a, int R, 
 }
 }  // namespace
 
-#ifdef SGLC_TIMELINE
-SGLC_API int sglc_attention_prefill_timeline(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tl, sizeof(unsigned long long) * 16);
-}
-SGLC_API int sglc_attention_prefill_block_times(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tl_blocks, sizeof(unsigned long long) * 2 * 2048);
-}
-#endif
 
 // Tuning hook: key tiles from which a query tile is split over two blocks (default 5).
 static int g_split_min = 5;

@@ -59,33 +59,6 @@ struct GemmArgs {
   int tiles_p, n_tiles;    // many-token kernel: row tiles, and all tiles (a block walks several)
 };
 
-// Optional timeline for tuning (compile with -DSGLC_TIMELINE): block (0,0,0) stores the
-// nanosecond timer at a few points of each role into `a.err[16 + slot]`.
-#ifdef SGLC_TIMELINE
-#ifdef SGLC_TL_ONLY_N
-// inside a replayed graph: the launches with N == SGLC_TL_ONLY_N leave their marks in a global
-__device__ unsigned long long g_gemm_tl[16];
-__device__ __forceinline__ void tl_mark(const GemmArgs& a, int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && a.N == SGLC_TL_ONLY_N) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_gemm_tl[slot] = t;
-  }
-}
-#else
-__device__ __forceinline__ void tl_mark(const GemmArgs& a, int slot) {
-  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    ((unsigned long long*)(a.err + 16))[slot] = t;
-  }
-}
-#endif
-#define TL(slot) tl_mark(a, slot)
-#else
-#define TL(slot)
-#endif
-
 struct SharedCtl {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
@@ -182,7 +155,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   const int stages = a.stages;
 
   pdl_launch_dependents();
-  if (threadIdx.x == 0) TL(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) {
       mbar_init(&ctl.full[s], 1);
@@ -205,7 +177,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl.tmem_base;
   volatile int* abort_flag = &ctl.abort_flag;
-  if (threadIdx.x == 0) TL(1);
   // split-K partial sums arrive here from the other blocks of the cluster at any time, so the
   // area is apart from the stage buffers (which this block's MMAs may still be reading)
   float* red_buf = reinterpret_cast<float*>(smem + (size_t)stages * STAGE_BYTES);
@@ -222,14 +193,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           mbar_expect_tx(&ctl.full[i], STAGE_BYTES);
           tma_load_2d(smem + (size_t)i * STAGE_BYTES, &map_p, &ctl.full[i], (kb0 + i) * BK, pt * BM);
         }
-        TL(2);
         pdl_wait();
-        TL(3);
         for (int i = 0; i < n_first; i++)
           tma_load_2d(smem + (size_t)i * STAGE_BYTES + P_BYTES, &map_q, &ctl.full[i], (kb0 + i) * BK,
                       qt * BN);
         issued = n_first;
-        TL(4);
       } else {
         pdl_wait();
       }
@@ -257,7 +225,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         int s = i % stages;
         ok = mbar_wait(&ctl.full[s], (i / stages) & 1, abort_flag);
         if (!ok) break;
-        if (i == 0) TL(5);
         tc_fence_after_sync();
         uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
         uint64_t dp = smem_desc_k_sw128(sp);
@@ -270,7 +237,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         mma_commit(&ctl.empty[s]);    // the stage is free once these MMAs have read it
       }
       if (ok) mma_commit(&ctl.accum);   // accumulator complete
-      TL(6);
     }
   } else {
     // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
@@ -308,7 +274,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       }
     }
     bool ok = n_kb > 0 ? mbar_wait(&ctl.accum, 0, abort_flag) : true;
-    if (threadIdx.x == 64) TL(7);
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16);
     constexpr int CH = BN < 32 ? 16 : 32;
@@ -411,7 +376,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         for (int j = 0; j < CH; j += 4)
           st_peer_v4(remote + (uint32_t)(c + j) * 4u, r[j], r[j + 1], r[j + 2], r[j + 3]);
       }
-      if (threadIdx.x == 64) TL(8);
     }
     if (a.splits > 1) {
       // one cluster barrier: every block's partial sums are where they are summed.  Nothing
@@ -420,7 +384,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
       cluster_arrive();
       cluster_wait();
       ok = ok && !ctl.abort_flag;
-      if (threadIdx.x == 64) TL(9);
       if (ok) {
         const float* buf = red_buf;
         // a thread sums four consecutive columns of one row at a time (16-byte reads of every
@@ -458,7 +421,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
           }
         }
       }
-      if (threadIdx.x == 64) TL(10);
     }
   }
   if (a.splits > 1 && warp < 2) {
@@ -466,7 +428,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     cluster_arrive();        // the producer and MMA warps take part in the cluster barrier too
     cluster_wait();
   }
-  if (threadIdx.x == 64) TL(11);
 
   tc_fence_before_sync();
   __syncthreads();
@@ -513,7 +474,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint8_t* epi = smem + (size_t)stages * STAGE_BYTES;       // two boxes
 
   pdl_launch_dependents();
-  if (threadIdx.x == 0) TL(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; s++) {
       mbar_init(&ctl.full[s], 1);
@@ -545,9 +505,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (warp == 0) {
     // ---- TMA producer: one ring of stages across all of the block's tiles ----
     if (elect_one()) {
-      TL(1);
       pdl_wait();
-      TL(2);
       int kc = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < a.n_tiles && ok; t += gridDim.x) {
@@ -589,7 +547,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const int s = kc % stages;
           ok = mbar_wait(&ctl.full[s], (kc / stages) & 1, abort_flag);
           if (!ok) break;
-          if (kc == 0) TL(3);
           tc_fence_after_sync();
           const uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint64_t da = smem_desc_k_sw128(sp);
@@ -600,7 +557,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           mma_commit(&ctl.empty[s]);
         }
         if (ok) mma_commit(&ctl.acc_full[buf]);
-        if (n < 3) TL(4 + n);
       }
     }
   } else {
@@ -621,7 +577,6 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       tc_fence_after_sync();
       // one thread decides for all whether the tile is finished or given up (a wait ran out
       // somewhere in the block): the barriers below need every thread on the same side
-      if (threadIdx.x == 64 && n < 2) TL(7 + 2 * n);
       if (threadIdx.x == 64) s_go[buf] = (ok && *abort_flag == 0) ? 1 : 0;
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
       ok = s_go[buf] != 0;
@@ -695,9 +650,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           epilogue_store<BN>(a, p_glob, qt * BN + c, v, 32);
         }
       }
-      if (threadIdx.x == 64 && n < 3) TL(n == 0 ? 8 : (n == 1 ? 10 : 11));
     }
-    if (threadIdx.x == 64) TL(12);
     if (threadIdx.x == 64) tma_store_wait_read();      // shared memory must outlive the last stores' reads
   }
   tc_fence_before_sync();
@@ -807,31 +760,16 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
 }
 }  // namespace
 
-#if defined(SGLC_TIMELINE) && defined(SGLC_TL_ONLY_N)
-SGLC_API int sglc_gemm_tc_timeline(unsigned long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_gemm_tl, sizeof(unsigned long long) * 16);
-}
-#endif
-
-// Tuning hook: the most K splits of the few-token orientation (0: the built-in choice).
-static int g_max_splits = 0;
-SGLC_API void sglc_gemm_tc_set_max_splits(int n) { g_max_splits = n; }
-// Tuning hook: more than 128 tokens go to the kernel whose blocks walk the tiles (1, default) or
-// to one block per tile (0).
-static int g_stream_kernel = 1;
-SGLC_API void sglc_gemm_tc_set_stream_kernel(int on) { g_stream_kernel = on; }
-
 // Orientation, tile width and K split for a problem size.
 // From 65 tokens on, a product over a short K goes to the many-token kernel although its one row
 // of tiles is half empty: the few-token orientation would split K over a cluster and pass
 // 128 x 128 partial sums, 64 KB a block, through distributed shared memory (measured at 96 and
 // 128 tokens: a decode step 15-17 % shorter; at 64 tokens and fewer the split wins or ties).
-static int g_direct_min_m = 65, g_direct_max_kb = 32;
-SGLC_API void sglc_gemm_tc_set_direct(int min_m, int max_kb) { g_direct_min_m = min_m; g_direct_max_kb = max_kb; }
+constexpr int DIRECT_MIN_M = 65, DIRECT_MAX_KB = 32;
 static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_per_split,
                  int* tiles_p, int* tiles_q) {
   int kb_total = (K + BK - 1) / BK;
-  if (M <= 128 && !(M >= g_direct_min_m && kb_total <= g_direct_max_kb)) {
+  if (M <= 128 && !(M >= DIRECT_MIN_M && kb_total <= DIRECT_MAX_KB)) {
     *swap = 1;
     *bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     *tiles_p = (N + BM - 1) / BM;
@@ -840,7 +778,6 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
     // last block's reduction stays short
     int want = (2 * 148) / (*tiles_p);
     if (want > 8) want = 8;
-    if (g_max_splits > 0 && want > g_max_splits) want = g_max_splits;
     if (want < 1) want = 1;
     if (want > kb_total) want = kb_total;
     int per = (kb_total + want - 1) / want;
@@ -850,21 +787,13 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
     *swap = 0;
     int tiles128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
     // a block of the many-token kernel walks its tiles one after the other: wide tiles (fewer
-    // bytes from L2 per flop) as soon as they occupy half of the SMs; one block per tile
-    // (the other kernel) wants a tile for every SM first
-    *bn = (tiles128 >= (g_stream_kernel ? 74 : 148) || N <= 64) ? 128 : 64;
+    // bytes from L2 per flop) as soon as they occupy half of the SMs
+    *bn = (tiles128 >= 74 || N <= 64) ? 128 : 64;
     *tiles_p = (M + BM - 1) / BM;
     *tiles_q = (N + *bn - 1) / *bn;
     *splits = 1;
     *kb_per_split = kb_total;
   }
-}
-
-// The plan the launcher would choose for (M,N,K): for tests and tuning.
-SGLC_API int sglc_gemm_tc_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
-  int per, tp, tq;
-  plan(M, N, K, swap, bn, splits, &per, &tp, &tq);
-  return SGLC_OK;
 }
 
 // A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
@@ -905,7 +834,7 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
     if (residual) a.tma_out = get_map(&mo, residual, M, N, ldo, BM | 0x10000u) ? 1 : 0;
     else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
   }
-  if (!swap && g_stream_kernel) {
+  if (!swap) {
     a.tiles_p = tp;
     a.n_tiles = tp * tq;
     return bn == 128 ? launch_stream<128>(mp, mq, mo, a, stream) : launch_stream<64>(mp, mq, mo, a, stream);

@@ -64,12 +64,74 @@ def _category_of(plan, spec):
     raise WeightError("part spec does not belong to the plan")
 
 
+class ShardedWeights:
+    """The shards that `model.safetensors.index.json` names, seen as one file: its `weight_map`
+    gives the shard of every tensor (the reference resolves a folder the same way, index first:
+    src/safetensors.c:676-843).  A tensor the index names must be in the shard it names; tensors a
+    shard holds beyond the index are not visible."""
+
+    def __init__(self, model_dir, index_path):
+        import json
+        self.path = index_path
+        try:
+            with open(index_path) as f:
+                index = json.load(f)
+            wmap = index["weight_map"]
+            if not isinstance(wmap, dict) or not wmap:
+                raise KeyError("weight_map")
+        except (OSError, ValueError, KeyError, TypeError) as e:
+            raise WeightError(f"{index_path}: not a shard index with a weight_map ({e})") from None
+        self._files = {}
+        self._where = {}
+        try:
+            for name, shard in wmap.items():
+                if not isinstance(shard, str) or os.path.basename(shard) != shard:
+                    raise WeightError(f"{index_path}: shard name {shard!r} of tensor '{name}' must be a file name "
+                                      "in the same folder")
+                if shard not in self._files:
+                    sp = os.path.join(model_dir, shard)
+                    if not os.path.exists(sp):
+                        raise WeightError(f"{index_path} names shard {shard}, which is not in {model_dir}")
+                    self._files[shard] = SafetensorsFile(sp)
+                self._where[name] = self._files[shard]
+            lost = [n for n, f in self._where.items() if n not in set(f.names())]
+            if lost:
+                raise WeightError(f"{index_path}: tensors not found in the shard it names: " + ", ".join(sorted(lost)))
+        except SafetensorsError as e:
+            self.close()
+            raise WeightError(str(e)) from None
+        except WeightError:
+            self.close()
+            raise
+
+    def names(self):
+        return list(self._where)
+
+    def shape(self, name):
+        return self._where[name].shape(name)
+
+    def dtype(self, name):
+        return self._where[name].dtype(name)
+
+    def tensor(self, name):
+        return self._where[name].tensor(name)
+
+    def close(self):
+        for f in self._files.values():
+            f.close()
+
+
 def open_weights(model_dir):
+    """(weights, path for messages): the shards of model.safetensors.index.json if the folder
+    has that index, else model.safetensors."""
+    index = os.path.join(model_dir, "model.safetensors.index.json")
+    if os.path.exists(index):
+        return ShardedWeights(model_dir, index), index
     path = os.path.join(model_dir, "model.safetensors")
     if not os.path.exists(path):
-        raise WeightError(f"no model.safetensors in {model_dir}")
+        raise WeightError(f"no model.safetensors (or model.safetensors.index.json) in {model_dir}")
     try:
-        return SafetensorsFile(path)
+        return SafetensorsFile(path), path
     except SafetensorsError as e:
         raise WeightError(str(e)) from None
 
@@ -77,7 +139,7 @@ def open_weights(model_dir):
 def load_checked(plan, model_dir):
     """{declared name: TensorRef} after checking the file against the plan."""
     need = required_tensors(plan)
-    f = open_weights(model_dir)
+    f, where = open_weights(model_dir)
     try:
         names = set(f.names())
         found = {}
@@ -104,7 +166,7 @@ def load_checked(plan, model_dir):
             if not any(fnmatch.fnmatchcase(bare, pat) for pat in plan.ignorable):
                 unexpected.append(n)
         if missing or wrong or unexpected:
-            lines = [f"{os.path.join(model_dir, 'model.safetensors')} does not fit the model:"]
+            lines = [f"{where} does not fit the model:"]
             if missing:
                 lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(sorted(missing)))
             if unexpected:

@@ -149,3 +149,50 @@ def test_random_weights_are_seeded_and_follow_the_scheme(tmp_path):
     # the written config reads back to the same configuration
     from sglang_c_b200.config import load_config
     assert load_config(str(tmp_path / "a"))[1] == cfg
+
+
+def test_sharded_checkpoint_through_its_index(tmp_path):
+    """model.safetensors.index.json -> shards (reference src/safetensors.c:676-843): the same
+    tensors load from hand-written shards; a shard or a tensor the index names and the folder
+    lacks is one clear error."""
+    arch, cfg, plan = _plan(TINY_A)
+    whole = write_random_model(str(tmp_path / "whole"), arch, cfg, 3, scheme="varied")
+    with SafetensorsFile(os.path.join(whole, "model.safetensors")) as f:
+        tensors = {n: f.tensor(n).clone() for n in f.names()}
+    names = sorted(tensors)
+    d = tmp_path / "sharded"
+    d.mkdir()
+    parts = [names[0::3], names[1::3], names[2::3]]
+    wmap = {}
+    for i, part in enumerate(parts):
+        shard = f"model-{i + 1:05d}-of-00003.safetensors"
+        write_safetensors(str(d / shard), {n: tensors[n] for n in part})
+        wmap.update({n: shard for n in part})
+    with open(d / "config.json", "w") as f:
+        json.dump(cfg.to_dict(), f)
+    with open(d / "model.safetensors.index.json", "w") as f:
+        json.dump({"metadata": {"total_size": 0}, "weight_map": wmap}, f)
+    refs = load_checked(plan, str(d))
+    assert sorted(refs) == sorted(required_tensors(plan))
+    for n, r in refs.items():
+        assert torch.equal(r.tensor, tensors[r.name])
+    # a tensor the index sends to the wrong shard
+    bad = dict(wmap)
+    bad[names[0]] = wmap[names[1]]
+    with open(d / "model.safetensors.index.json", "w") as f:
+        json.dump({"weight_map": bad}, f)
+    with pytest.raises(WeightError, match="not found in the shard"):
+        load_checked(plan, str(d))
+    # a shard that is not there
+    bad = dict(wmap)
+    bad[names[0]] = "model-00009-of-00003.safetensors"
+    with open(d / "model.safetensors.index.json", "w") as f:
+        json.dump({"weight_map": bad}, f)
+    with pytest.raises(WeightError, match="names shard"):
+        load_checked(plan, str(d))
+    # a tensor missing from the index is reported like any missing tensor
+    less = {n: s for n, s in wmap.items() if n != "ln_f.bias"}
+    with open(d / "model.safetensors.index.json", "w") as f:
+        json.dump({"weight_map": less}, f)
+    with pytest.raises(WeightError, match=r"missing tensors \(1\): ln_f.bias"):
+        load_checked(plan, str(d))

@@ -42,20 +42,44 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
         ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], want, H, scale,
                              window, max(lens))
         ref = _attention_reference(c, H, Hkv, D, scale, window)
-        before = torch.cuda.memory_allocated()
-        outs = []
-        for _ in range(2):                       # two calls in a row share the scratch
-            out = torch.full_like(want, float("nan"))
-            alloc0 = torch.cuda.memory_allocated()
+        outs = [torch.full_like(want, float("nan")) for _ in range(3)]
+        # a first call looks the scratch's address up; what the device has free is read after it,
+        # from the driver (cudaMemGetInfo: the caching allocator's own counters would not see a
+        # cudaMalloc made inside the library)
+        rc = _call(lib, c, outs[2], H, scale, window, max(lens), n_splits)
+        assert rc == 0, lib.sglc_attention_decode_noalloc_error(rc).decode()
+        torch.cuda.synchronize()
+        free0 = torch.cuda.mem_get_info()[0]
+        for out in outs[:2]:                     # two calls in a row share the scratch
             rc = _call(lib, c, out, H, scale, window, max(lens), n_splits)
             assert rc == 0, lib.sglc_attention_decode_noalloc_error(rc).decode()
-            torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == alloc0
-            outs.append(out)
+        assert lib.sglc_attention_decode_noalloc_check(
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+        assert torch.cuda.mem_get_info()[0] == free0, "the device's free memory moved during the calls"
+        outs = outs[:2]
         for out in outs:
             assert float((out.float() - want.float()).abs().max()) < TOL
             assert float((out.double().cpu() - ref).abs().max()) < TOL
         assert torch.equal(outs[0], outs[1])
+
+
+def test_no_alloc_entry_point_flags_a_position_beyond_max_keys():
+    """A caller's max_keys smaller than a token's position + 1: that token's rows are zeros and the
+    status word says so; the other token is computed as ever."""
+    from sglang_c_b200.csrc import build, ops
+    lib = build.load("attention_decode")
+    H, Hkv, D, ps = 4, 2, 64, 16
+    c = _paged_case([200, 40], [1, 1], H, Hkv, D, ps, torch.bfloat16, seed=9)
+    scale = 1.0 / math.sqrt(D)
+    want = torch.empty(2, H * D, dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode(c["q"], c["cache"], c["bt"], c["token_req"], c["positions"], want, H, scale, None, 200)
+    out = torch.full_like(want, float("nan"))
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert _call(lib, c, out, H, scale, None, 48, 2) == 0          # 48 keys cover the second token only
+    assert lib.sglc_attention_decode_noalloc_check(stream) == -12
+    assert lib.sglc_attention_decode_noalloc_check(stream) == 0     # cleared by the report
+    assert float(out[0].float().abs().max()) == 0.0
+    assert float((out[1].float() - want[1].float()).abs().max()) < TOL
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():

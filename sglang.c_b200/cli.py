@@ -50,7 +50,9 @@ def build_parser():
 
 
 def main(argv=None):
+    from . import log
     args = build_parser().parse_args(argv)
+    log.set_level(log.DEBUG if args.verbose else log.INFO)
     if args.device not in ("cuda", "auto") and not args.device.startswith("cuda:"):
         raise SystemExit(f"unknown --device '{args.device}' (this engine runs on cuda only)")
     device = "cuda:0" if args.device in ("cuda", "auto") else args.device
@@ -69,7 +71,7 @@ def main(argv=None):
             model_dir = tempfile.mkdtemp(prefix="sglc_random_")
             atexit.register(shutil.rmtree, model_dir, True)
         write_random_model(model_dir, arch, cfg, args.random_weights, scheme=args.init)
-        print(f"[sglc] wrote random weights (seed {args.random_weights}) to {model_dir}", file=sys.stderr)
+        log.info(f"wrote random weights (seed {args.random_weights}) to {model_dir}")
     if not model_dir:
         build_parser().print_usage(sys.stderr)
         return 1
@@ -89,8 +91,8 @@ def main(argv=None):
                   n_pages=args.pages, max_tokens=None if args.pages else max(need, 64) + args.page_size,
                   max_requests=4, max_step_tokens=args.token_budget, prefill_chunk=args.chunk,
                   token_budget=args.token_budget)
-    if args.verbose:
-        print(f"[sglc] model loaded in {time.time() - t0:.2f}s", file=sys.stderr)
+    log.debug(f"model loaded in {time.time() - t0:.2f}s ({s.engine.model.weight_bytes / 1e6:.1f} MB of weights, "
+              f"{s.engine.cache.n_pages} pages of {s.engine.page_size})")
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                         min_p=args.min_p, repetition_penalty=args.repetition_penalty,
                         ignore_eos=args.ignore_eos, seed=args.seed)
@@ -99,10 +101,9 @@ def main(argv=None):
     dt = time.time() - t1
     print(" ".join(str(t) for t in prompt + out))
     n = len(out)
-    print(f"generated {n} tokens in {dt:.2f}s ({n / dt if dt > 0 else 0:.1f} tok/s, "
-          f"{dt * 1000 / max(n, 1):.0f} ms/tok)", file=sys.stderr)
-    if args.verbose:
-        print(f"[sglc] stats: {s.get_stats()}", file=sys.stderr)
+    log.info(f"generated {n} tokens in {dt:.2f}s ({n / dt if dt > 0 else 0:.1f} tok/s, "
+             f"{dt * 1000 / max(n, 1):.0f} ms/tok)")
+    log.debug(f"stats: {s.get_stats()}")
     return 0
 
 

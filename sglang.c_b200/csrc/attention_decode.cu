@@ -81,7 +81,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                         int use_cluster, float* __restrict__ ws, int* __restrict__ counters,
                         const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
                         int new_stride, const int* __restrict__ slots, int nb_max, int* __restrict__ err,
-                        const int* __restrict__ token_list) {
+                        const int* __restrict__ token_list, int n_pages) {
   extern __shared__ float smem[];
   __shared__ float red[33];
   __shared__ int s_last;
@@ -139,6 +139,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     return;
   }
+#ifdef SGLC_BOUNDS_CHECK
+  // the page ids this token's keys lie in, against the pool's size (see common.cuh)
+  for (int i = lo / page_size + tid; i <= pos / page_size; i += THREADS)
+    if (!sglc_index_ok(spage[i], n_pages, err)) spage[i] = 0;
+  __syncthreads();
+#endif
   const int k0 = lo + sp * chunk;
   int k1 = k0 + chunk;
   if (k1 > pos + 1) k1 = pos + 1;
@@ -476,7 +482,7 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                                    int Hkv, int D, int page_size, float scale, int window,
                                    int max_keys, int n_splits, float* ws, int* counters,
                                    const void* k_new, const void* v_new, int new_stride,
-                                   const int* slots, int* err, const int* token_list,
+                                   const int* slots, int* err, const int* token_list, int n_pages,
                                    cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || page_size <= 0 || max_keys <= 0 || n_splits < 1)
@@ -504,7 +510,7 @@ SGLC_API int sglc_attention_decode(const void* q, int q_stride, void* cache,
                      (__nv_bfloat16*)cache, block_table, bt_stride, token_req, positions,
                      (__nv_bfloat16*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_splits,
                      chunk_cap, use_cluster, ws, counters, (const __nv_bfloat16*)k_new,
-                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err, token_list);
+                     (const __nv_bfloat16*)v_new, new_stride, slots, nb_max, err, token_list, n_pages);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -615,6 +621,6 @@ SGLC_API int sglc_attention_decode_noalloc(const void* q, int q_stride, const vo
       /*k_new=*/(const __nv_bfloat16*)nullptr, /*v_new=*/(const __nv_bfloat16*)nullptr, 0,
       /*slots=*/(const int*)nullptr, nb_max,
       /*err=*/reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(base) + NOALLOC_STATUS_OFFSET),
-      /*token_list=*/(const int*)nullptr);
+      /*token_list=*/(const int*)nullptr, /*n_pages=*/0x7fffffff);
   return sglc_launch_status();
 }

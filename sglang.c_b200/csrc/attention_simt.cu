@@ -19,7 +19,7 @@ __global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
                                       const int* __restrict__ token_req,
                                       const int* __restrict__ positions, TO* __restrict__ out,
                                       int o_stride, int T, int H, int Hkv, int D, int page_size,
-                                      float scale, int window, int max_keys) {
+                                      float scale, int window, int max_keys, int n_pages, int* err) {
   extern __shared__ float smem[];
   __shared__ float red[33];
   int t = blockIdx.x, h = blockIdx.y;
@@ -48,9 +48,11 @@ __global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     int p = lo + i;
     int page = bt[p / page_size];
-    const TC* kp = cache + (size_t)page * page_elems + head_off + (size_t)(p % page_size) * D;
     float s = 0.0f;
-    for (int d = 0; d < D; d++) s = fmaf(sq[d], to_f32(kp[d]), s);
+    if (sglc_index_ok(page, n_pages, err)) {
+      const TC* kp = cache + (size_t)page * page_elems + head_off + (size_t)(p % page_size) * D;
+      for (int d = 0; d < D; d++) s = fmaf(sq[d], to_f32(kp[d]), s);
+    }
     s *= scale;
     sc[i] = s;
     lmax = fmaxf(lmax, s);
@@ -73,6 +75,7 @@ __global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
       for (int i = g; i < n; i += G) {
         int p = lo + i;
         int page = bt[p / page_size];
+        if (!sglc_index_ok(page, n_pages, nullptr)) continue;      // (flagged in the score pass)
         const TC* vp = cache + (size_t)page * page_elems + v_off + head_off +
                        (size_t)(p % page_size) * D;
         acc = fmaf(sc[i], to_f32(vp[d]), acc);
@@ -94,12 +97,13 @@ __global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
 // layer's pages; block_table: [n_requests][bt_stride] page ids; token_req[t]: row of the
 // block table for token t; positions[t]: absolute position of token t (its own key is the
 // last one it sees); out: [T][o_stride].  max_keys: the most keys any token of this launch
-// sees (sizes shared memory).  q/out dtype = act_dtype, cache dtype = cache_dtype.
+// sees (sizes shared memory).  q/out dtype = act_dtype, cache dtype = cache_dtype.  n_pages and
+// err serve the bounds-check build (page ids are compared with n_pages; err gets the flag).
 SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
                                  const int* block_table, int bt_stride, const int* token_req,
                                  const int* positions, void* out, int o_stride, int T, int H,
                                  int Hkv, int D, int page_size, float scale, int window,
-                                 int max_keys, int act_dtype, int cache_dtype,
+                                 int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
                                  cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || page_size <= 0 || max_keys <= 0)
@@ -119,7 +123,7 @@ SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
     attention_simt_kernel<TQ, TC, TO><<<grid, threads, smem, stream>>>(                      \
         (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions, \
-        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, max_keys);               \
+        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, max_keys, n_pages, err); \
   } while (0)
   if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32)
     LAUNCH(float, float, float);

@@ -17,6 +17,8 @@ import tempfile
 import threading
 import time
 
+from .. import log
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 # no fast-math: the 32-bit path relies on IEEE division, sqrt and expf
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -24,6 +26,21 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 _lock = threading.RLock()
 _loaded = {}
+_bounds_check = False
+
+
+def set_bounds_check(on):
+    """From now on load the bounds-check build of every kernel library (compiled with
+    -DSGLC_BOUNDS_CHECK into files of their own): indices that kernels take from device memory
+    are compared with their ranges before use, see common.cuh.  For tests and for hunting a bad
+    index where no memory checker can be run; the ordinary build is what serves."""
+    global _bounds_check
+    with _lock:
+        _bounds_check = bool(on)
+
+
+def _flags():
+    return NVCC_FLAGS + (["-DSGLC_BOUNDS_CHECK"] if _bounds_check else [])
 
 
 class BuildError(RuntimeError):
@@ -66,7 +83,7 @@ def _build_dir():
 
 def _digest(name):
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     for fn in sorted(os.listdir(_HERE)):
         if fn == name + ".cu" or fn.endswith(".cuh"):
             with open(os.path.join(_HERE, fn), "rb") as f:
@@ -76,7 +93,7 @@ def _digest(name):
 
 
 def lib_path(name):
-    return os.path.join(_build_dir(), f"libsglc_{name}.so")
+    return os.path.join(_build_dir(), f"libsglc_{name}{'_chk' if _bounds_check else ''}.so")
 
 
 def build(name, verbose=False):
@@ -92,29 +109,27 @@ def build(name, verbose=False):
             if f.read().strip() == want:
                 return out
     tmp = out + f".tmp{os.getpid()}_{threading.get_ident()}"
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", _HERE, "-o", tmp, src]
+    cmd = [_nvcc()] + _flags() + ["-I", _HERE, "-o", tmp, src]
     t0 = time.time()
-    print(f"[sglc_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+    log.info(f"compiling {name}.cu for sm_100a ...", always=True)
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             cwd=os.path.dirname(out))
     while True:
         try:
-            log, _ = proc.communicate(timeout=5)
+            out_text, _ = proc.communicate(timeout=5)
             break
         except subprocess.TimeoutExpired:
-            print(f"[sglc_b200] ... still compiling {name}.cu ({time.time() - t0:.0f} s)",
-                  file=sys.stderr, flush=True)
+            log.info(f"... still compiling {name}.cu ({time.time() - t0:.0f} s)", always=True)
     if proc.returncode != 0:
         if os.path.exists(tmp):
             os.remove(tmp)
-        raise BuildError(f"nvcc failed on {name}.cu:\n{log}")
+        raise BuildError(f"nvcc failed on {name}.cu:\n{out_text}")
     os.replace(tmp, out)
     with open(stamp, "w") as f:
         f.write(want)
-    print(f"[sglc_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
-          file=sys.stderr, flush=True)
-    if verbose and log.strip():
-        print(log, file=sys.stderr)
+    log.info(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s", always=True)
+    if verbose and out_text.strip():
+        log.info(out_text, always=True)
     return out
 
 
@@ -147,7 +162,8 @@ def build_all(names=None, jobs=None):
 def load(name):
     """The ctypes handle of csrc/<name>.cu's library, built first if needed."""
     with _lock:
-        lib = _loaded.get(name)
+        key = (name, _bounds_check)
+        lib = _loaded.get(key)
         if lib is None:
             path = build(name)
             try:
@@ -156,5 +172,5 @@ def load(name):
                 raise BuildError(f"cannot load {path}: {e}") from None
             lib.sglc_error_string.restype = ctypes.c_char_p
             lib.sglc_error_string.argtypes = [ctypes.c_int]
-            _loaded[name] = lib
+            _loaded[key] = lib
         return lib

@@ -60,6 +60,22 @@ static inline int sglc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return (int)cudaGetLastError();
 }
 
+// The bounds-check build (-DSGLC_BOUNDS_CHECK, see build.set_bounds_check): every index that a
+// kernel takes from device memory (a page id out of a block table, a cache slot, a row number) is
+// compared with its range before it is used; an index outside is not dereferenced: the access is
+// skipped and the error word gets SGLC_FLAG_INDEX.  (The stand-in for a memory checker where none
+// can be run; the ordinary build trusts what the host validated when it built the step.)
+enum { SGLC_FLAG_WAIT = 1, SGLC_FLAG_INDEX = 4 };
+#ifdef SGLC_BOUNDS_CHECK
+__device__ __forceinline__ bool sglc_index_ok(long long i, long long n, int* err) {
+  if (i >= 0 && i < n) return true;
+  if (err) atomicOr(err, SGLC_FLAG_INDEX);
+  return false;
+}
+#else
+__device__ __forceinline__ bool sglc_index_ok(long long, long long, int*) { return true; }
+#endif
+
 #define SGLC_DEFINE_ERROR_STRING()                                            \
   SGLC_API void sglc_set_pdl(int on) { g_sglc_pdl = on; }                     \
   SGLC_API const char* sglc_error_string(int code) {                          \

@@ -227,7 +227,7 @@ def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, sc
                                    block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
                                    out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
                                    int(window or 0), int(max_keys), _dt(q, "attention q"),
-                                   _dt(cache, "cache"), _stream())
+                                   _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)), _stream())
     _check(lib, code, f"attention_simt (head_dim {D}, up to {max_keys} keys)")
 
 
@@ -431,7 +431,7 @@ def attention_decode(q, cache, block_table, token_req, positions, out, n_heads, 
                                      out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
                                      int(window or 0), int(max_keys), splits, _ptr(ws), _ptr(counters),
                                      _ptr(k_new), _ptr(v_new), new_stride, _ptr(slots), _ptr(err),
-                                     _ptr(token_list), _stream())
+                                     _ptr(token_list), n_pages, _stream())
     _check(lib, code, f"attention_decode (head_dim {D}, up to {max_keys} keys)")
 
 

@@ -491,9 +491,12 @@ class Engine:
         if int(self.err_flag.item()) != 0:
             self.err_flag.zero_()
             raise RuntimeError("a kernel met an out-of-range token or position id")
-        if self.rt.dtype == "bfloat16":
-            from ..csrc import ops
-            flag = ops.tc_error_flag(self.rt.device)
-            if int(flag.item()) != 0:
-                flag.zero_()
-                raise RuntimeError("a tensor-core kernel gave up on a bounded wait; its output is invalid")
+        from ..csrc import ops
+        flag = ops.tc_error_flag(self.rt.device)
+        word = int(flag.item())
+        if word != 0:
+            flag.zero_()
+            if word & 4:
+                raise RuntimeError("a kernel of the bounds-check build met an index outside its range "
+                                   "(a page id beyond the pool); the access was skipped, the output is invalid")
+            raise RuntimeError("a tensor-core kernel gave up on a bounded wait; its output is invalid")

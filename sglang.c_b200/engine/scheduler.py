@@ -27,6 +27,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import List, Optional
 
+from .. import log
 from ..sampling import Sampler, SamplingParams, request_stream, uniform
 from .engine import Engine, OutOfPages
 from .step import StepEntry
@@ -174,6 +175,7 @@ class Scheduler:
         self.stats.n_finished += 1
 
     def _preempt(self, r):
+        log.debug(f"pages short: request {r.id} gives back {r.n_computed} positions and waits")
         self.engine.end_request(r.id)
         self.running.remove(r)
         self.stats.recomputed_tokens += r.n_computed

@@ -103,3 +103,24 @@ def test_another_architecture_can_be_registered():
     register_architecture("ToyForTest", GPT2Config, build_plan, model_types=("toy",))
     assert resolve_architecture({"architectures": ["ToyForTest"]}).name == "ToyForTest"
     assert resolve_architecture({"model_type": "toy"}).name == "ToyForTest"
+
+
+def test_log_lines_have_the_reference_format_and_honour_the_level():
+    import re
+    from sglang_c_b200 import log
+    lines = []
+    log.set_sink(lines.append)
+    before = log.get_level()
+    try:
+        log.set_level("WARN")
+        log.info("not shown")
+        log.warn("pool nearly full")
+        log.info("always", always=True)
+        log.set_level(log.DEBUG)
+        log.debug("now shown")
+    finally:
+        log.set_level(before)
+        log.set_sink(None)
+    assert len(lines) == 3
+    assert re.match(r"^\d\d:\d\d:\d\d\.\d{3} WARN test_config\.py:\d+\] pool nearly full$", lines[0])
+    assert " INFO " in lines[1] and lines[2].endswith("now shown")

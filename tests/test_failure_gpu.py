@@ -30,3 +30,42 @@ def test_a_wait_that_runs_out_is_reported_and_the_engine_goes_on(model_dirs):
     after = eng.step([StepEntry("b", toks, [19])])
     assert torch.equal(before, after)
     eng.check_device_errors()
+
+
+def test_bounds_check_build_skips_and_flags_a_bad_page_id(model_dirs):
+    """The kernels built with bounds checks give the same logits as the ordinary build, and a page
+    id beyond the pool (put into the step's block table behind the engine's back, where only a
+    kernel can meet it) is skipped and reported instead of dereferenced."""
+    from sglang_c_b200.csrc import build
+    from sglang_c_b200.engine import Engine, StepEntry
+    toks = traces.random_tokens(2, 40, TINY["A"]["vocab_size"])
+    for dtype in ("float32", "bfloat16"):
+        d = model_dirs("A", dtype)
+        plain = Engine.from_dir(d, dtype=dtype, page_size=16, n_pages=8, max_requests=2, max_step_tokens=64)
+        plain.add_request("a")
+        want = plain.step([StepEntry("a", toks[:39], [38])]).clone()
+        want2 = plain.step([StepEntry("a", toks[39:], [0])]).clone()
+        build.set_bounds_check(True)
+        try:
+            eng = Engine.from_dir(d, dtype=dtype, page_size=16, n_pages=8, max_requests=2, max_step_tokens=64,
+                                  use_graphs=False)
+            eng.add_request("a")
+            assert torch.equal(eng.step([StepEntry("a", toks[:39], [38])]), want)
+            assert torch.equal(eng.step([StepEntry("a", toks[39:], [0])]), want2)
+            eng.check_device_errors()
+            # the next step's block table gets a page id far beyond the pool after the host's checks:
+            # the upload is what a kernel reads
+            upload = eng.bufs.upload
+
+            def corrupt(*a, **k):
+                eng.bufs.npview("bt0").reshape(eng.max_requests, eng.b_cap)[0, 0] = 1 << 20
+                return upload(*a, **k)
+
+            eng.bufs.upload = corrupt
+            eng.step([StepEntry("a", [toks[0]], [0])])
+            eng.bufs.upload = upload
+            with pytest.raises(RuntimeError, match="outside its range"):
+                eng.check_device_errors()
+            eng.check_device_errors()
+        finally:
+            build.set_bounds_check(False)

@@ -33,7 +33,7 @@ class OutOfPages(RuntimeError):
 
 class Engine:
     def __init__(self, plan, runtime, page_size=16, n_pages=None, max_tokens=None, max_requests=64,
-                 max_step_tokens=2048, model_dir=None, use_graphs=True):
+                 max_step_tokens=2048, model_dir=None, use_graphs=True, use_host_walker=True):
         self.rt = runtime
         self.plan = plan
         self.model = Model(plan, runtime)
@@ -69,6 +69,11 @@ class Engine:
         self._graphs = {}
         self._graph_seen = set()
         self.graph_replays = 0
+        # a model of built-in parts has its launches made by the C++ walker (engine/host_model.py);
+        # any other model, and use_host_walker=False, keep the Python forward pass
+        self.use_host_walker = bool(use_host_walker)
+        self._host = None
+        self._host_tried = False
 
     # -- construction ---------------------------------------------------------
     @classmethod
@@ -419,6 +424,12 @@ class Engine:
 
     def _forward(self, ctx, out):
         from ..csrc import ops
+        if self.use_host_walker and not self._host_tried:
+            from .host_model import HostModel
+            self._host_tried = True
+            self._host = HostModel.build(self.model, self.cache, self.page_size)
+        if self._host is not None and self.use_host_walker and ops._PROFILE is None:
+            return self._host.forward(ctx, self.ws, out)
         with ops.pinned_stream():        # one stream lookup for the pass's hundred launches
             return self.model.forward(ctx, self.cache, out)
 

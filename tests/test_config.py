@@ -124,3 +124,10 @@ def test_log_lines_have_the_reference_format_and_honour_the_level():
     assert len(lines) == 3
     assert re.match(r"^\d\d:\d\d:\d\d\.\d{3} WARN test_config\.py:\d+\] pool nearly full$", lines[0])
     assert " INFO " in lines[1] and lines[2].endswith("now shown")
+
+
+def test_walker_structures_match_the_c_side_and_every_launcher_binds():
+    """Runs without a GPU: loading the libraries and comparing structure sizes needs none."""
+    from sglang_c_b200.engine import host_model
+    lib = host_model._walker()
+    assert lib is host_model._walker()

@@ -85,7 +85,7 @@ def _digest(name):
     h = hashlib.sha256()
     h.update(" ".join(_flags()).encode())
     for fn in sorted(os.listdir(_HERE)):
-        if fn == name + ".cu" or fn.endswith(".cuh"):
+        if fn == name + ".cu" or fn.endswith((".cuh", ".h")):
             with open(os.path.join(_HERE, fn), "rb") as f:
                 h.update(fn.encode())
                 h.update(f.read())

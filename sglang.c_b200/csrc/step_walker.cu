@@ -20,62 +20,9 @@
 
 #include "common.cuh"
 
-extern "C" {
+#include "step_walker.h"
 
-// ---- the model, as the host needs it (filled by engine/host_model.py through ctypes) ----------
-struct WalkLinear {
-  const void* w;            // [N][K], the runtime's matrix precision
-  const float* bias;        // [N] or null
-  int N, K;
-};
-struct WalkNorm {
-  const float* gamma;
-  const float* beta;
-  float eps;
-  int size;
-};
-struct WalkLayer {
-  WalkNorm norm1, norm2;
-  WalkLinear qkv, out, up, down;
-  int n_heads, n_kv_heads, head_dim, window;    // window 0: none
-  float scale;
-  int act;                                      // SGLC_ACT_*
-  int inner_size, pad;
-};
-struct WalkCall {
-  int layer;                // index into layers
-  int group;                // cache group of the call
-  int write;                // the call owns its cache (writes keys and values)
-  int n_pages;
-  void* cache;              // [n_pages][2][Hkv][page_size][D]
-};
-struct WalkModel {
-  const void* table;        // token table [V][E]
-  const void* pos_table;    // [P][E] or null
-  const WalkLayer* layers;
-  const WalkCall* order;
-  WalkNorm final_norm;
-  WalkLinear head;
-  int vocab, n_positions, hidden, n_layers, n_calls, bf16, page_size, pad;
-};
-struct WalkStep {
-  const int* tokens; const int* positions; const int* token_req; const int* want_rows;
-  const int* q_start; const int* kv_len; const int* decode_tokens;
-  const int* const* block_tables;               // per cache group
-  const int* const* slots;                      // per cache group
-  unsigned char* workspace; long long workspace_bytes;
-  float* logits;                                // [n_want][vocab]
-  int* err_flag;                                // bad token or position ids
-  int* tc_err;                                  // the tensor-core kernels' error word
-  float* tc_ws; long long tc_ws_floats; int* tc_counters; int tc_n_counters;
-  int T, R, n_want, max_q_len, max_keys, n_decode, decode_ordered, few_ok, bt_stride;
-  int stream_min_items, use_tma_decode, few_max_tokens;
-  long long few_max_weight;
-  cudaStream_t stream;
-  long long launches;                           // out: kernels launched
-  long long workspace_peak;                     // out
-  char where[96];                               // out: the operation that failed
-};
+extern "C" {
 
 // ---- the launchers of the other libraries, bound at start-up --------------------------------------
 typedef int (*fn_embed)(const int*, const int*, const void*, const void*, float*, int, int, int, int, int, int*,

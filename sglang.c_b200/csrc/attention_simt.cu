@@ -1,95 +1,155 @@
-// Causal attention over the paged cache, one block per (token, head), for any
-// mix of prompt portions and single decoded tokens.  All arithmetic is 32-bit:
+// Causal attention over the paged cache for any mix of prompt portions and single decoded
+// tokens.  All arithmetic is 32-bit:
 //   s[p] = (q·K_p)*scale for the keys p the query may see (p <= its position,
 //   and p > position - window if a window is set); m = max s; e = exp(s-m);
 //   o = sum_p e[p]*V_p / sum_p e[p]
 // (reference src/gpt2.c:238-270; GPU twin k_attn, src/cuda_backend.cu:1600-1651).
-// The work of one (token, head) depends only on that token's position and its
-// request's pages, never on the rest of the batch, so the result is the same
-// however the tokens were cut into steps.  This is the kernel of the 32-bit
-// path and the general fallback of the bfloat16 path.
+// A (token, head) is one warp.  It takes its keys in tiles of 32 by absolute position (tile k
+// holds positions 32k..32k+31: a lane a key for the scores, the softmax statistics kept online
+// from tile to tile, then a lane per output dimension over the tile's values), so its order of
+// additions depends only on its own first and last visible key, never on the rest of the batch:
+// the result is the same, bit for bit, however the tokens were cut into steps.  The tokens of a
+// block that belong to one request share each tile of that request's keys and values in shared
+// memory (a block of eight consecutive tokens of a prompt portion reads them once instead of
+// eight times: the reference's kernel, one block per token, reads them per token).  This is the
+// kernel of the 32-bit path and the general fallback of the bfloat16 path.
 #include "common.cuh"
 
 SGLC_DEFINE_ERROR_STRING()
 
-template <typename TQ, typename TC, typename TO>
-__global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
-                                      const TC* __restrict__ cache,
-                                      const int* __restrict__ block_table, int bt_stride,
-                                      const int* __restrict__ token_req,
-                                      const int* __restrict__ positions, TO* __restrict__ out,
-                                      int o_stride, int T, int H, int Hkv, int D, int page_size,
-                                      float scale, int window, int max_keys, int n_pages, int* err) {
-  extern __shared__ float smem[];
-  __shared__ float red[33];
-  int t = blockIdx.x, h = blockIdx.y;
-  if (t >= T) return;
-  int G = blockDim.x / D;          // groups of D threads that split the keys in the value pass
-  if (G < 1) G = 1;
-  float* sq = smem;                // D
-  float* part = sq + D;            // G*D partial outputs
-  float* sc = part + G * D;        // scores, up to max_keys
-  int r = token_req[t];
-  int pos = positions[t];
-  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  int n = pos - lo + 1;
-  if (n > max_keys) n = max_keys;  // cannot happen when the host sized max_keys right
-  int hk = h / (H / Hkv);
-  const int* bt = block_table + (size_t)r * bt_stride;
-  size_t page_elems = (size_t)2 * Hkv * page_size * D;
-  size_t head_off = (size_t)hk * page_size * D;
-  size_t v_off = (size_t)Hkv * page_size * D;
+// Four consecutive cache elements as 32-bit floats, by one load (p is aligned to four elements).
+__device__ __forceinline__ void load4(const float* p, float* v) {
+  const float4 x = *reinterpret_cast<const float4*>(p);
+  v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+  const uint2 x = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
 
-  const TQ* qp = q + (size_t)t * q_stride + (size_t)h * D;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) sq[d] = to_f32(qp[d]);
+// W: tokens of a block (a warp each).  Threads beyond the tokens' warps only help to stage tiles.
+template <typename TQ, typename TC, typename TO, int W, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restrict__ cache,
+                      const int* __restrict__ block_table, int bt_stride,
+                      const int* __restrict__ token_req, const int* __restrict__ positions,
+                      TO* __restrict__ out, int o_stride, int T, int H, int Hkv, int D, int page_size,
+                      float scale, int window, int n_pages, int* err) {
+  extern __shared__ __align__(16) float smem[];
+  __shared__ int s_req[W], s_lo[W], s_pos[W];
+  const int DP = D + 1;                       // padded key rows: a lane a key without bank conflicts
+  float* Ks = smem;                           // [32][D+1]
+  float* Vs = Ks + 32 * DP;                   // [32][D]
+  float* qs = Vs + 32 * D;                    // [W][D]
+  float* pw = qs + W * D;                     // [W][32]: a tile's weights
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, hk = h / (H / Hkv);
+  const int t0 = blockIdx.x * W;
+  if (tid < W) {
+    const int t = t0 + tid;
+    const bool on = t < T;
+    const int pos = on ? positions[t] : -1;
+    s_req[tid] = on ? token_req[t] : -1;
+    s_pos[tid] = pos;
+    s_lo[tid] = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  }
+  if (warp < W && t0 + warp < T) {
+    const TQ* qp = q + (size_t)(t0 + warp) * q_stride + (size_t)h * D;
+    for (int d = lane; d < D; d += 32) qs[warp * D + d] = to_f32(qp[d]);
+  }
   __syncthreads();
+  const bool mine = warp < W && t0 + warp < T;
+  const int my_req = mine ? s_req[warp] : -2, my_lo = mine ? s_lo[warp] : 0, my_pos = mine ? s_pos[warp] : -1;
+  float m = -INFINITY, l = 0.0f;
+  float acc[8];                               // dims lane, lane + 32, ... of the output
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+  const size_t page_elems = (size_t)2 * Hkv * page_size * D;
+  const size_t head_off = (size_t)hk * page_size * D, v_off = (size_t)Hkv * page_size * D;
 
-  float lmax = -INFINITY;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    int p = lo + i;
-    int page = bt[p / page_size];
-    float s = 0.0f;
-    if (sglc_index_ok(page, n_pages, err)) {
-      const TC* kp = cache + (size_t)page * page_elems + head_off + (size_t)(p % page_size) * D;
-      for (int d = 0; d < D; d++) s = fmaf(sq[d], to_f32(kp[d]), s);
+  // The tokens of a block that belong to one request (a run: a request's tokens lie together)
+  // share the tiles of that request's keys and values; the runs of a block take turns.
+  for (int lead = 0; lead < W; lead++) {
+    const int rl = s_req[lead];
+    if (rl < 0 || (lead > 0 && s_req[lead - 1] == rl)) continue;         // not the start of a run
+    int lo_min = s_lo[lead], pos_max = s_pos[lead];
+    for (int w = lead + 1; w < W && s_req[w] == rl; w++) {
+      lo_min = min(lo_min, s_lo[w]);
+      pos_max = max(pos_max, s_pos[w]);
     }
-    s *= scale;
-    sc[i] = s;
-    lmax = fmaxf(lmax, s);
-  }
-  float m = block_max(lmax, red);
-  float lsum = 0.0f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float e = expf(sc[i] - m);
-    sc[i] = e;
-    lsum += e;
-  }
-  float total = block_sum(lsum, red);   // also orders the writes of sc before the reads below
-
-  int g = threadIdx.x / D, d0 = threadIdx.x % D;
-  if (blockDim.x < D) { g = 0; d0 = threadIdx.x; }
-  if (g < G) {
-    int dstep = blockDim.x < D ? blockDim.x : D;
-    for (int d = d0; d < D; d += dstep) {
-      float acc = 0.0f;
-      for (int i = g; i < n; i += G) {
-        int p = lo + i;
-        int page = bt[p / page_size];
-        if (!sglc_index_ok(page, n_pages, nullptr)) continue;      // (flagged in the score pass)
-        const TC* vp = cache + (size_t)page * page_elems + v_off + head_off +
-                       (size_t)(p % page_size) * D;
-        acc = fmaf(sc[i], to_f32(vp[d]), acc);
+    const int* bt = block_table + (size_t)rl * bt_stride;
+    for (int kt = lo_min / 32; kt <= pos_max / 32; kt++) {
+      const int key0 = kt * 32;
+      __syncthreads();                        // the tile before has been used by everybody
+      {
+        // THREADS/32 threads bring one key and its value: the page is looked up once a key, and a
+        // thread's loads do not depend on one another
+        constexpr int TPK = THREADS / 32;
+        const int j = tid / TPK, part = tid % TPK, p = key0 + j;
+        const TC* kp = nullptr;
+        if (p >= lo_min && p <= pos_max) {
+          const int page = bt[p / page_size];
+          if (sglc_index_ok(page, n_pages, err))
+            kp = cache + (size_t)page * page_elems + head_off + (size_t)(p % page_size) * D;
+        }
+        if (D % 4 == 0) {
+          for (int d = part * 4; d < D; d += 4 * TPK) {
+            float k4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, v4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (kp) {
+              load4(kp + d, k4);
+              load4(kp + v_off + d, v4);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) Ks[j * DP + d + i] = k4[i];
+            *reinterpret_cast<float4*>(&Vs[j * D + d]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
+          }
+        } else {
+          for (int d = part; d < D; d += TPK) {
+            Ks[j * DP + d] = kp ? to_f32(kp[d]) : 0.0f;
+            Vs[j * D + d] = kp ? to_f32(kp[v_off + d]) : 0.0f;
+          }
+        }
       }
-      part[g * D + d] = acc;
+      __syncthreads();
+      // a token takes the tile if it belongs to the run and the tile holds keys it may see
+      if (my_req == rl && key0 <= my_pos && key0 + 31 >= my_lo) {
+        const int key = key0 + lane;
+        const bool valid = key >= my_lo && key <= my_pos;
+        const float* qv = qs + warp * D;
+        const float* kr = Ks + lane * DP;
+        float sc = 0.0f;
+        for (int d = 0; d < D; d++) sc = fmaf(qv[d], kr[d], sc);
+        sc = valid ? sc * scale : -INFINITY;
+        const float m_new = fmaxf(m, warp_max(sc));
+        const float corr = expf(m - m_new);                             // (first tile: exp(-inf) = 0)
+        const float p = valid ? expf(sc - m_new) : 0.0f;
+        l = l * corr + warp_sum(p);
+        m = m_new;
+        pw[warp * 32 + lane] = p;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const int d = lane + 32 * i;
+          if (d < D) {
+            float a = acc[i] * corr;
+            for (int j = 0; j < 32; j++) a = fmaf(pw[warp * 32 + j], Vs[j * D + d], a);
+            acc[i] = a;
+          }
+        }
+        __syncwarp();
+      }
     }
   }
-  __syncthreads();
-  TO* op = out + (size_t)t * o_stride + (size_t)h * D;
-  float inv = 1.0f / total;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.0f;
-    for (int gg = 0; gg < G; gg++) acc += part[gg * D + d];
-    op[d] = from_f32<TO>(acc * inv);
+  if (mine) {
+    TO* op = out + (size_t)(t0 + warp) * o_stride + (size_t)h * D;
+    const float inv = 1.0f / l;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int d = lane + 32 * i;
+      if (d < D) op[d] = from_f32<TO>(acc[i] * inv);
+    }
   }
 }
 
@@ -97,40 +157,42 @@ __global__ void attention_simt_kernel(const TQ* __restrict__ q, int q_stride,
 // layer's pages; block_table: [n_requests][bt_stride] page ids; token_req[t]: row of the
 // block table for token t; positions[t]: absolute position of token t (its own key is the
 // last one it sees); out: [T][o_stride].  max_keys: the most keys any token of this launch
-// sees (sizes shared memory).  q/out dtype = act_dtype, cache dtype = cache_dtype.  n_pages and
-// err serve the bounds-check build (page ids are compared with n_pages; err gets the flag).
+// sees.  q/out dtype = act_dtype, cache dtype = cache_dtype.  n_pages and err serve the
+// bounds-check build (page ids are compared with n_pages; err gets the flag).  max_q_len: the
+// longest portion of the step (1: every request brings one token, and a block takes one token).
 SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
                                  const int* block_table, int bt_stride, const int* token_req,
                                  const int* positions, void* out, int o_stride, int T, int H,
                                  int Hkv, int D, int page_size, float scale, int window,
                                  int max_keys, int act_dtype, int cache_dtype, int n_pages, int* err,
-                                 cudaStream_t stream) {
+                                 int max_q_len, cudaStream_t stream) {
   if (T <= 0) return SGLC_OK;
   if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || D <= 0 || page_size <= 0 || max_keys <= 0)
     return SGLC_ERR_ARGUMENT;
-  if (H > 65535) return SGLC_ERR_UNSUPPORTED;
-  int threads = 128;
-  if (D > 128) threads = 256;
-  if (D > 256) return SGLC_ERR_UNSUPPORTED;
-  int G = threads / D < 1 ? 1 : threads / D;
-  size_t smem = ((size_t)D + (size_t)G * D + (size_t)max_keys) * sizeof(float);
-  if (smem > 220 * 1024) return SGLC_ERR_UNSUPPORTED;
-  dim3 grid(T, H);
-#define LAUNCH(TQ, TC, TO)                                                                   \
-  do {                                                                                       \
-    if (smem > 48 * 1024)                                                                    \
-      cudaFuncSetAttribute(attention_simt_kernel<TQ, TC, TO>,                                \
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
-    attention_simt_kernel<TQ, TC, TO><<<grid, threads, smem, stream>>>(                      \
-        (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions, \
-        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, max_keys, n_pages, err); \
+  if (H > 65535 || D > 256) return SGLC_ERR_UNSUPPORTED;
+  // single tokens of many requests share nothing: a token a block; portions: eight tokens a block
+  const bool single = max_q_len <= 1;
+  const int W = single ? 1 : 8;
+  const size_t smem = ((size_t)32 * (D + 1) + (size_t)32 * D + (size_t)W * D + (size_t)W * 32) * sizeof(float);
+  dim3 grid((T + W - 1) / W, H);
+#define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
+  do {                                                                                                 \
+    if (smem > 48 * 1024)                                                                              \
+      cudaFuncSetAttribute(attention_simt_kernel<TQ, TC, TO, WW, TH>,                                  \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
+    attention_simt_kernel<TQ, TC, TO, WW, TH><<<grid, TH, smem, stream>>>(                              \
+        (const TQ*)q, q_stride, (const TC*)cache, block_table, bt_stride, token_req, positions,        \
+        (TO*)out, o_stride, T, H, Hkv, D, page_size, scale, window, n_pages, err);                     \
   } while (0)
-  if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32)
-    LAUNCH(float, float, float);
-  else if (act_dtype == SGLC_BF16 && cache_dtype == SGLC_BF16)
-    LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
-  else
+  if (act_dtype == SGLC_F32 && cache_dtype == SGLC_F32) {
+    if (single) LAUNCH(float, float, float, 1, 128);
+    else LAUNCH(float, float, float, 8, 256);
+  } else if (act_dtype == SGLC_BF16 && cache_dtype == SGLC_BF16) {
+    if (single) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, 1, 128);
+    else LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, 8, 256);
+  } else {
     return SGLC_ERR_ARGUMENT;
+  }
 #undef LAUNCH
   return sglc_launch_status();
 }

@@ -210,9 +210,11 @@ def kv_write(k_src, v_src, cache, slots, n_kv_heads, head_dim):
 
 
 def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, scale, window,
-                   max_keys):
+                   max_keys, max_q_len=None):
     """Causal attention of T tokens over the paged cache, 32-bit arithmetic.
-    q: [T, n_heads*head_dim] view; out likewise; block_table int32 [R, max_blocks]."""
+    q: [T, n_heads*head_dim] view; out likewise; block_table int32 [R, max_blocks].
+    max_q_len: the longest portion among the tokens (1 when every request brings one token;
+    unknown: None); it only decides how many tokens share a block."""
     _need_cuda(q, cache, block_table, token_req, positions, out)
     for t, nm in ((block_table, "block_table"), (token_req, "token_req"), (positions, "positions")):
         _i32(t, nm)
@@ -227,7 +229,8 @@ def attention_simt(q, cache, block_table, token_req, positions, out, n_heads, sc
                                    block_table.stride(0), _ptr(token_req), _ptr(positions), _ptr(out),
                                    out.stride(0), T, n_heads, Hkv, D, page_size, ctypes.c_float(scale),
                                    int(window or 0), int(max_keys), _dt(q, "attention q"),
-                                   _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)), _stream())
+                                   _dt(cache, "cache"), n_pages, _ptr(tc_error_flag(q.device)),
+                                   int(max_q_len) if max_q_len else 2, _stream())
     _check(lib, code, f"attention_simt (head_dim {D}, up to {max_keys} keys)")
 
 

@@ -39,7 +39,7 @@ typedef int (*fn_gemm_few)(const void*, const void*, const float*, void*, float*
 typedef int (*fn_kv_write)(const void*, const void*, int, void*, const int*, int, int, int, int, int, int, int,
                            cudaStream_t);
 typedef int (*fn_attention_simt)(const void*, int, const void*, const int*, int, const int*, const int*, void*, int,
-                                 int, int, int, int, int, float, int, int, int, int, int, int*, cudaStream_t);
+                                 int, int, int, int, int, float, int, int, int, int, int, int*, int, cudaStream_t);
 typedef int (*fn_attention_prefill_tc)(const void*, int, const void*, const int*, int, const int*, const int*, void*,
                                        int, int, int, int, int, int, int, float, int, int, int, int, int*,
                                        cudaStream_t);
@@ -216,7 +216,7 @@ struct Walk {
       return;
     }
     check(g.attention_simt(q, stride, c.cache, bt, s.bt_stride, s.token_req, s.positions, o, o_stride, s.T, H, Hkv, D,
-                           ps, L.scale, L.window, s.max_keys, dt(), dt(), c.n_pages, s.tc_err, s.stream),
+                           ps, L.scale, L.window, s.max_keys, dt(), dt(), c.n_pages, s.tc_err, s.max_q_len, s.stream),
           "attention_simt");
   }
 

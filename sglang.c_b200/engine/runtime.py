@@ -87,4 +87,4 @@ class Runtime:
                                      n_tokens=ctx.n_decode)
             return
         ops.attention_simt(q, cache, grp.block_table, ctx.token_req, ctx.positions, out, n_heads,
-                           scale, window, ctx.max_keys)
+                           scale, window, ctx.max_keys, max_q_len=ctx.max_q_len)

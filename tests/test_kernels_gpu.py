@@ -67,7 +67,8 @@ def test_layernorm(n, E, eps, out_dtype):
 
 
 @pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (65, 129, 100), (130, 50257 // 16, 96), (3, 320, 1600)])
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (5, 70, 33), (65, 129, 100), (130, 50257 // 16, 96), (3, 320, 1600),
+                                   (16, 1571, 772), (9, 40, 4), (1500, 1200, 200), (1155, 2304, 100)])
 def test_gemm_simt(M, N, K, in_dtype):
     ops = _ops()
     a, w, bias = _rand(M, K, dtype=in_dtype, seed=7), _rand(N, K, dtype=in_dtype, seed=8, scale=0.1), _rand(N, seed=9)
@@ -94,6 +95,21 @@ def test_gemm_simt(M, N, K, in_dtype):
     wide = _rand(M, K + 24, dtype=in_dtype, seed=11)
     ops.gemm_simt(wide[:, 8:8 + K], w, None, out=out)
     assert float((out.double() - wide[:, 8:8 + K].double() @ w.double().t()).abs().max()) < tol
+
+
+def test_gemm_simt_same_bits_at_every_row_count():
+    """The 32-bit product has a kernel for few rows, one for many rows and many features, and one
+    between; a row's outputs have the same bits from each of them (one accumulator per output,
+    k ascending), so that a token's logits do not depend on how many tokens its step brought."""
+    ops = _ops()
+    N, K = 1571, 772
+    a, w, bias = _rand(1400, K, seed=21), _rand(N, K, seed=22, scale=0.1), _rand(N, seed=23)
+    whole = torch.empty(1400, N, device=DEV)
+    ops.gemm_simt(a, w, bias, out=whole, act="gelu_tanh")        # 128 x 128 blocks
+    for lo, n in ((0, 1), (3, 8), (1384, 16), (100, 17), (640, 64), (700, 65), (0, 700)):
+        part = torch.empty(n, N, device=DEV)
+        ops.gemm_simt(a[lo:lo + n], w, bias, out=part, act="gelu_tanh")
+        assert torch.equal(part, whole[lo:lo + n]), (lo, n)
 
 
 def _paged_case(lens, q_lens, H, Hkv, D, page_size, dtype, seed, n_pages_extra=3, far_key=None):

@@ -1,7 +1,7 @@
 """Builds the CUDA sources of this folder for sm_100a, one shared library per
 .cu file, on first use, and loads them with ctypes.
 
-A library is rebuilt when its source, `common.cuh` or the flags change (a hash
+A library is rebuilt when its source, a header of this folder or the flags change (a hash
 is stored beside it).  Libraries are kept in-tree under `csrc/_build/`; if that
 folder cannot be written they go to a per-user folder under the system's
 temporary directory.  While nvcc runs, a line is printed to stderr every few
@@ -84,11 +84,14 @@ def _build_dir():
 def _digest(name):
     h = hashlib.sha256()
     h.update(" ".join(_flags()).encode())
-    for fn in sorted(os.listdir(_HERE)):
-        if fn == name + ".cu" or fn.endswith((".cuh", ".h")):
-            with open(os.path.join(_HERE, fn), "rb") as f:
-                h.update(fn.encode())
-                h.update(f.read())
+    files = [fn for fn in os.listdir(_HERE) if fn == name + ".cu" or fn.endswith((".cuh", ".h"))]
+    host = os.path.join(_HERE, "host")              # the host engine's headers
+    if os.path.isdir(host):
+        files += [os.path.join("host", fn) for fn in os.listdir(host) if fn.endswith(".hpp")]
+    for fn in sorted(files):
+        with open(os.path.join(_HERE, fn), "rb") as f:
+            h.update(fn.encode())
+            h.update(f.read())
     return h.hexdigest()
 
 

@@ -1,0 +1,122 @@
+"""The native engine behind the C interface on the device: greedy generation against the plain
+implementation, and everything it generates (greedy and sampled, penalties, stop ids, few pages
+so that requests are preempted and recomputed) against the Python scheduler on the same model:
+both launch the same kernels, so the ids are equal."""
+import numpy as np
+import pytest
+
+import plain_gpt2
+import traces
+from conftest import PAGE_SIZE, TINY
+
+pytestmark = pytest.mark.gpu
+STORE = {"float32": "float32", "bfloat16": "bfloat16"}
+TIE = {"float32": 1e-4, "bfloat16": 2e-2}
+
+
+def drain(s):
+    out = {}
+    while True:
+        g = s.poll()
+        if g is None:
+            return out
+        out[g[0]] = g[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(model_dirs, name, dtype):
+    from sglang_c_b200.engine.c_api import CEngine
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    lens = [5, 17, 32] if name == "A" else [1, 9, 40, 63, 100]
+    prompts = [traces.random_tokens(70 + i, n, V) for i, n in enumerate(lens)]
+    e = CEngine(d, dtype=dtype, page_size=PAGE_SIZE[name], max_tokens=1024, max_requests=8, max_step_tokens=64,
+                prefill_chunk=24)
+    ids = [e.submit_ids(p, 16) for p in prompts]
+    e.run_until_done()
+    got = drain(e)
+    cfg, w = plain_gpt2.read_model_dir(d)
+    for rid, p in zip(ids, prompts):
+        assert len(got[rid]) == 16
+        seq = list(p)
+        for t in got[rid]:
+            lg = plain_gpt2.forward(cfg, w, seq)[-1]
+            best = int(np.argmax(lg))
+            assert t == best or lg[best] - lg[t] < TIE[dtype], (t, best, float(lg[best] - lg[t]))
+            seq.append(t)
+    st = e.get_stats()
+    assert st.n_finished == len(prompts) and st.pool_free == st.pool_pages and st.graph_replays > 0
+    assert e.check()
+    e.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n_pages", [("A", 9), ("B", 40), ("C", 64)])
+def test_everything_it_generates_equals_the_python_engines(model_dirs, name, n_pages, dtype):
+    """Mixed sampling options, arrivals over time and a pool so small that requests are preempted:
+    the same ids, finish reasons, log-probabilities and counters from both engines."""
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    d = model_dirs(name, STORE[dtype])
+    V = TINY[name]["vocab_size"]
+    kw = dict(dtype=dtype, page_size=PAGE_SIZE[name], n_pages=n_pages, max_requests=4, max_step_tokens=48,
+              prefill_chunk=20, seed=11, want_logprobs=True)
+    py = sched_new(d, **kw)
+    ce = CEngine(d, **kw)
+    sps = [SamplingParams(), SamplingParams(temperature=0.9, seed=3), SamplingParams(temperature=1.3, top_k=20, top_p=0.9),
+           SamplingParams(temperature=0.7, repetition_penalty=1.3, frequency_penalty=0.2, presence_penalty=0.1),
+           SamplingParams(temperature=1.0, min_p=0.05, stop_ids=[3, 5, 7]), SamplingParams(ignore_eos=True)]
+    # A: short prompts that grow long, so that the running requests outgrow the pool
+    lens = {"A": [10, 5, 14, 8, 3, 12], "B": [33, 5, 61, 18, 2, 47, 29, 70], "C": [300, 40, 5, 180, 77, 260]}[name]
+    new = (lambda i: 50) if name == "A" else (lambda i: 6 + 3 * (i % 4))
+    arrivals = [(traces.random_tokens(500 + i, n, V), new(i), sps[i % len(sps)]) for i, n in enumerate(lens)]
+    steps = 0
+    while (arrivals or py.nactive()) and steps < 2000:
+        if arrivals and steps % 3 == 0:
+            p, n, sp = arrivals.pop(0)
+            a, b = py.submit_ids(p, n, sp), ce.submit_ids(p, n, sp)
+            assert a == b > 0
+        py.step()
+        ce.step()
+        assert ce.check()
+        steps += 1
+    while py.nactive():          # (the Python scheduler reads a step's ids one call later)
+        py.step()
+    assert ce.nactive() == 0
+    got_py = {}
+    while True:
+        g = py.poll()
+        if g is None:
+            break
+        got_py[g[0]] = (g[1], py.requests[g[0]].finish_reason, py.poll_logprobs(g[0]))
+    got_c = {}
+    while True:
+        g = ce.poll()
+        if g is None:
+            break
+        got_c[g[0]] = (g[1], ce.last_finish, ce.last_logprobs)
+    assert set(got_c) == set(got_py)
+    for rid in got_py:
+        assert got_c[rid][0] == got_py[rid][0], rid
+        assert got_c[rid][1] == got_py[rid][1], rid
+        np.testing.assert_allclose(got_c[rid][2], got_py[rid][2], rtol=0, atol=1e-6)
+    cs, st = ce.get_stats(), py.get_stats()
+    for k in ("prefill_tokens", "decode_tokens", "n_finished", "n_preempt", "recomputed_tokens", "pool_free"):
+        assert getattr(cs, k) == getattr(st, k), k
+    if name == "A":
+        assert cs.n_preempt >= 1
+    ce.close()
+
+
+def test_it_refuses_to_start_without_its_kernel_libraries(model_dirs, tmp_path):
+    from sglang_c_b200.engine.c_api import CEngine, CEngineError, COptions
+    import ctypes as C
+    e = CEngine(model_dirs("A"), dry_run=True)
+    o = COptions()
+    e.lib.sglc_engine_options_default(C.byref(o))
+    o.library_dir = str(tmp_path).encode()
+    err = C.create_string_buffer(4096)
+    assert not e.lib.sglc_engine_new(model_dirs("A").encode(), C.byref(o), err, len(err))
+    assert b"cannot be loaded" in err.value and b"no CPU path" in err.value

@@ -13,7 +13,8 @@ is flushed); `e2e` is the same through the Python entry point (scheduler, host
 token ids in and out); `prefill` is one step of 2,048 prompt tokens (2 x 1,024);
 `roofline` is the decode step's bytes (every weight once, the cache of the live
 requests) over its time, against the measured copy bandwidth; `points` has decode
-at batch 1 and 64 and the true 32-bit path; `kernels` says where a decode and a
+at batch 1 and 64, the true 32-bit path and the batch-8 decode through the C interface
+(`e2e_c_api_b8`); `kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
 sizes and the mixed workload to `points`.
 """
@@ -201,9 +202,13 @@ def time_decode(eng, batch, context, steps, warmup):
     return statistics.median(regions), launches, regions
 
 
-def time_prefill(eng, n_prompts, prompt_len, warmup):
+def time_prefill(eng, n_prompts, prompt_len, warmup, behind_sleep=False):
     """One step of n_prompts whole prompts; the median of N_REGIONS regions of at least REGION_MS
-    of device time each (a region is steps in a row, each on fresh requests)."""
+    of device time each (a region is steps in a row, each on fresh requests).  The events stand
+    around the call of the step, so the host's preparation of a 2,048-token step (about 0.2 ms
+    during which the device waits) is inside; with behind_sleep the step is queued behind a
+    millisecond of device sleep instead, which hides the host's part as a scheduler that prepares
+    a step while the last one runs does: the device's own time for the step."""
     import numpy as np
     import torch
     from sglang_c_b200.engine import StepEntry
@@ -219,6 +224,8 @@ def time_prefill(eng, n_prompts, prompt_len, warmup):
         entries = [StepEntry(r, [int(t) for t in rng.integers(0, V, size=prompt_len)], [prompt_len - 1])
                    for r in reqs]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if behind_sleep:
+            torch.cuda._sleep(2_000_000)
         e0.record()
         eng.step(entries)
         e1.record()
@@ -340,6 +347,74 @@ def time_e2e(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
     return statistics.median(regions), h2d, d2h
 
 
+def time_e2e_c(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
+    """The same decode through the engine's C interface (csrc/sglc_engine.h, all native): token
+    ids on the host in, token ids on the host out, every step; wall clock; regions as time_e2e."""
+    import numpy as np
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    n_timed = max(steps, 100)
+    e = CEngine(model_dir, seed=0, dtype=dtype, page_size=PAGE, max_tokens=batch * (context + n_timed + warmup + 64),
+                max_requests=max(batch, 1), max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
+    V = e.vocab_size
+    rng = np.random.default_rng(5)
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+    regions = []
+    for _ in range(N_REGIONS):
+        ids = [e.submit_ids([int(t) for t in rng.integers(0, V, size=context)], warmup + n_timed + 32, sp)
+               for _ in range(batch)]
+        while True:                                # prompts done; every request decodes from here
+            e.step()
+            ran = e.last_step()
+            if len(ran) == batch and all(n == 1 for _, n, _ in ran):
+                break
+        for _ in range(warmup):
+            e.step()
+        n0 = e.get_stats().decode_tokens
+        t0 = time.perf_counter()
+        for _ in range(n_timed):
+            e.step()                               # returns with the step's ids on the host
+        dt = time.perf_counter() - t0
+        regions.append((e.get_stats().decode_tokens - n0) / dt)
+        for i in ids:
+            e.abort(i)
+        while e.poll() is not None:
+            pass
+    e.close()
+    return statistics.median(regions)
+
+
+def run_mixed_c(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
+    """run_mixed through the engine's C interface."""
+    import numpy as np
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    rng = np.random.default_rng(seed)
+    P = cfg_d["n_positions"]
+    lens = [int(n) for n in rng.integers(16, P - max_new + 1, size=n_requests)]
+    e = CEngine(model_dir, seed=seed, dtype="bfloat16", page_size=PAGE,
+                max_tokens=sum(n + max_new + PAGE for n in lens), max_requests=n_requests,
+                max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
+    V = cfg_d["vocab_size"]
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+    prompts = [[int(t) for t in rng.integers(0, V, size=n)] for n in lens]
+    e.submit_ids(prompts[0][:64], 4, sp)
+    e.run_until_done()
+    e.poll()
+    t0 = time.perf_counter()
+    for p in prompts:
+        assert e.submit_ids(p, max_new, sp) > 0
+    steps = e.run_until_done()
+    dt = time.perf_counter() - t0
+    st = e.get_stats()
+    gen = n_requests * max_new
+    out = {"requests": n_requests, "prompt_tokens": sum(lens), "generated_tokens": gen, "seconds": dt,
+           "steps": steps, "generated_tok_s": gen / dt, "total_tok_s": (gen + sum(lens)) / dt,
+           "n_preempt": st.n_preempt, "graph_replays": st.graph_replays}
+    e.close()
+    return out
+
+
 def run_mixed(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
     """The mixed workload: requests with uniform random prompt lengths in [16, 1024] and max_new
     greedy tokens each, all submitted at once to the scheduler (continuous batching, prompt
@@ -446,8 +521,10 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     r["bytes"] = model_bytes_flops(cfg_d, BATCH, CONTEXT + steps // 2)
     pms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3)
     pflops = prefill_flops(cfg_d, 2, PREFILL_TOKENS // 2)
+    dms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3, behind_sleep=True)
     r["prefill"] = {"value": PREFILL_TOKENS / (pms / 1e3), "tokens": PREFILL_TOKENS, "ms": pms,
-                    "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"]}
+                    "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"],
+                    "device_ms": dms, "device_frac": pflops / (dms / 1e3) / (pk["bf16_tflops"] * 1e12)}
     r["points"] = {}
     for b in points:
         t, _, _ = time_decode(eng, b, CONTEXT, steps, warmup)
@@ -459,6 +536,7 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     del eng
     torch.cuda.empty_cache()
     r["e2e"] = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
+    r["points"]["e2e_c_api_b8"] = time_e2e_c(model_dir, BATCH, CONTEXT, steps, warmup)
     if fp32:
         # the true 32-bit path (plain FFMA products, 32-bit cache): same step function and scheduler
         eng = Engine.from_dir(model_dir, dtype="float32", page_size=PAGE, max_tokens=BATCH * (CONTEXT + 256) + 4096,
@@ -516,6 +594,8 @@ def main():
     points = r["points"]
     if args.full:
         points["mixed_small_generated_tok_s"] = run_mixed(r["model_dir"], dict(base, n_layer=n_layer))["generated_tok_s"]
+        points["mixed_small_c_api_generated_tok_s"] = \
+            run_mixed_c(r["model_dir"], dict(base, n_layer=n_layer))["generated_tok_s"]
         for other in ("medium", "xl"):
             if other == args.model:
                 continue

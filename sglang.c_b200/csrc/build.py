@@ -162,6 +162,37 @@ def build_all(names=None, jobs=None):
     return [lib_path(n) for n in names]
 
 
+def build_app(name="sglc"):
+    """Compile csrc/apps/<name>.c, a C program on the engine's C interface, against the host
+    engine's library (built first) and return the executable's path (beside the libraries)."""
+    build("host_engine")
+    src = os.path.join(_HERE, "apps", name + ".c")
+    out = os.path.join(_build_dir(), name)
+    stamp = out + ".hash"
+    h = hashlib.sha256()
+    for fn in (src, os.path.join(_HERE, "sglc_engine.h")):
+        with open(fn, "rb") as f:
+            h.update(f.read())
+    want = h.hexdigest()
+    if os.path.exists(out) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == want:
+                return out
+    cc = os.environ.get("CC") or shutil.which("cc") or shutil.which("gcc")
+    if not cc:
+        raise BuildError("no C compiler found (looked at $CC, cc and gcc)")
+    tmp = out + f".tmp{os.getpid()}"
+    cmd = [cc, "-std=c11", "-O2", "-D_POSIX_C_SOURCE=200809L", "-I", _HERE, src, "-o", tmp, "-L", _build_dir(),
+           "-lsglc_host_engine", "-Wl,-rpath," + _build_dir()]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"{cc} failed on apps/{name}.c:\n{proc.stdout}")
+    os.replace(tmp, out)
+    with open(stamp, "w") as f:
+        f.write(want)
+    return out
+
+
 def load(name):
     """The ctypes handle of csrc/<name>.cu's library, built first if needed."""
     with _lock:

@@ -254,3 +254,22 @@ def test_sharded_checkpoints_and_prefixed_names(tmp_path):
         json.dump({"weight_map": wmap}, fh)
     with pytest.raises(CEngineError, match="tensors not found in the shard it names"):
         CEngine(d, dry_run=True)
+
+
+def test_a_c_program_on_the_interface_generates(tmp_path):
+    """csrc/apps/sglc.c, compiled with the system's C compiler and linked against the engine's
+    library, run without a device."""
+    import subprocess
+    from sglang_c_b200.csrc import build
+    exe = build.build_app("sglc")
+    d = model_dir(tmp_path)
+    r = subprocess.run([exe, "--model", d, "--prompt-ids", "5, 6 7", "--max-new", "5", "--dry-run", "--verbose"],
+                       capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == [str(t) for t in [5, 6, 7] + [formula(1, 3 + i, 50) for i in range(5)]]
+    assert "generated 5 tokens" in r.stderr and "finish reason 3" in r.stderr
+    r = subprocess.run([exe, "--model", d, "--prompt-ids", "5 99", "--dry-run"], capture_output=True, text=True)
+    assert r.returncode == 2 and "refused" in r.stderr
+    r = subprocess.run([exe, "--model", str(tmp_path / "nothing"), "--prompt-ids", "5", "--dry-run"],
+                       capture_output=True, text=True)
+    assert r.returncode == 2 and "no config.json" in r.stderr

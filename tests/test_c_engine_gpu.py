@@ -120,3 +120,22 @@ def test_it_refuses_to_start_without_its_kernel_libraries(model_dirs, tmp_path):
     err = C.create_string_buffer(4096)
     assert not e.lib.sglc_engine_new(model_dirs("A").encode(), C.byref(o), err, len(err))
     assert b"cannot be loaded" in err.value and b"no CPU path" in err.value
+
+
+def test_the_c_program_generates_what_the_python_entry_point_generates(model_dirs):
+    import os
+    import subprocess
+    from conftest import ROOT
+    from sglang_c_b200.engine import generate, sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    d = model_dirs("B", "bfloat16")
+    prompt = traces.random_tokens(3, 21, TINY["B"]["vocab_size"])
+    r = subprocess.run([os.path.join(ROOT, "bin", "sglc_native"), "--model", d, "--prompt-ids",
+                        " ".join(map(str, prompt)), "--max-new", "12", "--temperature", "0.9", "--seed", "4",
+                        "--page-size", "8", "--verbose"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    got = [int(t) for t in r.stdout.split()]
+    s = sched_new(d, seed=4, dtype="bfloat16", page_size=8, max_tokens=128, max_requests=4)
+    want = generate(s, prompt, SamplingParams(temperature=0.9, top_k=50, top_p=0.95, seed=4), 12)
+    assert got == prompt + want
+    assert "generated" in r.stderr and "MB of weights" in r.stderr

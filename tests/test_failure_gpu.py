@@ -69,3 +69,36 @@ def test_bounds_check_build_skips_and_flags_a_bad_page_id(model_dirs):
             eng.check_device_errors()
         finally:
             build.set_bounds_check(False)
+
+
+def test_a_step_that_fails_half_way_is_rolled_back(model_dirs):
+    """A launch that raises in the middle of a step (made to, on the host): the requests had been
+    grown for the step's tokens, whose keys and values were never all written; the growth is taken
+    back, pages return, and the same step run again gives what an undisturbed engine gives."""
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.engine import Engine, StepEntry
+    d = model_dirs("A", "float32")
+    toks = traces.random_tokens(2, 40, TINY["A"]["vocab_size"])
+    kw = dict(dtype="float32", page_size=16, n_pages=8, max_requests=2, max_step_tokens=64)
+    eng = Engine.from_dir(d, use_host_walker=False, use_graphs=False, **kw)
+    eng.add_request("a")
+    eng.step([StepEntry("a", toks[:20], [])])
+    free = eng.cache.n_free_pages()
+    real, calls = eng.rt.gemm, [0]
+
+    def failing(*a, **k):
+        calls[0] += 1
+        if calls[0] == 6:                      # in the second layer: the first has written its cache
+            raise ops.KernelError("made to fail")
+        return real(*a, **k)
+
+    eng.rt.gemm = failing
+    with pytest.raises(ops.KernelError, match="made to fail"):
+        eng.step([StepEntry("a", toks[20:], [19])])
+    eng.rt.gemm = real
+    assert eng.length("a") == 20 and eng.cache.n_free_pages() == free
+    eng.cache.check()
+    again = eng.step([StepEntry("a", toks[20:], [19])]).clone()
+    ref = Engine.from_dir(d, **kw)
+    ref.add_request("a")
+    assert torch.equal(again, ref.step([StepEntry("a", toks, [39])]))

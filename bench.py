@@ -221,7 +221,8 @@ def time_prefill(eng, n_prompts, prompt_len, warmup, behind_sleep=False):
         reqs = [f"p{it[0]}_{i}" for i in range(n_prompts)]
         for r in reqs:
             eng.add_request(r)
-        entries = [StepEntry(r, [int(t) for t in rng.integers(0, V, size=prompt_len)], [prompt_len - 1])
+        # (ids as arrays, as the scheduler hands a prompt's portions to the engine)
+        entries = [StepEntry(r, rng.integers(0, V, size=prompt_len).astype(np.int32), [prompt_len - 1])
                    for r in reqs]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if behind_sleep:
@@ -384,6 +385,42 @@ def time_e2e_c(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
     return statistics.median(regions)
 
 
+def time_prefill_c(model_dir, n_prompts, prompt_len, warmup=3):
+    """One step of n_prompts whole prompts through the C interface, wall clock around the call of
+    sglc_engine_step: the host's preparation, the step, the sampling of one token per prompt and
+    the ids back on the host.  Median of N_REGIONS regions of at least REGION_MS."""
+    import numpy as np
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    e = CEngine(model_dir, dtype="bfloat16", page_size=PAGE, max_tokens=n_prompts * (prompt_len + 64),
+                max_requests=max(n_prompts, 1), max_step_tokens=n_prompts * prompt_len, prefill_chunk=prompt_len)
+    rng = np.random.default_rng(99)
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+
+    def once():
+        for _ in range(n_prompts):
+            assert e.submit_ids([int(t) for t in rng.integers(0, e.vocab_size, size=prompt_len)], 1, sp) > 0
+        t0 = time.perf_counter()
+        done = e.step()
+        dt = time.perf_counter() - t0
+        assert done == n_prompts
+        while e.poll() is not None:
+            pass
+        return dt * 1e3
+
+    for _ in range(max(warmup, 3)):
+        once()
+    regions = []
+    for _ in range(N_REGIONS):
+        ms, n = 0.0, 0
+        while ms < REGION_MS:
+            ms += once()
+            n += 1
+        regions.append(ms / n)
+    e.close()
+    return statistics.median(regions)
+
+
 def run_mixed_c(model_dir, cfg_d, n_requests=64, max_new=128, seed=0):
     """run_mixed through the engine's C interface."""
     import numpy as np
@@ -537,6 +574,9 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     torch.cuda.empty_cache()
     r["e2e"] = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
     r["points"]["e2e_c_api_b8"] = time_e2e_c(model_dir, BATCH, CONTEXT, steps, warmup)
+    # (a request must leave a position for the token it generates: prompts of 1,023 tokens)
+    r["points"]["prefill_c_api_tok_s"] = \
+        (PREFILL_TOKENS - 2) / (time_prefill_c(model_dir, 2, PREFILL_TOKENS // 2 - 1) / 1e3)
     if fp32:
         # the true 32-bit path (plain FFMA products, 32-bit cache): same step function and scheduler
         eng = Engine.from_dir(model_dir, dtype="float32", page_size=PAGE, max_tokens=BATCH * (CONTEXT + 256) + 4096,

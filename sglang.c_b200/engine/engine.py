@@ -145,7 +145,10 @@ class Engine:
             if n == 1:
                 bad = not (0 <= int(e.tokens[0]) < V)
             else:
-                arr = np.asarray(e.tokens)
+                # a portion is made an array once, here (a list of a thousand ids costs 35 us to
+                # convert; the packed block below takes the array)
+                arr = e.tokens if isinstance(e.tokens, np.ndarray) else np.asarray(e.tokens)
+                e.tokens = arr
                 bad = bool(arr.min() < 0 or arr.max() >= V)
             if bad:
                 t = next(t for t in e.tokens if not (0 <= int(t) < V))

@@ -27,6 +27,8 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import List, Optional
 
+import numpy as np
+
 from .. import log
 from ..sampling import Sampler, SamplingParams, request_stream, uniform
 from .engine import Engine, OutOfPages
@@ -40,6 +42,7 @@ KEEP_TAKEN = 256       # taken requests whose record is kept for questions after
 class Request:
     id: int
     prompt: List[int]
+    prompt_arr: object           # the prompt as an int32 array (portions of it go to the engine as views)
     max_new: int
     sp: SamplingParams
     rng: int
@@ -123,7 +126,8 @@ class Scheduler:
         if min(need, plan.max_positions) > pool_tokens:
             return -1
         sp = sp or SamplingParams()
-        r = Request(self.next_id, ids, max_new, sp, request_stream(self.seed ^ sp.seed, self.next_id))
+        r = Request(self.next_id, ids, np.asarray(ids, dtype=np.int32), max_new, sp,
+                    request_stream(self.seed ^ sp.seed, self.next_id))
         self.next_id += 1
         self.requests[r.id] = r
         self.waiting.append(r)
@@ -271,6 +275,8 @@ class Scheduler:
                 np_ = len(r.prompt)
                 if r.n_computed >= np_:                   # past the prompt: no need to join the lists
                     toks = r.gen[r.n_computed - np_:r.n_computed - np_ + n]
+                elif r.n_computed + n <= np_:             # inside the prompt: a view of its array
+                    toks = r.prompt_arr[r.n_computed:r.n_computed + n]
                 else:
                     toks = r.tokens[r.n_computed:r.n_computed + n]
                 last = (r.n_computed + n == np_ + len(r.gen))

@@ -17,7 +17,7 @@ class StepEntry:
     """The next `tokens` of request `req`; `want` lists the places among them
     whose logits are asked for (may be empty)."""
     req: object
-    tokens: List[int]
+    tokens: List[int]            # or an integer array
     want: List[int]
 
 

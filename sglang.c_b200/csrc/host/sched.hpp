@@ -98,27 +98,34 @@ struct StepItem {
 struct SchedStats {
   long long prefill_tokens = 0, decode_tokens = 0, n_finished = 0, n_running = 0, n_waiting = 0;
   long long pool_pages = 0, pool_free = 0, n_preempt = 0, prefill_chunk = 0, n_steps = 0, recomputed_tokens = 0;
+  long long steps_ahead = 0;      // steps queued before the ids of the step ahead of them were read
 };
 
 // What runs a planned step: the device engine, or a stand-in without a device.
 class StepRunner {
  public:
   virtual ~StepRunner() {}
-  // Runs the items' tokens as one batch over the cache (already grown for them) and samples one
-  // token for every item with `sampled` set, in item order, with the uniforms given in that
-  // order.  false with `err` set: nothing of the step counts.
-  virtual bool run(const std::vector<StepItem>& items, const std::vector<double>& uniforms, bool want_logprobs,
-                   std::vector<int>* tokens, std::vector<float>* logprobs, std::string* err) = 0;
+  // Queues the items' tokens as one batch over the cache (already grown for them) and the sampling
+  // of one token for every item with `sampled` set, in item order, with the uniforms given in that
+  // order; returns without waiting.  With `ids_on_device` every item brings one token, and these
+  // are the ids the launch before this one sampled, row for row, which the host has not seen: they
+  // pass from the sampler's output to the step's token array on the device.  At most two launches
+  // may be uncollected.  false with `err` set: nothing was queued.
+  virtual bool launch(const std::vector<StepItem>& items, const std::vector<double>& uniforms, bool want_logprobs,
+                      bool ids_on_device, int* ticket, std::string* err) = 0;
+  // Waits for a launch and gives its sampled ids.  false with `err` set: nothing of that step
+  // (or of a step queued behind it) counts.
+  virtual bool collect(int ticket, std::vector<int>* tokens, std::vector<float>* logprobs, std::string* err) = 0;
 };
 
 class Scheduler {
  public:
   Scheduler(CacheTables* cache, StepRunner* runner, int vocab, int max_positions, int eos, uint64_t seed,
-            int prefill_chunk, int token_budget, bool want_logprobs)
+            int prefill_chunk, int token_budget, bool want_logprobs, bool run_ahead)
       : cache_(cache), runner_(runner), vocab_(vocab), max_positions_(max_positions), eos_(eos), seed_(seed),
         // the reference: SGL_PREFILL_CHUNK, default 512, <= 0 means 4096 (src/scheduler.c:138-143)
         prefill_chunk_(prefill_chunk > 0 ? prefill_chunk : 4096), token_budget_(token_budget),
-        want_logprobs_(want_logprobs) {
+        want_logprobs_(want_logprobs), run_ahead_(run_ahead) {
     stats_.prefill_chunk = prefill_chunk_;
     stats_.pool_pages = cache->n_pages();
   }
@@ -236,51 +243,159 @@ class Scheduler {
     return chosen;
   }
 
-  // Run one step; how many requests finished in it, or -1 with `err` set (nothing changed but
-  // preemptions and admissions already made).
+  // Run one step; how many requests finished in this call, or -1 with `err` set (the cache is as
+  // before the failed step).
+  //
+  // With run_ahead, a step's sampled ids are read one call later: while every running request
+  // just decodes (none waits, none can end by its length, none has penalties, pages suffice), a
+  // call first queues the next step of single tokens behind the step in flight (its ids pass from
+  // the sampler to the token array on the device), then waits for the ids of the step in flight
+  // and appends them.  So the device always has the next step queued while the host does its
+  // bookkeeping.  Whatever changes the set of running requests sends the next call down the plain
+  // path: wait, plan, launch.  A request that ends while a step with it is queued has that step's
+  // id dropped.
   int step(std::string* err) {
+    int finished = 0;
+    if (flight_.active) {
+      Flight next;
+      if (run_ahead_ && can_run_ahead() && launch(decode_items(), true, &next, err)) {
+        const int f = collect(&flight_, &next, err);
+        if (f < 0) return -1;
+        flight_ = next;
+        stats_.steps_ahead++;
+        return f;
+      }
+      err->clear();
+      finished = collect(&flight_, nullptr, err);
+      if (finished < 0) return -1;
+    }
     std::vector<StepItem> chosen = plan_step();
+    if (chosen.empty()) {
+      last_step_.clear();
+      return finished;
+    }
+    Flight now;
+    if (!launch(chosen, false, &now, err)) return -1;
+    if (!run_ahead_) {
+      const int f = collect(&now, nullptr, err);
+      return f < 0 ? -1 : finished + f;
+    }
+    flight_ = now;
+    return finished;
+  }
+  // a step may still be in flight when the caller asks whether anything is active
+  bool in_flight() const { return flight_.active; }
+
+ private:
+  struct FlightItem {
+    long long id;
+    int n, old_len;
+    bool sampled;
+    uint64_t stream;          // the request's random stream before this step drew from it
+  };
+  struct Flight {
+    bool active = false, all_decode = false;
+    int ticket = 0;
+    std::vector<FlightItem> items;
+  };
+
+  // every running request was sampled in the step in flight, in this order, as a single token;
+  // none waits; none can end by its length or the model's positions with the id in flight; none
+  // needs its history on the host; and one more position for each fits the free pages
+  bool can_run_ahead() const {
+    if (!flight_.all_decode || !waiting_.empty() || running_.empty() || flight_.items.size() != running_.size()) return false;
+    std::vector<std::pair<long long, int>> wants;
+    for (size_t i = 0; i < running_.size(); ++i) {
+      const Request* r = running_[i];
+      if (r->id != flight_.items[i].id || r->sp.has_penalties()) return false;
+      if ((int)r->gen.size() + 2 > r->max_new || r->n_computed + 2 > max_positions_) return false;
+      wants.emplace_back(r->id, r->n_computed + 1);
+    }
+    return (int)running_.size() <= token_budget_ && cache_->can_extend_all(wants);
+  }
+  std::vector<StepItem> decode_items() const {
+    std::vector<StepItem> items;
+    for (Request* r : running_) items.push_back({r, 1, r->n_computed, true});
+    return items;
+  }
+
+  // grow the cache, draw the uniforms and queue the step; on failure everything is as before
+  bool launch(const std::vector<StepItem>& chosen, bool ids_on_device, Flight* f, std::string* err) {
     last_step_.clear();
     for (const StepItem& it : chosen) last_step_.push_back({it.r->id, it.n, it.sampled});
-    if (chosen.empty()) return 0;
     for (const StepItem& it : chosen)
       if (!cache_->extend(it.r->id, it.old_len + it.n)) {            // (cannot happen after can_extend_all)
         roll_back(chosen);
-        return *err = "the cache refused pages that it had promised", -1;
+        return *err = "the cache refused pages that it had promised", false;
       }
     std::vector<double> us;
-    std::vector<uint64_t> streams;            // as they were, should the step fail
-    for (const StepItem& it : chosen)
-      if (it.sampled) {
-        streams.push_back(it.r->rng);
-        us.push_back(it.r->sp.greedy() ? 0.0 : next_uniform(&it.r->rng));
-      }
-    std::vector<int> toks;
-    std::vector<float> lps;
-    if (!runner_->run(chosen, us, want_logprobs_, &toks, &lps, err) || toks.size() != us.size()) {
-      if (err->empty()) *err = "the step gave fewer sampled tokens than it was asked for";
-      size_t k = 0;
-      for (const StepItem& it : chosen)
-        if (it.sampled) it.r->rng = streams[k++];
+    f->items.clear();
+    f->all_decode = true;
+    for (const StepItem& it : chosen) {
+      f->items.push_back({it.r->id, it.n, it.old_len, it.sampled, it.r->rng});
+      f->all_decode = f->all_decode && it.n == 1 && it.sampled;
+      if (it.sampled) us.push_back(it.r->sp.greedy() ? 0.0 : next_uniform(&it.r->rng));
+    }
+    if (!runner_->launch(chosen, us, want_logprobs_, ids_on_device, &f->ticket, err)) {
+      for (size_t i = 0; i < chosen.size(); ++i) chosen[i].r->rng = f->items[i].stream;
       roll_back(chosen);
-      return -1;
+      return false;
     }
     for (const StepItem& it : chosen) {
       if (it.old_len + it.n <= (int)it.r->prompt.size()) stats_.prefill_tokens += it.n;
       it.r->n_computed += it.n;
     }
     stats_.n_steps++;
-    int finished = 0;
-    size_t k = 0;
-    for (const StepItem& it : chosen)
-      if (it.sampled) {
-        finished += append(it.r, toks[k], want_logprobs_ && k < lps.size() ? &lps[k] : nullptr) ? 1 : 0;
-        ++k;
-      }
-    return finished;
+    f->active = true;
+    return true;
   }
 
- private:
+  // Wait for a step's ids and append them; how many requests ended, or -1: the step (and `behind`,
+  // a step queued after it) is undone.
+  int collect(Flight* f, Flight* behind, std::string* err) {
+    std::vector<int> toks;
+    std::vector<float> lps;
+    size_t n_sampled = 0;
+    for (const FlightItem& it : f->items) n_sampled += it.sampled;
+    f->active = false;
+    if (!runner_->collect(f->ticket, &toks, &lps, err) || toks.size() != n_sampled) {
+      if (err->empty()) *err = "the step gave fewer sampled tokens than it was asked for";
+      if (behind && behind->active) {
+        std::string ignored;
+        std::vector<int> t2;
+        std::vector<float> l2;
+        runner_->collect(behind->ticket, &t2, &l2, &ignored);        // drain it; its ids rest on bad ones
+        undo(*behind);
+        behind->active = false;
+      }
+      undo(*f);
+      return -1;
+    }
+    int finished = 0;
+    size_t k = 0;
+    for (const FlightItem& it : f->items) {
+      if (!it.sampled) continue;
+      const size_t row = k++;
+      auto found = requests_.find(it.id);
+      // ended or aborted after this step was queued: its id is dropped
+      if (found == requests_.end() || found->second->state != REQ_RUNNING) continue;
+      Request* r = found->second.get();
+      finished += append(r, toks[row], want_logprobs_ && row < lps.size() ? &lps[row] : nullptr, it.old_len + it.n) ? 1 : 0;
+    }
+    return finished;
+  }
+  // a failed step: lengths, counters and random streams as before it
+  void undo(const Flight& f) {
+    for (const FlightItem& it : f.items) {
+      auto found = requests_.find(it.id);
+      if (found == requests_.end() || found->second->state != REQ_RUNNING) continue;
+      Request* r = found->second.get();
+      if (cache_->has(r->id) && cache_->length(r->id) > it.old_len) cache_->truncate(r->id, it.old_len);
+      if (r->n_computed > it.old_len) r->n_computed = it.old_len;
+      r->rng = it.stream;
+    }
+  }
+
   static std::vector<std::pair<long long, int>> wants_of(const std::vector<StepItem>& chosen) {
     std::vector<std::pair<long long, int>> w;
     for (const StepItem& it : chosen) w.emplace_back(it.r->id, it.old_len + it.n);
@@ -313,7 +428,9 @@ class Scheduler {
   }
   // The reference's req_sample_append (src/scheduler.c:288-310): eos or a stop id ends the
   // request without being appended; then max_new and the model's positions.
-  bool append(Request* r, int tok, const float* logprob) {
+  // n_computed: the request's tokens in the cache after the step that gave `tok` (a later step
+  // may be queued already).
+  bool append(Request* r, int tok, const float* logprob, int n_computed) {
     auto end = [&](int reason) {
       running_.erase(std::find(running_.begin(), running_.end(), r));
       finish(r, reason, true);
@@ -325,7 +442,7 @@ class Scheduler {
     if (logprob) r->logprobs.push_back(*logprob);
     stats_.decode_tokens++;
     if ((int)r->gen.size() >= r->max_new) return end(FIN_LENGTH);
-    if (r->n_computed + 1 >= max_positions_) return end(FIN_CONTEXT);
+    if (n_computed + 1 >= max_positions_) return end(FIN_CONTEXT);
     return false;
   }
 
@@ -335,6 +452,8 @@ class Scheduler {
   uint64_t seed_;
   int prefill_chunk_, token_budget_;
   bool want_logprobs_;
+  bool run_ahead_;
+  Flight flight_;
   long long next_id_ = 1;
   std::unordered_map<long long, std::unique_ptr<Request>> requests_;
   std::deque<Request*> waiting_;            // first come first served; preempted requests re-enter by arrival

@@ -242,7 +242,7 @@ bool check_tensors(const ModelSpec& m, const Checkpoint& ck, std::map<std::strin
     const TensorView* t = nullptr;
     std::string found;
     for (const std::string& p : m.prefixes)
-      if ((t = ck.find(p + w.name))) {
+      if ((t = ck.find(p + w.name)) != nullptr) {
         found = p + w.name;
         break;
       }
@@ -493,18 +493,29 @@ bool load_model(const std::string& dir, bool bf16, bool device, int page_size, l
 class DryRunner : public StepRunner {
  public:
   explicit DryRunner(int vocab) : vocab_(vocab) {}
-  bool run(const std::vector<StepItem>& items, const std::vector<double>&, bool want_logprobs, std::vector<int>* tokens,
-           std::vector<float>* logprobs, std::string*) override {
+  bool launch(const std::vector<StepItem>& items, const std::vector<double>&, bool want_logprobs, bool, int* ticket,
+              std::string*) override {
+    tokens_[turn_].clear();
+    logprobs_[turn_].clear();
     for (const StepItem& it : items)
       if (it.sampled) {
-        tokens->push_back((int)(((long long)it.r->id * 7919 + (long long)(it.old_len + it.n) * 104729) % vocab_));
-        if (want_logprobs) logprobs->push_back(0.0f);
+        tokens_[turn_].push_back((int)(((long long)it.r->id * 7919 + (long long)(it.old_len + it.n) * 104729) % vocab_));
+        if (want_logprobs) logprobs_[turn_].push_back(0.0f);
       }
+    *ticket = turn_;
+    turn_ ^= 1;
+    return true;
+  }
+  bool collect(int ticket, std::vector<int>* tokens, std::vector<float>* logprobs, std::string*) override {
+    *tokens = tokens_[ticket];
+    *logprobs = logprobs_[ticket];
     return true;
   }
 
  private:
-  int vocab_;
+  int vocab_, turn_ = 0;
+  std::vector<int> tokens_[2];
+  std::vector<float> logprobs_[2];
 };
 
 // ---- a step on the device ------------------------------------------------------------------------------------
@@ -526,6 +537,9 @@ class DeviceRunner : public StepRunner {
   DeviceRunner(const DeviceModel* dm, const CacheTables* cache, const Kernels* k, const sglc_engine_options& o)
       : dm_(dm), cache_(cache), k_(k), opt_(o) {}
   ~DeviceRunner() override {
+    if (stream_) cudaStreamSynchronize(stream_);          // a step may still be in flight
+    for (int i = 0; i < 2; ++i)
+      if (done_[i]) cudaEventDestroy(done_[i]);
     for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
     for (void* p : dev_) cudaFree(p);
     for (void* p : pinned_) cudaFreeHost(p);
@@ -538,6 +552,7 @@ class DeviceRunner : public StepRunner {
     const WalkModel& wm = dm_->wm;
     CU(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
     CU(cudaEventCreateWithFlags(&copied_, cudaEventDisableTiming));
+    for (int i = 0; i < 2; ++i) CU(cudaEventCreateWithFlags(&done_[i], cudaEventDisableTiming));
     t_cap_ = opt_.max_step_tokens;
     r_cap_ = opt_.max_requests;
     b_cap_ = (wm.n_positions + opt_.page_size - 1) / opt_.page_size;
@@ -571,17 +586,23 @@ class DeviceRunner : public StepRunner {
     if (!device((void**)&ws_, (size_t)ws_bytes_, err)) return false;
     logit_rows_ = std::max(r_cap_, 64);
     if (!device((void**)&logits_, (size_t)logit_rows_ * wm.vocab * 4, err)) return false;
+    // the two error words and the sampled ids lie together: one copy brings both back
     if (!device((void**)&tc_ws_, (size_t)TC_WS_FLOATS * 4, err) || !device((void**)&tc_counters_, TC_COUNTERS * 4, err) ||
-        !device((void**)&flags_, 2 * 4, err))
+        !device((void**)&flags_, (size_t)(4 + r_cap_) * 4, err))
       return false;
+    d_out_ = flags_ + 4;
     CU(cudaMemset(tc_counters_, 0, TC_COUNTERS * 4));
-    CU(cudaMemset(flags_, 0, 8));
-    // the sampler's records and results
-    if (!pinned((void**)&h_params_, (size_t)r_cap_ * 40, err) || !device((void**)&d_params_, (size_t)r_cap_ * 40, err) ||
-        !device((void**)&d_out_, (size_t)r_cap_ * 4, err) || !device((void**)&d_logprob_, (size_t)r_cap_ * 4, err) ||
-        !pinned((void**)&h_out_, (size_t)r_cap_ * 4, err) || !pinned((void**)&h_logprob_, (size_t)r_cap_ * 4, err) ||
-        !pinned((void**)&h_flags_, 8, err))
+    CU(cudaMemset(flags_, 0, (size_t)(4 + r_cap_) * 4));
+    // the sampler's records and results; the host's copies twice, taken in turn: a launch may
+    // follow before the last one's results are read
+    if (!device((void**)&d_params_, (size_t)r_cap_ * 40, err) || !device((void**)&d_logprob_, (size_t)r_cap_ * 4, err))
       return false;
+    for (int i = 0; i < 2; ++i) {
+      if (!pinned((void**)&h_params_[i], (size_t)r_cap_ * 40, err) || !pinned((void**)&h_flags_[i], (size_t)(4 + r_cap_) * 4, err) ||
+          !pinned((void**)&h_logprob_[i], (size_t)r_cap_ * 4, err))
+        return false;
+      h_out_[i] = h_flags_[i] + 4;
+    }
     hist_cap_ = 4096;
     if (!device((void**)&d_hist_tok_, (size_t)hist_cap_ * 4, err) || !device((void**)&d_hist_cnt_, (size_t)hist_cap_ * 4, err) ||
         !pinned((void**)&h_hist_, (size_t)hist_cap_ * 8, err))
@@ -592,8 +613,8 @@ class DeviceRunner : public StepRunner {
     return true;
   }
 
-  bool run(const std::vector<StepItem>& items, const std::vector<double>& uniforms, bool want_logprobs,
-           std::vector<int>* tokens, std::vector<float>* logprobs, std::string* err) override {
+  bool launch(const std::vector<StepItem>& items, const std::vector<double>& uniforms, bool want_logprobs,
+              bool ids_on_device, int* ticket, std::string* err) override {
     const int R = (int)items.size(), ps = opt_.page_size;
     int T = 0;
     for (const StepItem& it : items) T += it.n;
@@ -606,7 +627,7 @@ class DeviceRunner : public StepRunner {
       const StepItem& it = items[r];
       const int o = it.old_len, n = it.n;
       for (int j = 0; j < n; ++j) {
-        tok[t0 + j] = it.r->token(o + j);
+        tok[t0 + j] = ids_on_device ? 0 : it.r->token(o + j);
         pos[t0 + j] = o + j;
         trq[t0 + j] = r;
       }
@@ -635,7 +656,9 @@ class DeviceRunner : public StepRunner {
     copied_once_ = true;
 
     WalkStep s = {};
-    s.tokens = d_ + f_tokens_.off; s.positions = d_ + f_positions_.off; s.token_req = d_ + f_token_req_.off;
+    // (ids_on_device: what the launch before this one sampled, row for row, read where the
+    // sampler left it; this step's own sampler overwrites it after the embedding has read it)
+    s.tokens = ids_on_device ? d_out_ : d_ + f_tokens_.off; s.positions = d_ + f_positions_.off; s.token_req = d_ + f_token_req_.off;
     s.want_rows = d_ + f_want_.off; s.q_start = d_ + f_q_start_.off; s.kv_len = d_ + f_kv_len_.off;
     s.decode_tokens = d_ + f_decode_.off;
     for (int g = 0; g < n_groups_; ++g) {
@@ -655,25 +678,36 @@ class DeviceRunner : public StepRunner {
     s.stream_min_items = STREAM_MIN_ITEMS; s.use_tma_decode = 1;
     s.few_max_tokens = FEW_MAX_TOKENS; s.few_max_weight = FEW_MAX_WEIGHT;
     s.stream = stream_;
-    if (!forward(&s, err)) return false;
+    if (!forward(&s, ids_on_device, err)) return false;
 
     // one token for every wanted row, on the device; ids (and the error words) come back in one wait
+    const int turn = turn_;
     if (nw > 0) {
-      if (!sample(items, uniforms, nw, want_logprobs, err)) return false;
-      CU(cudaMemcpyAsync(h_out_, d_out_, (size_t)nw * 4, cudaMemcpyDeviceToHost, stream_));
-      if (want_logprobs) CU(cudaMemcpyAsync(h_logprob_, d_logprob_, (size_t)nw * 4, cudaMemcpyDeviceToHost, stream_));
+      if (!sample(items, uniforms, nw, want_logprobs, turn, err)) return false;
+      if (want_logprobs)
+        CU(cudaMemcpyAsync(h_logprob_[turn], d_logprob_, (size_t)nw * 4, cudaMemcpyDeviceToHost, stream_));
     }
-    CU(cudaMemcpyAsync(h_flags_, flags_, 8, cudaMemcpyDeviceToHost, stream_));
-    CU(cudaStreamSynchronize(stream_));
-    if (h_flags_[0] || h_flags_[1]) {
-      const int a = h_flags_[0], b = h_flags_[1];
+    CU(cudaMemcpyAsync(h_flags_[turn], flags_, (size_t)(4 + nw) * 4, cudaMemcpyDeviceToHost, stream_));
+    CU(cudaEventRecord(done_[turn], stream_));
+    n_of_[turn] = nw;
+    logprobs_of_[turn] = want_logprobs;
+    *ticket = turn;
+    turn_ ^= 1;
+    return true;
+  }
+
+  bool collect(int ticket, std::vector<int>* tokens, std::vector<float>* logprobs, std::string* err) override {
+    CU(cudaEventSynchronize(done_[ticket]));
+    const int* flags = h_flags_[ticket];
+    if (flags[0] || flags[1]) {
+      const int a = flags[0], b = flags[1];
       cudaMemsetAsync(flags_, 0, 8, stream_);
       if (a) return *err = "a kernel met an out-of-range token or position id", false;
       if (b & SGLC_FLAG_INDEX) return *err = "a kernel of the bounds-check build met an index outside its range", false;
       return *err = "a tensor-core kernel gave up on a bounded wait; its output is invalid", false;
     }
-    tokens->assign(h_out_, h_out_ + nw);
-    if (want_logprobs) logprobs->assign(h_logprob_, h_logprob_ + nw);
+    tokens->assign(h_out_[ticket], h_out_[ticket] + n_of_[ticket]);
+    if (logprobs_of_[ticket]) logprobs->assign(h_logprob_[ticket], h_logprob_[ticket] + n_of_[ticket]);
     return true;
   }
 
@@ -721,7 +755,7 @@ class DeviceRunner : public StepRunner {
   // step varies in lies in device arrays at fixed addresses.  A shape runs as plain launches the
   // first time it is seen and is captured the second time; a step of single tokens, which will
   // come again, is captured the first time.
-  bool forward(WalkStep* s, std::string* err) {
+  bool forward(WalkStep* s, bool ids_on_device, std::string* err) {
     if (!opt_.use_graphs) {
       if (!walk(s, err)) return false;
       launches += s->launches;
@@ -730,7 +764,7 @@ class DeviceRunner : public StepRunner {
     const int bound = graph_bound(*s);
     s->max_keys = bound;
     const GraphKey key{s->T, s->R, s->n_want, s->max_q_len > 1 ? (s->max_q_len + 127) / 128 : 0, bound, s->n_decode,
-                       s->decode_ordered};
+                       s->decode_ordered + 2 * (ids_on_device ? 1 : 0)};      // (the token array's address is captured)
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
       const bool steady = s->n_decode == s->T && plain_steps_ > 0;
@@ -773,16 +807,21 @@ class DeviceRunner : public StepRunner {
   }
 
   bool sample(const std::vector<StepItem>& items, const std::vector<double>& uniforms, int nw, bool want_logprobs,
-              std::string* err) {
+              int turn, std::string* err) {
+    int* const h_params = h_params_[turn];
     // records of 10 words: temperature, top_p, min_p, u, top_k, the three penalties, and the
     // row's range of (token, count) pairs (csrc/sampling.cu)
     std::vector<int> hist;                       // token, count, token, count, ...
     int row = 0;
+    bool plain_greedy = true;                    // every row: argmax and nothing else
+    for (const StepItem& it : items)
+      if (it.sampled && !(it.r->sp.greedy() && !it.r->sp.has_penalties())) plain_greedy = false;
+    const bool records_there = plain_greedy && greedy_rows_ >= nw;   // the device already holds nw such records
     for (const StepItem& it : items) {
       if (!it.sampled) continue;
       const Sampling& sp = it.r->sp;
-      float* f = (float*)(h_params_ + (size_t)row * 10);
-      int* w = h_params_ + (size_t)row * 10;
+      float* f = (float*)(h_params + (size_t)row * 10);
+      int* w = h_params + (size_t)row * 10;
       const int begin = (int)hist.size() / 2;
       if (sp.has_penalties() && !it.r->gen.empty()) {
         std::map<int, int> counts;
@@ -815,7 +854,8 @@ class DeviceRunner : public StepRunner {
       CU(cudaMemcpyAsync(d_hist_tok_, h_hist_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, stream_));
       CU(cudaMemcpyAsync(d_hist_cnt_, h_hist_ + hist_cap_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, stream_));
     }
-    CU(cudaMemcpyAsync(d_params_, h_params_, (size_t)nw * 40, cudaMemcpyHostToDevice, stream_));
+    if (!records_there) CU(cudaMemcpyAsync(d_params_, h_params, (size_t)nw * 40, cudaMemcpyHostToDevice, stream_));
+    greedy_rows_ = plain_greedy ? std::max(greedy_rows_, nw) : 0;
     const int code = k_->sample(logits_, dm_->wm.vocab, dm_->wm.vocab, nw, d_params_, d_hist_tok_, d_hist_cnt_, d_out_,
                                 want_logprobs ? d_logprob_ : nullptr, stream_);
     ++launches;
@@ -841,9 +881,12 @@ class DeviceRunner : public StepRunner {
   int *h_ = nullptr, *d_ = nullptr;
   unsigned char* ws_ = nullptr;
   long long ws_bytes_ = 0;
-  float *logits_ = nullptr, *tc_ws_ = nullptr, *d_logprob_ = nullptr, *h_logprob_ = nullptr;
-  int *tc_counters_ = nullptr, *flags_ = nullptr, *h_flags_ = nullptr;
-  int *h_params_ = nullptr, *d_params_ = nullptr, *d_out_ = nullptr, *h_out_ = nullptr;
+  float *logits_ = nullptr, *tc_ws_ = nullptr, *d_logprob_ = nullptr, *h_logprob_[2] = {nullptr, nullptr};
+  int *tc_counters_ = nullptr, *flags_ = nullptr, *h_flags_[2] = {nullptr, nullptr};
+  int *h_params_[2] = {nullptr, nullptr}, *d_params_ = nullptr, *d_out_ = nullptr, *h_out_[2] = {nullptr, nullptr};
+  cudaEvent_t done_[2] = {nullptr, nullptr};
+  int turn_ = 0, n_of_[2] = {0, 0}, greedy_rows_ = 0;
+  bool logprobs_of_[2] = {false, false};
   int *d_hist_tok_ = nullptr, *d_hist_cnt_ = nullptr, *h_hist_ = nullptr;
   std::vector<const int*> bts_, slots_;
   std::vector<void*> dev_, pinned_;
@@ -881,6 +924,7 @@ SGLC_API void sglc_engine_options_default(sglc_engine_options* o) {
   o->prefill_chunk = 512;
   o->use_graphs = 1;
   o->eos_token_id = -2;
+  o->run_ahead = 1;
 }
 
 SGLC_API sglc_engine* sglc_engine_new(const char* model_dir, const sglc_engine_options* options, char* err, int err_len) {
@@ -934,7 +978,7 @@ SGLC_API sglc_engine* sglc_engine_new(const char* model_dir, const sglc_engine_o
   e->eos = o.eos_token_id == -2 ? m.eos : (o.eos_token_id >= 0 ? o.eos_token_id : -1);
   const int budget = o.token_budget > 0 ? std::min(o.token_budget, o.max_step_tokens) : o.max_step_tokens;
   e->sched.reset(new Scheduler(e->cache.get(), e->runner.get(), m.vocab, m.positions, e->eos, o.seed, o.prefill_chunk,
-                               budget, o.want_logprobs != 0));
+                               budget, o.want_logprobs != 0, o.run_ahead != 0));
   return e.release();
 }
 
@@ -1002,6 +1046,7 @@ SGLC_API void sglc_engine_get_stats(sglc_engine* e, sglc_stats* out) {
   out->n_running = s.n_running; out->n_waiting = s.n_waiting; out->pool_pages = s.pool_pages; out->pool_free = s.pool_free;
   out->n_preempt = s.n_preempt; out->prefill_chunk = s.prefill_chunk; out->n_steps = s.n_steps;
   out->recomputed_tokens = s.recomputed_tokens;
+  out->steps_ahead = s.steps_ahead;
   if (e->device_runner) {
     out->graph_replays = e->device_runner->graph_replays;
     out->launches = e->device_runner->launches;
@@ -1037,6 +1082,73 @@ SGLC_API int sglc_engine_check(sglc_engine* e) {
 }
 
 SGLC_API const char* sglc_engine_last_error(sglc_engine* e) { return e->last_error.c_str(); }
+
+// The page tables alone under a random order of operations (requests arrive, grow by portions of
+// any size, are cut back, end), two cache groups, one with a window: after every operation the
+// invariants hold, a request's table covers its length, and the windowed group holds no page that
+// no later query can see.  0, or -1 with the reason in err.
+SGLC_API int sglc_pages_selftest(int page_size, int n_pages, int max_requests, int window, unsigned seed, int n_ops,
+                                 char* err, int err_len) {
+  CacheTables t(page_size, n_pages, max_requests, {0, window});
+  uint64_t state = request_stream(seed, 1);
+  auto rnd = [&](int n) { return (int)(next_uniform(&state) * n); };
+  std::vector<long long> live;
+  long long next = 1;
+  std::string why;
+  auto fail = [&](const std::string& what) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", what.c_str());
+    return -1;
+  };
+  for (int op = 0; op < n_ops; ++op) {
+    const int kind = rnd(10);
+    if (kind < 2 || live.empty()) {
+      if (t.n_free_slots() == 0) continue;
+      if (t.add(next) < 0) return fail("add refused with a free slot");
+      live.push_back(next++);
+    } else if (kind < 7) {
+      const long long r = live[rnd((int)live.size())];
+      const int new_len = t.length(r) + 1 + rnd(3 * page_size);
+      const bool can = t.can_extend_all({{r, new_len}});
+      const int before = t.length(r);
+      const bool did = t.extend(r, new_len);
+      if (can != did) return fail("can_extend_all and extend disagree");
+      if (t.length(r) != (did ? new_len : before)) return fail("extend left a wrong length");
+    } else if (kind < 8) {
+      const long long r = live[rnd((int)live.size())];
+      const int new_len = rnd(t.length(r) + 1);
+      const int before = t.length(r);
+      if (t.truncate(r, new_len)) {
+        if (t.length(r) != new_len) return fail("truncate left a wrong length");
+      } else if (t.length(r) != before) {
+        return fail("a refused truncate changed the length");
+      }
+    } else {
+      const int i = rnd((int)live.size());
+      if (!t.free(live[i])) return fail("free refused a live request");
+      if (t.free(live[i])) return fail("a request could be freed twice");
+      live.erase(live.begin() + i);
+    }
+    if (!t.check(&why)) return fail(why);
+    for (long long r : live) {
+      const int len = t.length(r), blocks = (len + page_size - 1) / page_size;
+      for (int g = 0; g < 2; ++g) {
+        const std::vector<int>& tab = t.table(g, r);
+        if ((int)tab.size() < blocks) return fail("a block table is shorter than its request");
+        // every position a query at `len` or later may see has its page
+        const int first_pos = (g == 1 && window > 0 && len - window + 1 > 0) ? len - window + 1 : 0;
+        for (int b = first_pos / page_size; b < blocks; ++b)
+          if (tab[b] < 0) return fail("a page that is still visible was given back");
+        if (g == 0)
+          for (int b = 0; b < blocks; ++b)
+            if (tab[b] < 0) return fail("a group without a window gave a page back");
+      }
+    }
+  }
+  for (long long r : live) t.free(r);
+  if (!t.check(&why)) return fail(why);
+  if (t.n_free_pages() != n_pages || t.n_free_slots() != max_requests) return fail("pages or slots were lost");
+  return 0;
+}
 SGLC_API int sglc_engine_vocab_size(sglc_engine* e) { return e->model.spec.vocab; }
 SGLC_API int sglc_engine_max_positions(sglc_engine* e) { return e->model.spec.positions; }
 SGLC_API int sglc_engine_eos_token_id(sglc_engine* e) { return e->eos; }

@@ -52,6 +52,9 @@ typedef struct sglc_engine_options {
   int use_graphs;                 /* replay CUDA graphs of step shapes seen before */
   int eos_token_id;               /* -2: the model's own (config.json), -1: none */
   int want_logprobs;
+  int run_ahead;                  /* 1: while every running request just decodes, a step's ids are read one call
+                                     later and the next step is queued behind it without the host having seen
+                                     them (sglc_engine_step then reports a request's end one call later) */
   int dry_run;                    /* 1: no device at all: configuration, tensor checks, page tables and scheduling
                                      run, tokens come from a fixed formula (for tests on machines without a GPU) */
   const char* library_dir;        /* where the kernel libraries are; null: beside this library */
@@ -60,7 +63,7 @@ typedef struct sglc_engine_options {
 typedef struct sglc_stats {       /* the reference's counters (include/sgl/scheduler.h:19-31) that apply */
   long long prefill_tokens, decode_tokens, n_finished, n_running, n_waiting;
   long long pool_pages, pool_free, n_preempt, prefill_chunk, n_steps, recomputed_tokens;
-  long long graph_replays, launches, weight_bytes, cache_bytes;
+  long long graph_replays, launches, weight_bytes, cache_bytes, steps_ahead;
 } sglc_stats;
 
 enum { SGLC_FINISH_NONE = 0, SGLC_FINISH_EOS = 1, SGLC_FINISH_STOP = 2, SGLC_FINISH_LENGTH = 3,

@@ -21,14 +21,14 @@ class COptions(C.Structure):
                 ("max_tokens", C.c_longlong), ("max_requests", C.c_int), ("max_step_tokens", C.c_int),
                 ("prefill_chunk", C.c_int), ("token_budget", C.c_int), ("seed", C.c_ulonglong),
                 ("use_graphs", C.c_int), ("eos_token_id", C.c_int), ("want_logprobs", C.c_int),
-                ("dry_run", C.c_int), ("library_dir", C.c_char_p)]
+                ("run_ahead", C.c_int), ("dry_run", C.c_int), ("library_dir", C.c_char_p)]
 
 
 class CStats(C.Structure):
     _fields_ = [(n, C.c_longlong) for n in
                 ("prefill_tokens", "decode_tokens", "n_finished", "n_running", "n_waiting", "pool_pages",
                  "pool_free", "n_preempt", "prefill_chunk", "n_steps", "recomputed_tokens", "graph_replays",
-                 "launches", "weight_bytes", "cache_bytes")]
+                 "launches", "weight_bytes", "cache_bytes", "steps_ahead")]
 
 
 FINISH = {0: None, 1: "eos", 2: "stop", 3: "length", 4: "context", 5: "abort"}
@@ -78,7 +78,7 @@ class CEngine:
 
     def __init__(self, model_dir, seed=0, dtype="bfloat16", device=0, page_size=16, n_pages=None, max_tokens=None,
                  max_requests=64, max_step_tokens=2048, prefill_chunk=512, token_budget=None, want_logprobs=False,
-                 use_graphs=True, eos_token_id="from_model", dry_run=False):
+                 use_graphs=True, eos_token_id="from_model", run_ahead=True, dry_run=False):
         self.lib = _lib(dry_run)
         o = COptions()
         self.lib.sglc_engine_options_default(C.byref(o))
@@ -89,6 +89,7 @@ class CEngine:
         o.max_requests, o.max_step_tokens = int(max_requests), int(max_step_tokens)
         o.prefill_chunk, o.token_budget, o.seed = int(prefill_chunk or 0), int(token_budget or 0), int(seed)
         o.use_graphs, o.want_logprobs, o.dry_run = int(use_graphs), int(want_logprobs), int(dry_run)
+        o.run_ahead = int(run_ahead)
         o.eos_token_id = -2 if eos_token_id == "from_model" else (-1 if eos_token_id is None else int(eos_token_id))
         err = C.create_string_buffer(1 << 16)
         self.h = self.lib.sglc_engine_new(str(model_dir).encode(), C.byref(o), err, len(err))

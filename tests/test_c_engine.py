@@ -65,7 +65,8 @@ def drain(s):
 
 def test_the_interface_generates_and_reports(tmp_path):
     d = model_dir(tmp_path)
-    e = CEngine(d, dry_run=True, page_size=4, n_pages=16, max_requests=4, max_step_tokens=8, prefill_chunk=6)
+    e = CEngine(d, dry_run=True, run_ahead=False, page_size=4, n_pages=16, max_requests=4, max_step_tokens=8,
+                prefill_chunk=6)
     assert e.vocab_size == 50 and e.max_positions == 40 and e.eos_token_id is None
     a = e.submit_ids(list(range(10)), max_new=3)
     assert a == 1
@@ -116,7 +117,7 @@ def test_finishing_rules(tmp_path):
     e.run_until_done()
     got = drain(e)[r]
     assert e.last_finish == "context" and len(got) + 36 <= 40
-    e = CEngine(d, dry_run=True, max_requests=1)
+    e = CEngine(d, dry_run=True, run_ahead=False, max_requests=1)
     a, b = e.submit_ids([1, 2, 3, 4, 5], 10), e.submit_ids([1, 2, 3], 10)
     e.step()
     assert e.abort(b) == 0 and e.abort(a) == 0 and e.abort(a) == -1 and e.abort(12345) == -1
@@ -130,7 +131,7 @@ def test_decisions_equal_the_python_schedulers_under_random_arrivals(tmp_path, s
     preemptions, same output: few pages, so that requests are preempted and recomputed."""
     rng = random.Random(seed)
     kw = dict(page_size=4, n_pages=10, max_requests=3, max_step_tokens=12)
-    ce = CEngine(model_dir(tmp_path), dry_run=True, prefill_chunk=5, seed=seed, **kw)
+    ce = CEngine(model_dir(tmp_path), dry_run=True, run_ahead=False, prefill_chunk=5, seed=seed, **kw)
     fe = FormulaEngine(vocab=50, max_positions=40, **kw)
     ps = Scheduler(fe, seed=seed, prefill_chunk=5, sampler=FormulaSampler(50))
     pending = [([rng.randrange(50) for _ in range(rng.randrange(1, 14))], rng.randrange(1, 9)) for _ in range(14)]
@@ -155,7 +156,8 @@ def test_decisions_equal_the_python_schedulers_under_random_arrivals(tmp_path, s
 
 def test_when_pages_run_out_the_latest_arrival_is_preempted_and_recomputed(tmp_path):
     # 6 pages of 4 positions; three requests of 6 prompt tokens that each grow to 14
-    e = CEngine(model_dir(tmp_path), dry_run=True, page_size=4, n_pages=6, max_step_tokens=32, max_requests=4)
+    e = CEngine(model_dir(tmp_path), dry_run=True, run_ahead=False, page_size=4, n_pages=6, max_step_tokens=32,
+                max_requests=4)
     prompts = [[1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12], [13, 14, 15, 16, 17, 18]]
     ids = [e.submit_ids(p, 8) for p in prompts]
     preempted = set()
@@ -185,6 +187,50 @@ def drain_ids(e):
         if g is None:
             return list(DONE)
         DONE[g[0]] = g[1]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_steps_queued_ahead_change_no_output(tmp_path, seed):
+    """run_ahead reads a step's ids one call later and queues the next step of single tokens
+    before it has seen them: the same output, request by request, as reading every step at once;
+    requests that end by eos, a stop id, their length or the model's positions while a step with
+    them is queued have that step's id dropped; aborts in between; few pages."""
+    d = model_dir(tmp_path)
+    outs = []
+    for ahead in (False, True):
+        rng = random.Random(seed)
+        e = CEngine(d, dry_run=True, run_ahead=ahead, page_size=4, n_pages=12, max_requests=3, max_step_tokens=12,
+                    prefill_chunk=5, seed=seed, eos_token_id=7)
+        pending = [([rng.randrange(50) for _ in range(rng.randrange(1, 14))], rng.randrange(1, 25),
+                    SamplingParams(stop_ids=[rng.randrange(50)], ignore_eos=rng.random() < 0.3)) for _ in range(16)]
+        submitted, reasons, steps = [], {}, 0
+        while (pending or e.nactive()) and steps < 4000:
+            if pending and rng.random() < 0.3:
+                p, n, sp = pending.pop()
+                submitted.append(e.submit_ids(p, n, sp))
+                if len(submitted) == 5:
+                    # (aborted before it has run a step: whatever is in flight, it generated nothing)
+                    assert e.abort(submitted[-1]) == 0
+            e.step()
+            assert e.check()
+            steps += 1
+        assert e.nactive() == 0
+        # two more that arrive together and decode side by side with nobody waiting
+        for p in ([1, 2, 3], [4, 5, 6, 7]):
+            assert e.submit_ids(p, 12, SamplingParams(ignore_eos=True)) > 0
+        e.run_until_done()
+        got = {}
+        while True:
+            g = e.poll()
+            if g is None:
+                break
+            got[g[0]] = (g[1], e.last_finish)
+        st = e.get_stats()
+        assert st.pool_free == st.pool_pages == 12
+        assert (st.steps_ahead > 0) == ahead
+        outs.append(got)
+    assert outs[0] == outs[1]
+    assert {r for _, r in outs[1].values()} >= {"length", "abort"}
 
 
 def test_configuration_errors_name_the_key(tmp_path):
@@ -273,3 +319,17 @@ def test_a_c_program_on_the_interface_generates(tmp_path):
     r = subprocess.run([exe, "--model", str(tmp_path / "nothing"), "--prompt-ids", "5", "--dry-run"],
                        capture_output=True, text=True)
     assert r.returncode == 2 and "no config.json" in r.stderr
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_page_tables_under_random_orders(seed):
+    """The native page tables alone: requests arrive, grow by portions of any size, are cut back
+    and end in random order, in a group with all keys and a group with a window; no page lost,
+    held twice or freed twice, no visible page given back (checked inside the library)."""
+    import ctypes as C
+    from sglang_c_b200.csrc import build
+    lib = build.load("host_engine")
+    err = C.create_string_buffer(512)
+    for page_size, n_pages, window in ((4, 24, 9), (16, 12, 40), (1, 64, 5)):
+        rc = lib.sglc_pages_selftest(page_size, n_pages, 5, window, seed, 4000, err, len(err))
+        assert rc == 0, err.value.decode()

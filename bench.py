@@ -393,7 +393,8 @@ def time_prefill_c(model_dir, n_prompts, prompt_len, warmup=3):
     from sglang_c_b200.engine.c_api import CEngine
     from sglang_c_b200.sampling import SamplingParams
     e = CEngine(model_dir, dtype="bfloat16", page_size=PAGE, max_tokens=n_prompts * (prompt_len + 64),
-                max_requests=max(n_prompts, 1), max_step_tokens=n_prompts * prompt_len, prefill_chunk=prompt_len)
+                max_requests=max(n_prompts, 1), max_step_tokens=n_prompts * prompt_len, prefill_chunk=prompt_len,
+                run_ahead=False)              # (the call returns with the step's ids)
     rng = np.random.default_rng(99)
     sp = SamplingParams(temperature=0.0, ignore_eos=True)
 

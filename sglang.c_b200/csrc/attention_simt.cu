@@ -31,7 +31,7 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
 
 // W: tokens of a block (a warp each).  Threads beyond the tokens' warps only help to stage tiles.
 template <typename TQ, typename TC, typename TO, int W, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 3 : 4)     // (registers capped so that three blocks of 256 share an SM)
 attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restrict__ cache,
                       const int* __restrict__ block_table, int bt_stride,
                       const int* __restrict__ token_req, const int* __restrict__ positions,
@@ -39,11 +39,13 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
                       float scale, int window, int n_pages, int* err) {
   extern __shared__ __align__(16) float smem[];
   __shared__ int s_req[W], s_lo[W], s_pos[W];
-  const int DP = D + 1;                       // padded key rows: a lane a key without bank conflicts
-  float* Ks = smem;                           // [32][D+1]
+  // padded key rows: a lane a key without bank conflicts (by 4 where rows are read 16 bytes at a time)
+  const bool wide = D % 4 == 0;
+  const int DP = wide ? D + 4 : D + 1;
+  float* Ks = smem;                           // [32][DP]
   float* Vs = Ks + 32 * DP;                   // [32][D]
-  float* qs = Vs + 32 * D;                    // [W][D]
-  float* pw = qs + W * D;                     // [W][32]: a tile's weights
+  float* pw = Vs + 32 * D;                    // [W][32]: a tile's weights (16-byte aligned whatever D is)
+  float* qs = pw + W * 32;                    // [W][D]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y, hk = h / (H / Hkv);
   const int t0 = blockIdx.x * W;
@@ -101,8 +103,7 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
               load4(kp + d, k4);
               load4(kp + v_off + d, v4);
             }
-#pragma unroll
-            for (int i = 0; i < 4; i++) Ks[j * DP + d + i] = k4[i];
+            *reinterpret_cast<float4*>(&Ks[j * DP + d]) = make_float4(k4[0], k4[1], k4[2], k4[3]);
             *reinterpret_cast<float4*>(&Vs[j * D + d]) = make_float4(v4[0], v4[1], v4[2], v4[3]);
           }
         } else {
@@ -120,7 +121,18 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
         const float* qv = qs + warp * D;
         const float* kr = Ks + lane * DP;
         float sc = 0.0f;
-        for (int d = 0; d < D; d++) sc = fmaf(qv[d], kr[d], sc);
+        if (wide) {                           // (the same additions in the same order, four a load)
+          for (int d = 0; d < D; d += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qv + d);
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
+            sc = fmaf(q4.x, k4.x, sc);
+            sc = fmaf(q4.y, k4.y, sc);
+            sc = fmaf(q4.z, k4.z, sc);
+            sc = fmaf(q4.w, k4.w, sc);
+          }
+        } else {
+          for (int d = 0; d < D; d++) sc = fmaf(qv[d], kr[d], sc);
+        }
         sc = valid ? sc * scale : -INFINITY;
         const float m_new = fmaxf(m, warp_max(sc));
         const float corr = expf(m - m_new);                             // (first tile: exp(-inf) = 0)
@@ -129,12 +141,19 @@ attention_simt_kernel(const TQ* __restrict__ q, int q_stride, const TC* __restri
         m = m_new;
         pw[warp * 32 + lane] = p;
         __syncwarp();
+        float pj[32];                         // the tile's weights, read once for all output columns
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 p4 = *reinterpret_cast<const float4*>(&pw[warp * 32 + j]);
+          pj[j] = p4.x; pj[j + 1] = p4.y; pj[j + 2] = p4.z; pj[j + 3] = p4.w;
+        }
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const int d = lane + 32 * i;
           if (d < D) {
             float a = acc[i] * corr;
-            for (int j = 0; j < 32; j++) a = fmaf(pw[warp * 32 + j], Vs[j * D + d], a);
+#pragma unroll
+            for (int j = 0; j < 32; j++) a = fmaf(pj[j], Vs[j * D + d], a);
             acc[i] = a;
           }
         }
@@ -173,7 +192,7 @@ SGLC_API int sglc_attention_simt(const void* q, int q_stride, const void* cache,
   // single tokens of many requests share nothing: a token a block; portions: eight tokens a block
   const bool single = max_q_len <= 1;
   const int W = single ? 1 : 8;
-  const size_t smem = ((size_t)32 * (D + 1) + (size_t)32 * D + (size_t)W * D + (size_t)W * 32) * sizeof(float);
+  const size_t smem = ((size_t)32 * (D % 4 == 0 ? D + 4 : D + 1) + (size_t)32 * D + (size_t)W * D + (size_t)W * 32) * sizeof(float);
   dim3 grid((T + W - 1) / W, H);
 #define LAUNCH(TQ, TC, TO, WW, TH)                                                                     \
   do {                                                                                                 \

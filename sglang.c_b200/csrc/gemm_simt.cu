@@ -91,7 +91,7 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float
 constexpr int LM = 128, LK = 16, LP = LM + 4;
 
 template <int NW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)          // two blocks an SM: at most 128 registers a thread
 gemm_simt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
                        float* __restrict__ out, float* __restrict__ residual, int M, int N, int K, int lda,
                        int ldo, int act) {

@@ -57,6 +57,12 @@ struct GemmArgs {
   int act;
   int* err;                // set to 1 if a bounded wait ran out
   int tiles_p, n_tiles;    // many-token kernel: row tiles, and all tiles (a block walks several)
+  // many-token kernel, optional: the output columns from kv_q_cols on are keys and values of the
+  // step's tokens ([keys of kv_heads heads of kv_dim][values likewise]) and go straight into the
+  // paged cache [page][2][kv_heads][kv_page][kv_dim] at kv_slots[token] instead of into `out`
+  void* kv_cache;
+  const int* kv_slots;
+  int kv_q_cols, kv_heads, kv_dim, kv_page, kv_n_pages;
 };
 
 struct SharedCtl {
@@ -581,7 +587,40 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
       ok = s_go[buf] != 0;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
-      if (ok && a.tma_out) {
+      if (ok && a.kv_cache != nullptr && qt * BN >= a.kv_q_cols) {
+        // a tile of keys or values: a thread has a token's row and writes it where the token's
+        // slot says, 64 bytes a chunk (a chunk of 32 columns lies within one head)
+        const int tok = pt * BM + row;
+        const int slot = tok < a.M ? a.kv_slots[tok] : -1;
+        const bool live = slot >= 0 && sglc_index_ok(slot / a.kv_page, a.kv_n_pages, a.err);
+        const size_t page = live ? (size_t)(slot / a.kv_page) : 0, off = live ? (size_t)(slot % a.kv_page) : 0;
+        const int kv_width = a.kv_heads * a.kv_dim;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
+          }
+          const int cc = qt * BN + c - a.kv_q_cols;
+          if (!live || qt * BN + c >= a.N) continue;
+          const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / a.kv_dim, d = rem - head * a.kv_dim;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.kv_cache) +
+                               (((page * 2 + which) * a.kv_heads + head) * a.kv_page + off) * a.kv_dim + d;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) {
+            __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+              hh[x] = __floats2bfloat162_rn(act_tc(__uint_as_float(r[8 * q4 + 2 * x]) + bias_s[c + 8 * q4 + 2 * x], a.act),
+                                            act_tc(__uint_as_float(r[8 * q4 + 2 * x + 1]) + bias_s[c + 8 * q4 + 2 * x + 1], a.act));
+            *reinterpret_cast<uint4*>(dst + 8 * q4) = *reinterpret_cast<uint4*>(hh);
+          }
+        }
+      } else if (ok && a.tma_out) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -799,16 +838,22 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
 // A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
 // null; out [M,N] rows ldo apart (bfloat16, or float if out_f32), or residual (float, in place).
 // err: device int, set to 1 if a wait ran out.
-SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void* out,
-                          float* residual, int M, int N, int K, int lda, int ldo, int out_f32,
-                          int act, int* err, cudaStream_t stream) {
+struct KvScatter {
+  void* cache;
+  const int* slots;
+  int q_cols, heads, dim, page, n_pages;
+};
+
+static int gemm_tc_run(const void* A, const void* W, const float* bias, void* out, float* residual, int M, int N,
+                       int K, int lda, int ldo, int out_f32, int act, int* err, const KvScatter* kv,
+                       cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SGLC_OK;
   if (K <= 0) return SGLC_ERR_ARGUMENT;
   if (K % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return SGLC_ERR_UNSUPPORTED;
   int swap, bn, splits, per, tp, tq;
   plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
-  GemmArgs a;
+  GemmArgs a = {};
   a.M = M; a.N = N; a.K = K;
   a.swap = swap;
   a.kb_total = (K + BK - 1) / BK;
@@ -834,6 +879,14 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
     if (residual) a.tma_out = get_map(&mo, residual, M, N, ldo, BM | 0x10000u) ? 1 : 0;
     else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
   }
+  if (kv) {
+    // only the many-token kernel scatters, whole tiles of keys or values, 32-column chunks within a head
+    if (swap || !a.tma_out || kv->dim % 32 != 0 || kv->q_cols % bn != 0 || N != kv->q_cols + 2 * kv->heads * kv->dim ||
+        kv->page <= 0 || ((uintptr_t)kv->cache & 15))
+      return SGLC_ERR_UNSUPPORTED;
+    a.kv_cache = kv->cache; a.kv_slots = kv->slots; a.kv_q_cols = kv->q_cols; a.kv_heads = kv->heads;
+    a.kv_dim = kv->dim; a.kv_page = kv->page; a.kv_n_pages = kv->n_pages;
+  }
   if (!swap) {
     a.tiles_p = tp;
     a.n_tiles = tp * tq;
@@ -854,4 +907,25 @@ SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void*
     case 128: return launch<128>(mp, mq, mo, a, grid, stream);
   }
   return SGLC_ERR_ARGUMENT;
+}
+
+SGLC_API int sglc_gemm_tc(const void* A, const void* W, const float* bias, void* out,
+                          float* residual, int M, int N, int K, int lda, int ldo, int out_f32,
+                          int act, int* err, cudaStream_t stream) {
+  return gemm_tc_run(A, W, bias, out, residual, M, N, K, lda, ldo, out_f32, act, err, nullptr, stream);
+}
+
+// The fused query/key/value projection of a step with prompt portions: out[:, :q_cols] takes the
+// queries as sglc_gemm_tc would write them; the columns from q_cols on (keys of `heads` heads of
+// `dim`, then values likewise) go straight into the paged cache
+// [n_pages][2][heads][page_size][dim] (bfloat16) at slots[token] = page * page_size + offset, and
+// not into `out`.  SGLC_ERR_UNSUPPORTED (nothing launched) when the product would not take the
+// many-token kernel or the sizes do not fall on its tiles: the caller then projects and writes
+// the cache separately.
+SGLC_API int sglc_gemm_tc_kv(const void* A, const void* W, const float* bias, void* out, int M, int N, int K, int lda,
+                             int ldo, int act, void* cache, const int* slots, int q_cols, int heads, int dim,
+                             int page_size, int n_pages, int* err, cudaStream_t stream) {
+  if (!cache || !slots || heads <= 0 || dim <= 0) return SGLC_ERR_ARGUMENT;
+  const KvScatter kv{cache, slots, q_cols, heads, dim, page_size, n_pages};
+  return gemm_tc_run(A, W, bias, out, nullptr, M, N, K, lda, ldo, 0, act, err, &kv, stream);
 }

@@ -107,7 +107,7 @@ typedef int (*fn_sample)(float*, int, int, int, const void*, const int*, const i
 // which library a launcher lives in (engine/host_model.py has the same table)
 const char* const LAUNCHER_LIB[][2] = {
     {"sglc_embed", "embed"}, {"sglc_layernorm", "layernorm"}, {"sglc_gemm_simt", "gemm_simt"},
-    {"sglc_gemm_tc", "gemm_tc"}, {"sglc_gemm_few_supports", "gemm_few"}, {"sglc_gemm_few", "gemm_few"},
+    {"sglc_gemm_tc", "gemm_tc"}, {"sglc_gemm_tc_kv", "gemm_tc"}, {"sglc_gemm_few_supports", "gemm_few"}, {"sglc_gemm_few", "gemm_few"},
     {"sglc_kv_write", "kv_cache"}, {"sglc_attention_simt", "attention_simt"},
     {"sglc_attention_prefill_tc", "attention_prefill_tc"}, {"sglc_attention_decode_splits", "attention_decode"},
     {"sglc_attention_decode_scratch", "attention_decode"}, {"sglc_attention_decode", "attention_decode"},

@@ -87,6 +87,9 @@ def _dt(t, what):
         raise KernelError(f"{what}: dtype {t.dtype} is not handled (float32 or bfloat16)") from None
 
 
+UNSUPPORTED = -2      # a launcher's "size not supported by this kernel"
+
+
 def _need_cuda(*tensors):
     for t in tensors:
         if t is not None and not t.is_cuda:
@@ -308,6 +311,34 @@ def gemm_tc(a, w, bias, out=None, residual=None, act=None, supported=False):
                             a.stride(0), dst.stride(0), 1 if dst.dtype == torch.float32 else 0,
                             ACT[act], _ptr(err), _stream())
     _check(lib, code, f"gemm_tc M={M} N={N} K={K}")
+
+
+def gemm_tc_kv(a, w, bias, out, cache, slots, n_heads, n_kv_heads, head_dim):
+    """The query/key/value projection of a step with prompt portions, with the cache write in its
+    epilogue: out[:, :n_heads*head_dim] takes the queries; keys and values go straight into the
+    paged cache [n_pages, 2, n_kv_heads, page_size, head_dim] at slots[token].  Returns False,
+    having launched nothing, when the product would not take the many-token kernel or the sizes
+    do not fall on its tiles (the caller then projects and writes the cache separately)."""
+    _need_cuda(a, w, bias, out, cache, slots)
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w) or w.shape[1] != K or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
+            or out.shape[1] != N or out.stride(1) != 1 or not cache.is_contiguous() \
+            or N != (n_heads + 2 * n_kv_heads) * head_dim:
+        return False
+    _i32(slots, "slots")
+    n_pages, two, Hkv, page_size, D = cache.shape
+    if two != 2 or Hkv != n_kv_heads or D != head_dim or slots.numel() < M:
+        raise KernelError("gemm_tc_kv: the cache or the slots do not match the projection")
+    lib = build.load("gemm_tc")
+    err = _tc_buffers(a.device)[2]
+    code = lib.sglc_gemm_tc_kv(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, a.stride(0), out.stride(0), ACT[None],
+                               _ptr(cache), _ptr(slots), n_heads * head_dim, n_kv_heads, head_dim, page_size, n_pages,
+                               _ptr(err), _stream())
+    if code == UNSUPPORTED:
+        return False
+    _check(lib, code, f"gemm_tc_kv M={M} N={N} K={K}")
+    return True
 
 
 FEW_MAX_TOKENS = 2           # products of so few tokens go to gemm_few ...

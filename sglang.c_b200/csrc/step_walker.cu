@@ -33,6 +33,8 @@ typedef int (*fn_gemm_simt)(const void*, const void*, const float*, void*, float
                             int, cudaStream_t);
 typedef int (*fn_gemm_tc)(const void*, const void*, const float*, void*, float*, int, int, int, int, int, int, int,
                           int*, cudaStream_t);
+typedef int (*fn_gemm_tc_kv)(const void*, const void*, const float*, void*, int, int, int, int, int, int, void*,
+                             const int*, int, int, int, int, int, int*, cudaStream_t);
 typedef int (*fn_gemm_few_supports)(int, int, int, int);
 typedef int (*fn_gemm_few)(const void*, const void*, const float*, void*, float*, int, int, int, int, int, int, int,
                            cudaStream_t);
@@ -64,6 +66,7 @@ struct Bound {
   fn_layernorm layernorm;
   fn_gemm_simt gemm_simt;
   fn_gemm_tc gemm_tc;
+  fn_gemm_tc_kv gemm_tc_kv;
   fn_gemm_few_supports gemm_few_supports;
   fn_gemm_few gemm_few;
   fn_kv_write kv_write;
@@ -77,7 +80,7 @@ struct Bound {
   fn_attention_decode_stream attention_decode_stream;
 } g = {};
 
-const char* const NAMES[] = {"sglc_embed", "sglc_layernorm", "sglc_gemm_simt", "sglc_gemm_tc",
+const char* const NAMES[] = {"sglc_embed", "sglc_layernorm", "sglc_gemm_simt", "sglc_gemm_tc", "sglc_gemm_tc_kv",
                              "sglc_gemm_few_supports", "sglc_gemm_few", "sglc_kv_write", "sglc_attention_simt",
                              "sglc_attention_prefill_tc", "sglc_attention_decode_splits",
                              "sglc_attention_decode_scratch", "sglc_attention_decode", "sglc_attention_decode_tma",
@@ -184,8 +187,27 @@ struct Walk {
   }
 
   // keys and values into the cache, then causal attention over it (engine/runtime.py: attend)
+  // the query/key/value projection; true if its epilogue has written keys and values into the
+  // cache (engine/runtime.py: project_qkv)
+  bool project_qkv(const void* h, int T, const WalkLayer& L, const WalkCall& c, void* qkv, int wq) {
+    if (rc) return false;
+    const bool tc_ok = m.bf16 && L.qkv.K % 8 == 0 && m.hidden % 8 == 0 && ((uintptr_t)h & 15) == 0 &&
+                       ((uintptr_t)L.qkv.w & 15) == 0;
+    if (tc_ok && c.write && s.max_q_len > 1 && L.qkv.N == (L.n_heads + 2 * L.n_kv_heads) * L.head_dim) {
+      const int code = g.gemm_tc_kv(h, L.qkv.w, L.qkv.bias, qkv, T, L.qkv.N, L.qkv.K, m.hidden, wq, SGLC_ACT_NONE, c.cache,
+                                    s.slots[c.group], L.n_heads * L.head_dim, L.n_kv_heads, L.head_dim, m.page_size,
+                                    c.n_pages, s.tc_err, s.stream);
+      if (code != SGLC_ERR_UNSUPPORTED) {
+        check(code, "gemm_tc_kv");
+        return rc == 0;
+      }
+    }
+    gemm(h, T, m.hidden, L.qkv, qkv, wq, false, nullptr, SGLC_ACT_NONE);
+    return false;
+  }
+
   void attend(const unsigned char* q, const unsigned char* k, const unsigned char* v, int stride, const WalkCall& c,
-              const WalkLayer& L, unsigned char* o, int o_stride) {
+              const WalkLayer& L, unsigned char* o, int o_stride, bool kv_written) {
     if (rc) return;
     const int H = L.n_heads, Hkv = L.n_kv_heads, D = L.head_dim, ps = m.page_size;
     const int* bt = s.block_tables[c.group];
@@ -200,7 +222,7 @@ struct Walk {
                        fuse ? stride : 0, fuse ? slots : nullptr, s.decode_ordered ? s.decode_tokens : nullptr, s.T);
       return;
     }
-    if (c.write)
+    if (c.write && !kv_written)
       if (!check(g.kv_write(k, v, stride, c.cache, slots, s.T, Hkv, D, ps, c.n_pages, dt(), dt(), s.stream), "kv_write"))
         return;
     if (bf16_ok && (D == 64 || D == 128) && L.scale > 0 && o_stride % 8 == 0 && ((uintptr_t)o & 15) == 0) {
@@ -232,10 +254,10 @@ struct Walk {
       const int wq = (H + 2 * Hkv) * D;
       unsigned char* qkv = alloc(T, wq, es);
       if (!qkv) return;
-      gemm(h, T, E, L.qkv, qkv, wq, false, nullptr, SGLC_ACT_NONE);
+      const bool kv_written = project_qkv(h, T, L, c, qkv, wq);
       unsigned char* o = alloc(T, (long long)H * D, es);
       if (!o) return;
-      attend(qkv, qkv + (size_t)H * D * es, qkv + (size_t)(H + Hkv) * D * es, wq, c, L, o, H * D);
+      attend(qkv, qkv + (size_t)H * D * es, qkv + (size_t)(H + Hkv) * D * es, wq, c, L, o, H * D, kv_written);
       gemm(o, T, H * D, L.out, nullptr, E, false, x, SGLC_ACT_NONE);
     }
     off = inner;                                     // the mixer's buffers make room for the feed-forward's

@@ -53,9 +53,22 @@ class Runtime:
             return ops.gemm_tc(a, w, bias, out=out, residual=residual, act=act, supported=True)
         return ops.gemm_simt(a, w, bias, out=out, residual=residual, act=act)
 
-    def attend(self, ctx, q, k, v, binding, grp, out, n_heads, n_kv_heads, head_dim, scale, window):
-        """Put the step's keys and values into the cache (if this call owns it) and run causal
-        attention of the step's queries over the cache."""
+    def project_qkv(self, ctx, h, linear, qkv, binding, grp, n_heads, n_kv_heads, head_dim):
+        """qkv = h·Wᵀ + b for a mixer that owns its cache.  In a step with prompt portions the
+        tensor-core product writes the keys and values into the cache from its epilogue (they
+        are not needed in `qkv` then: the attention kernels of such a step read the cache);
+        returns whether it did, for attend()."""
+        if self.dtype == "bfloat16" and binding.write and ctx.max_q_len > 1 \
+                and ops.gemm_tc_kv(h, linear.weight, linear.bias, qkv, binding.tensor, grp.slots, n_heads,
+                                   n_kv_heads, head_dim):
+            return True
+        linear.forward(ctx, h, out=qkv)
+        return False
+
+    def attend(self, ctx, q, k, v, binding, grp, out, n_heads, n_kv_heads, head_dim, scale, window,
+               kv_written=False):
+        """Put the step's keys and values into the cache (if this call owns it and project_qkv
+        has not done so already) and run causal attention of the step's queries over the cache."""
         cache = binding.tensor
         bf16_ok = self.dtype == "bfloat16" and head_dim % 8 == 0 and q.stride(0) % 8 == 0 \
             and q.data_ptr() % 16 == 0
@@ -72,7 +85,7 @@ class Runtime:
                                         slots=grp.slots if fuse else None,
                                         token_list=ctx.decode_tokens if ctx.decode_ordered else None,
                                         n_tokens=ctx.T)
-        if binding.write:
+        if binding.write and not kv_written:
             ops.kv_write(k, v, cache, grp.slots, n_kv_heads, head_dim)
         if bf16_ok and ops.attention_prefill_tc_supported(q, cache, scale) \
                 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:

@@ -59,14 +59,19 @@ class CausalAttention(Part):
         H, Hkv, D = p["n_heads"], p["n_kv_heads"], p["head_dim"]
         T = h.shape[0]
         qkv = ctx.alloc((T, (H + 2 * Hkv) * D), self.rt.act_dtype)
-        self.qkv.forward(ctx, h, out=qkv)
+        grp = ctx.group(cache.group)
+        if position is None:
+            kv_written = ctx.rt.project_qkv(ctx, h, self.qkv, qkv, cache, grp, H, Hkv, D)
+        else:                        # keys are turned before they are cached
+            self.qkv.forward(ctx, h, out=qkv)
+            kv_written = False
         q = ctx.columns(qkv, 0, H * D)
         k = ctx.columns(qkv, H * D, (H + Hkv) * D)
         v = ctx.columns(qkv, (H + Hkv) * D, (H + 2 * Hkv) * D)
         if position is not None:
             position.rotate(ctx, q, k)
-        grp = ctx.group(cache.group)
         o = ctx.alloc((T, H * D), self.rt.act_dtype)
-        ctx.rt.attend(ctx, q, k, v, cache, grp, o, H, Hkv, D, float(p["scale"]), p.get("window"))
+        ctx.rt.attend(ctx, q, k, v, cache, grp, o, H, Hkv, D, float(p["scale"]), p.get("window"),
+                      kv_written=kv_written)
         self.out.forward(ctx, o, residual=residual)
         return residual

@@ -212,6 +212,50 @@ def test_attention_simt_and_kv_write(case_id, dtype):
     assert torch.equal(out2, out)
 
 
+@pytest.mark.parametrize("M,H,Hkv,D,K,ps", [(300, 4, 4, 64, 256, 16), (1000, 8, 2, 128, 512, 16), (129, 2, 2, 32, 64, 8),
+                                            (2048, 12, 12, 64, 768, 16)])
+def test_gemm_tc_kv_writes_what_projection_and_cache_write_would(M, H, Hkv, D, K, ps):
+    """The query/key/value projection with the cache write in its epilogue: the same queries in
+    `out`, the same bits in the same places of the cache as the plain product followed by
+    kv_write; the key and value columns of `out` are not written; other pages are not touched."""
+    ops = _ops()
+    N = (H + 2 * Hkv) * D
+    a, w, bias = _rand(M, K, dtype=torch.bfloat16, seed=31), _rand(N, K, dtype=torch.bfloat16, seed=32, scale=0.1), \
+        _rand(N, seed=33)
+    n_pages = (M + ps - 1) // ps + 5
+    g = torch.Generator().manual_seed(M)
+    slots = torch.randperm(n_pages * ps, generator=g)[:M].to(torch.int32).to(DEV)      # scattered over the pool
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(a, w, bias, out=plain)
+    want = torch.full((n_pages, 2, Hkv, ps, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.kv_write(plain[:, H * D:(H + Hkv) * D], plain[:, (H + Hkv) * D:], want, slots, Hkv, D)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = torch.full_like(want, 7.0)
+    assert ops.gemm_tc_kv(a, w, bias, out, cache, slots, H, Hkv, D)
+    assert torch.equal(out[:, :H * D], plain[:, :H * D])
+    assert bool(torch.isnan(out[:, H * D:]).all())
+    assert torch.equal(cache, want)
+
+
+def test_gemm_tc_kv_declines_what_it_cannot_do():
+    ops = _ops()
+    for M, H, Hkv, D, K in ((64, 4, 4, 64, 256), (300, 4, 4, 48, 256), (300, 3, 3, 64, 256)):
+        # few tokens (the other orientation); heads that are no multiple of 32 wide; queries that
+        # do not end on a tile (3 x 64 columns with 128-wide tiles is fine only if tiles are 64 wide)
+        N = (H + 2 * Hkv) * D
+        a, w = _rand(M, K, dtype=torch.bfloat16, seed=1), _rand(N, K, dtype=torch.bfloat16, seed=2)
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        cache = torch.zeros(M // 16 + 2, 2, Hkv, 16, D, dtype=torch.bfloat16, device=DEV)
+        slots = torch.arange(M, dtype=torch.int32, device=DEV)
+        done = ops.gemm_tc_kv(a, w, None, out, cache, slots, H, Hkv, D)
+        if done:                       # (the third case may fall on 64-wide tiles)
+            plain = torch.empty_like(out)
+            ops.gemm_tc(a, w, None, out=plain)
+            assert torch.equal(out[:, :H * D], plain[:, :H * D])
+        else:
+            assert float(out.abs().max()) == 0.0 and float(cache.abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_a_far_key(dtype):
     """One key hundreds of positions back carries nearly all the weight: a kernel

@@ -57,12 +57,18 @@ struct GemmArgs {
   int act;
   int* err;                // set to 1 if a bounded wait ran out
   int tiles_p, n_tiles;    // many-token kernel: row tiles, and all tiles (a block walks several)
-  // many-token kernel, optional: the output columns from kv_q_cols on are keys and values of the
-  // step's tokens ([keys of kv_heads heads of kv_dim][values likewise]) and go straight into the
-  // paged cache [page][2][kv_heads][kv_page][kv_dim] at kv_slots[token] instead of into `out`
-  void* kv_cache;
-  const int* kv_slots;
-  int kv_q_cols, kv_heads, kv_dim, kv_page, kv_n_pages;
+};
+
+// The many-token kernel's KV form: the output columns from q_cols on are keys and values of the
+// step's tokens ([keys of `heads` heads of `dim`][values likewise]) and go straight into the paged
+// cache [page][2][heads][page][dim] at slots[token] instead of into `out`.  (Its own structure and
+// its own instantiation of the kernel: the other kernels of this file are compiled as they were
+// without it; their register allocation, and with it their speed, moved when these fields were
+// part of GemmArgs.)
+struct KvArgs {
+  void* cache;
+  const int* slots;
+  int q_cols, heads, dim, page, n_pages;
 };
 
 struct SharedCtl {
@@ -461,10 +467,10 @@ struct StreamCtl {
   int abort_flag;
 };
 
-template <int BN>
+template <int BN, bool KV>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                      const __grid_constant__ CUtensorMap map_out, const GemmArgs a) {
+                      const __grid_constant__ CUtensorMap map_out, const GemmArgs a, const KvArgs kv) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   constexpr int A_BYTES = BM * BK * 2;
@@ -587,14 +593,14 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
       ok = s_go[buf] != 0;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
-      if (ok && a.kv_cache != nullptr && qt * BN >= a.kv_q_cols) {
+      if (KV && ok && qt * BN >= kv.q_cols) {
         // a tile of keys or values: a thread has a token's row and writes it where the token's
         // slot says, 64 bytes a chunk (a chunk of 32 columns lies within one head)
         const int tok = pt * BM + row;
-        const int slot = tok < a.M ? a.kv_slots[tok] : -1;
-        const bool live = slot >= 0 && sglc_index_ok(slot / a.kv_page, a.kv_n_pages, a.err);
-        const size_t page = live ? (size_t)(slot / a.kv_page) : 0, off = live ? (size_t)(slot % a.kv_page) : 0;
-        const int kv_width = a.kv_heads * a.kv_dim;
+        const int slot = tok < a.M ? kv.slots[tok] : -1;
+        const bool live = slot >= 0 && sglc_index_ok(slot / kv.page, kv.n_pages, a.err);
+        const size_t page = live ? (size_t)(slot / kv.page) : 0, off = live ? (size_t)(slot % kv.page) : 0;
+        const int kv_width = kv.heads * kv.dim;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -605,11 +611,11 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
           }
-          const int cc = qt * BN + c - a.kv_q_cols;
+          const int cc = qt * BN + c - kv.q_cols;
           if (!live || qt * BN + c >= a.N) continue;
-          const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / a.kv_dim, d = rem - head * a.kv_dim;
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.kv_cache) +
-                               (((page * 2 + which) * a.kv_heads + head) * a.kv_page + off) * a.kv_dim + d;
+          const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / kv.dim, d = rem - head * kv.dim;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(kv.cache) +
+                               (((page * 2 + which) * kv.heads + head) * kv.page + off) * kv.dim + d;
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) {
             __align__(16) __nv_bfloat162 hh[4];
@@ -766,8 +772,8 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const CUtensorMap& mo, 
   }
   return sglc_launch(gemm_tc_kernel<BN>, grid, dim3(THREADS), smem, stream, a.splits, true, mp, mq, mo, a);
 }
-template <int BN>
-int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a,
+template <int BN, bool KV>
+int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a, const KvArgs& kv,
                   cudaStream_t stream) {
   static int n_sm = 0;
   if (n_sm == 0) {
@@ -783,7 +789,7 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   if (granted == 0) {
     for (; stages >= 2; stages--) {
       const size_t want = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
-      if (cudaFuncSetAttribute(gemm_tc_stream_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+      if (cudaFuncSetAttribute(gemm_tc_stream_kernel<BN, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
           cudaSuccess)
         break;
       cudaGetLastError();
@@ -795,7 +801,7 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   a.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
   int grid = a.n_tiles < n_sm ? a.n_tiles : n_sm;
-  return sglc_launch(gemm_tc_stream_kernel<BN>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a);
+  return sglc_launch(gemm_tc_stream_kernel<BN, KV>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a, kv);
 }
 }  // namespace
 
@@ -838,14 +844,8 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
 // A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
 // null; out [M,N] rows ldo apart (bfloat16, or float if out_f32), or residual (float, in place).
 // err: device int, set to 1 if a wait ran out.
-struct KvScatter {
-  void* cache;
-  const int* slots;
-  int q_cols, heads, dim, page, n_pages;
-};
-
 static int gemm_tc_run(const void* A, const void* W, const float* bias, void* out, float* residual, int M, int N,
-                       int K, int lda, int ldo, int out_f32, int act, int* err, const KvScatter* kv,
+                       int K, int lda, int ldo, int out_f32, int act, int* err, const KvArgs* kv,
                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return SGLC_OK;
   if (K <= 0) return SGLC_ERR_ARGUMENT;
@@ -853,7 +853,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     return SGLC_ERR_UNSUPPORTED;
   int swap, bn, splits, per, tp, tq;
   plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
-  GemmArgs a = {};
+  GemmArgs a;
   a.M = M; a.N = N; a.K = K;
   a.swap = swap;
   a.kb_total = (K + BK - 1) / BK;
@@ -884,13 +884,13 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     if (swap || !a.tma_out || kv->dim % 32 != 0 || kv->q_cols % bn != 0 || N != kv->q_cols + 2 * kv->heads * kv->dim ||
         kv->page <= 0 || ((uintptr_t)kv->cache & 15))
       return SGLC_ERR_UNSUPPORTED;
-    a.kv_cache = kv->cache; a.kv_slots = kv->slots; a.kv_q_cols = kv->q_cols; a.kv_heads = kv->heads;
-    a.kv_dim = kv->dim; a.kv_page = kv->page; a.kv_n_pages = kv->n_pages;
   }
   if (!swap) {
     a.tiles_p = tp;
     a.n_tiles = tp * tq;
-    return bn == 128 ? launch_stream<128>(mp, mq, mo, a, stream) : launch_stream<64>(mp, mq, mo, a, stream);
+    const KvArgs none = {};
+    if (kv) return bn == 128 ? launch_stream<128, true>(mp, mq, mo, a, *kv, stream) : launch_stream<64, true>(mp, mq, mo, a, *kv, stream);
+    return bn == 128 ? launch_stream<128, false>(mp, mq, mo, a, none, stream) : launch_stream<64, false>(mp, mq, mo, a, none, stream);
   }
   int stage_bytes = BM * BK * 2 + bn * BK * 2;
   int budget = swap ? 96 * 1024 : (bn == 128 ? 100 * 1024 : 100 * 1024);
@@ -926,6 +926,6 @@ SGLC_API int sglc_gemm_tc_kv(const void* A, const void* W, const float* bias, vo
                              int ldo, int act, void* cache, const int* slots, int q_cols, int heads, int dim,
                              int page_size, int n_pages, int* err, cudaStream_t stream) {
   if (!cache || !slots || heads <= 0 || dim <= 0) return SGLC_ERR_ARGUMENT;
-  const KvScatter kv{cache, slots, q_cols, heads, dim, page_size, n_pages};
+  const KvArgs kv{cache, slots, q_cols, heads, dim, page_size, n_pages};
   return gemm_tc_run(A, W, bias, out, nullptr, M, N, K, lda, ldo, 0, act, err, &kv, stream);
 }

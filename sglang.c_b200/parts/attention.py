@@ -2,6 +2,7 @@
 from ..cache.needs import CacheNeed
 from .base import Part
 from .linear import Linear, declare_linear
+from .position import PositionEncoding
 from .registry import register_part
 
 
@@ -60,11 +61,14 @@ class CausalAttention(Part):
         T = h.shape[0]
         qkv = ctx.alloc((T, (H + 2 * Hkv) * D), self.rt.act_dtype)
         grp = ctx.group(cache.group)
-        if position is None:
-            kv_written = ctx.rt.project_qkv(ctx, h, self.qkv, qkv, cache, grp, H, Hkv, D)
-        else:                        # keys are turned before they are cached
+        # a position part that acts inside the mixer turns the keys before they are cached: then
+        # the projection cannot write them; one that leaves PositionEncoding.rotate as it is does not
+        turns = position is not None and getattr(type(position), "rotate", None) is not PositionEncoding.rotate
+        if turns:
             self.qkv.forward(ctx, h, out=qkv)
             kv_written = False
+        else:
+            kv_written = ctx.rt.project_qkv(ctx, h, self.qkv, qkv, cache, grp, H, Hkv, D)
         q = ctx.columns(qkv, 0, H * D)
         k = ctx.columns(qkv, H * D, (H + Hkv) * D)
         v = ctx.columns(qkv, (H + Hkv) * D, (H + 2 * Hkv) * D)

@@ -592,6 +592,64 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     return r
 
 
+def only(kind, base, n_layer, steps, warmup):
+    """A handful of steps of one kind, each run as its launches (no graph: a profiler then sees
+    the kernels in launch order), and one line of JSON with their device time."""
+    import numpy as np
+    import torch
+    from sglang_c_b200.engine import Engine, StepEntry
+    tmp = tempfile.mkdtemp(prefix="sglc_bench_")
+    atexit.register(shutil.rmtree, tmp, True)
+    model_dir = make_model(tmp, base, n_layer)
+    dtype = "float32" if kind == "fp32" else "bfloat16"
+    eng = Engine.from_dir(model_dir, dtype=dtype, page_size=PAGE, max_tokens=BATCH * (CONTEXT + 256) + 4096,
+                          max_requests=BATCH, max_step_tokens=PREFILL_TOKENS, use_graphs=False)
+    rng = np.random.default_rng(0)
+    V = eng.plan.vocab_size
+    out = {"only": kind, "n_layer": n_layer, "dtype": dtype}
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    if kind in ("prefill", "fp32"):
+        it = [0]
+
+        def prefill():
+            it[0] += 1
+            reqs = [f"p{it[0]}_{i}" for i in range(2)]
+            for r in reqs:
+                eng.add_request(r)
+            eng.step([StepEntry(r, rng.integers(0, V, size=PREFILL_TOKENS // 2).astype(np.int32), [PREFILL_TOKENS // 2 - 1])
+                      for r in reqs])
+            torch.cuda.synchronize()
+            for r in reqs:
+                eng.end_request(r)
+        timed(prefill, warmup)
+        out["prefill_ms_eager"] = timed(prefill, steps)
+    if kind in ("decode", "fp32"):
+        reqs = [f"d{i}" for i in range(BATCH)]
+        for r in reqs:
+            eng.add_request(r)
+        done = 0
+        while done < CONTEXT:
+            n = min(eng.max_step_tokens // BATCH, CONTEXT - done)
+            eng.step([StepEntry(r, rng.integers(0, V, size=n).astype(np.int32), []) for r in reqs])
+            done += n
+
+        def decode():
+            eng.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in reqs])
+        timed(decode, warmup)
+        out["decode_ms_eager"] = timed(decode, steps)
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -607,6 +665,9 @@ def main():
                          "(64 requests, prompts of 16..1024 tokens, 128 generated each) under `points`")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                     help="decode: the contract's line; mixed: only the mixed workload through the scheduler")
+    ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
+                    help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
+                         "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_main(args)
@@ -619,6 +680,8 @@ def main():
     pk = peaks()
     base = MODELS[args.model]
     n_layer = args.layers or base["n_layer"]
+    if args.only:
+        return only(args.only, base, n_layer, steps, warmup)
     if args.workload == "mixed":
         tmp = tempfile.mkdtemp(prefix="sglc_bench_")
         atexit.register(shutil.rmtree, tmp, True)

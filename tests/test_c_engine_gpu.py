@@ -139,3 +139,35 @@ def test_the_c_program_generates_what_the_python_entry_point_generates(model_dir
     want = generate(s, prompt, SamplingParams(temperature=0.9, top_k=50, top_p=0.95, seed=4), 12)
     assert got == prompt + want
     assert "generated" in r.stderr and "MB of weights" in r.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_equals_the_python_engines(model_dirs, dtype):
+    """Two requests that decode for hundreds of steps side by side (steps queued ahead, a new
+    graph each time the context bound moves, pages taken one by one), a third that arrives in
+    between and stops at a stop id: the same ids from both engines."""
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    d = model_dirs("C", STORE[dtype])
+    V = TINY["C"]["vocab_size"]
+    kw = dict(dtype=dtype, page_size=16, n_pages=140, max_requests=4, max_step_tokens=64, prefill_chunk=32, seed=2)
+    py, ce = sched_new(d, **kw), CEngine(d, **kw)
+    jobs = [(traces.random_tokens(1, 9, V), 700, SamplingParams(temperature=0.8, ignore_eos=True)),
+            (traces.random_tokens(2, 40, V), 650, SamplingParams(ignore_eos=True))]
+    for p, n, sp in jobs:
+        assert py.submit_ids(p, n, sp) == ce.submit_ids(p, n, sp) > 0
+    for s in (py, ce):
+        for _ in range(300):
+            s.step()
+    late = (traces.random_tokens(3, 21, V), 200, SamplingParams(temperature=1.1, stop_ids=[1, 2, 3, 4, 5, 6, 7, 8]))
+    assert py.submit_ids(*late) == ce.submit_ids(*late) > 0
+    py.run_until_done()
+    ce.run_until_done()
+    got_py, got_c = drain(py), drain(ce)
+    assert got_c == got_py
+    assert len(got_c[1]) == 700 and len(got_c[2]) == 650
+    st = ce.get_stats()
+    assert st.steps_ahead > 500 and st.graph_replays > 600 and st.pool_free == st.pool_pages
+    assert ce.check()
+    ce.close()

@@ -897,6 +897,15 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   int stages = budget / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > per) stages = per;
+  // Many tiles and no split (the head over the vocabulary, a few tokens): with a deep ring two
+  // blocks share an SM and the tiles take two waves, the second on a part of the SMs; each block
+  // is bound by its start-up and the latency of its K blocks, not by bandwidth, so a shallower
+  // ring that lets all tiles be resident at once ends sooner.
+  if (swap && splits == 1 && tp * tq > 2 * 148) {
+    const int per_sm = (tp * tq + 147) / 148;
+    const int fit = (int)((224 * 1024 / per_sm - 4096) / stage_bytes);
+    if (fit >= 2 && fit < stages) stages = fit;
+  }
   if (stages < 1) stages = 1;
   a.stages = stages;
   dim3 grid(tp, tq, splits);

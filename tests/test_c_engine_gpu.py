@@ -171,3 +171,37 @@ def test_long_decoding_equals_the_python_engines(model_dirs, dtype):
     assert st.steps_ahead > 500 and st.graph_replays > 600 and st.pool_free == st.pool_pages
     assert ce.check()
     ce.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_half_and_double_precision_files_load_alike(model_dirs, tmp_path, dtype):
+    """A file with float16 matrices and float64 vectors: the native loader converts as the Python
+    loader does (float16 and float64 to 32-bit exactly / by rounding, then to the runtime's
+    precision), so both engines generate the same ids."""
+    import json
+    import os
+    import torch
+    from sglang_c_b200.engine import generate, sched_new
+    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.sampling import SamplingParams
+    from sglang_c_b200.weights.safetensors_io import SafetensorsFile, write_safetensors
+    src = model_dirs("B")
+    d = str(tmp_path / "mixed_precisions")
+    os.makedirs(d)
+    with open(os.path.join(src, "config.json")) as f, open(os.path.join(d, "config.json"), "w") as g:
+        json.dump(json.load(f), g)
+    f = SafetensorsFile(os.path.join(src, "model.safetensors"))
+    tensors = {n: (f.tensor(n).to(torch.float16) if f.tensor(n).dim() == 2 else f.tensor(n).to(torch.float64))
+               for n in f.names()}
+    f.close()
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    prompts = [traces.random_tokens(9, 30, TINY["B"]["vocab_size"]), traces.random_tokens(10, 7, TINY["B"]["vocab_size"])]
+    sp = SamplingParams(temperature=0.9, seed=1)
+    kw = dict(dtype=dtype, page_size=8, max_tokens=512, max_requests=4, seed=6)
+    want = generate(sched_new(d, **kw), prompts, sp, 20)
+    ce = CEngine(d, **kw)
+    ids = [ce.submit_ids(p, 20, sp) for p in prompts]
+    ce.run_until_done()
+    got = drain(ce)
+    assert [got[i] for i in ids] == want
+    ce.close()

@@ -108,6 +108,11 @@ int sglc_engine_last_step(sglc_engine* e, long long* ids, int* n_tokens, int* sa
  * with the reason as the last error. */
 int sglc_engine_check(sglc_engine* e);
 const char* sglc_engine_last_error(sglc_engine* e);
+/* For tests: the page tables alone (two cache groups, the second with `window`) under n_ops random
+ * operations (requests arrive, grow by portions of any size, are cut back, end), with the
+ * invariants checked after each; 0, or -1 with the reason in err.  Needs no device. */
+int sglc_pages_selftest(int page_size, int n_pages, int max_requests, int window, unsigned seed, int n_ops,
+                        char* err, int err_len);
 /* Sizes the model was built with, from config.json. */
 int sglc_engine_vocab_size(sglc_engine* e);
 int sglc_engine_max_positions(sglc_engine* e);

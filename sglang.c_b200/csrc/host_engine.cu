@@ -47,7 +47,7 @@ constexpr int STREAM_MIN_ITEMS = 160;              // (token, head) items from w
 constexpr int FEW_MAX_TOKENS = 2;
 constexpr long long FEW_MAX_WEIGHT = 3ll << 20;
 constexpr int ORDER_SPREAD = 64;                   // contexts that differ by a stage of keys: their order matters
-constexpr int MAX_GRAPHS = 48;
+constexpr int MAX_GRAPHS = 96;                     // (a step shape has a graph for each of the two turns of its arrays)
 
 std::string fmt(const char* f, ...) {
   char buf[1024];
@@ -537,22 +537,32 @@ class DeviceRunner : public StepRunner {
   DeviceRunner(const DeviceModel* dm, const CacheTables* cache, const Kernels* k, const sglc_engine_options& o)
       : dm_(dm), cache_(cache), k_(k), opt_(o) {}
   ~DeviceRunner() override {
-    if (stream_) cudaStreamSynchronize(stream_);          // a step may still be in flight
+    for (cudaStream_t st : {stream_, up_stream_, down_stream_})
+      if (st) cudaStreamSynchronize(st);                  // a step may still be in flight
     for (int i = 0; i < 2; ++i)
-      if (done_[i]) cudaEventDestroy(done_[i]);
+      for (cudaEvent_t ev : {done_[i], uploaded_[i], ran_[i]})
+        if (ev) cudaEventDestroy(ev);
     for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
     for (void* p : dev_) cudaFree(p);
     for (void* p : pinned_) cudaFreeHost(p);
-    if (copied_) cudaEventDestroy(copied_);
-    if (stream_) cudaStreamDestroy(stream_);
+    for (cudaStream_t st : {stream_, up_stream_, down_stream_})
+      if (st) cudaStreamDestroy(st);
   }
   long long graph_replays = 0, launches = 0;
 
   bool init(std::string* err) {
     const WalkModel& wm = dm_->wm;
+    // The kernels of the steps run back to back on one stream; a step's arrays go up and its ids
+    // come down on two others, so that the copies of the step queued ahead lie beside the step in
+    // flight, not between two steps.  Everything a step uploads exists twice, taken in turn.
     CU(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
-    CU(cudaEventCreateWithFlags(&copied_, cudaEventDisableTiming));
-    for (int i = 0; i < 2; ++i) CU(cudaEventCreateWithFlags(&done_[i], cudaEventDisableTiming));
+    CU(cudaStreamCreateWithFlags(&up_stream_, cudaStreamNonBlocking));
+    CU(cudaStreamCreateWithFlags(&down_stream_, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      CU(cudaEventCreateWithFlags(&done_[i], cudaEventDisableTiming));
+      CU(cudaEventCreateWithFlags(&uploaded_[i], cudaEventDisableTiming));
+      CU(cudaEventCreateWithFlags(&ran_[i], cudaEventDisableTiming));
+    }
     t_cap_ = opt_.max_step_tokens;
     r_cap_ = opt_.max_requests;
     b_cap_ = (wm.n_positions + opt_.page_size - 1) / opt_.page_size;
@@ -571,9 +581,12 @@ class DeviceRunner : public StepRunner {
       f_bt_.push_back(field(r_cap_ * b_cap_));
     }
     total_ = off;
-    if (!pinned((void**)&h_, (size_t)total_ * 4, err) || !device((void**)&d_, (size_t)total_ * 4, err)) return false;
-    memset(h_, 0, (size_t)total_ * 4);
-    CU(cudaMemset(d_, 0, (size_t)total_ * 4));
+    for (int i = 0; i < 2; ++i) {
+      if (!pinned((void**)&h_blk_[i], (size_t)total_ * 4, err) || !device((void**)&d_blk_[i], (size_t)total_ * 4, err))
+        return false;
+      memset(h_blk_[i], 0, (size_t)total_ * 4);
+      CU(cudaMemset(d_blk_[i], 0, (size_t)total_ * 4));
+    }
     // the step workspace: what the parts take per token (the 32-bit residual stream, the widest
     // layer's buffers, the final norm's rows), rounded up for the 256-byte alignment of the pieces
     const long long es = wm.bf16 ? 2 : 4, E = wm.hidden;
@@ -586,19 +599,21 @@ class DeviceRunner : public StepRunner {
     if (!device((void**)&ws_, (size_t)ws_bytes_, err)) return false;
     logit_rows_ = std::max(r_cap_, 64);
     if (!device((void**)&logits_, (size_t)logit_rows_ * wm.vocab * 4, err)) return false;
-    // the two error words and the sampled ids lie together: one copy brings both back
-    if (!device((void**)&tc_ws_, (size_t)TC_WS_FLOATS * 4, err) || !device((void**)&tc_counters_, TC_COUNTERS * 4, err) ||
-        !device((void**)&flags_, (size_t)(4 + r_cap_) * 4, err))
+    // the two error words and the sampled ids of a step lie together (one copy brings both back),
+    // once per turn: a step's ids are still being read (by the copy down, and by the next step's
+    // embedding) when the step after the next samples
+    if (!device((void**)&tc_ws_, (size_t)TC_WS_FLOATS * 4, err) || !device((void**)&tc_counters_, TC_COUNTERS * 4, err))
       return false;
-    d_out_ = flags_ + 4;
     CU(cudaMemset(tc_counters_, 0, TC_COUNTERS * 4));
-    CU(cudaMemset(flags_, 0, (size_t)(4 + r_cap_) * 4));
+    for (int i = 0; i < 2; ++i) {
+      if (!device((void**)&d_res_[i], (size_t)(4 + r_cap_) * 4, err) || !device((void**)&d_logprob_[i], (size_t)r_cap_ * 4, err))
+        return false;
+      CU(cudaMemset(d_res_[i], 0, (size_t)(4 + r_cap_) * 4));
+    }
     // the sampler's records and results; the host's copies twice, taken in turn: a launch may
     // follow before the last one's results are read
-    if (!device((void**)&d_params_, (size_t)r_cap_ * 40, err) || !device((void**)&d_logprob_, (size_t)r_cap_ * 4, err))
-      return false;
     for (int i = 0; i < 2; ++i) {
-      if (!pinned((void**)&h_params_[i], (size_t)r_cap_ * 40, err) || !pinned((void**)&h_flags_[i], (size_t)(4 + r_cap_) * 4, err) ||
+      if (!device((void**)&d_params_[i], (size_t)r_cap_ * 40, err) || !pinned((void**)&h_params_[i], (size_t)r_cap_ * 40, err) || !pinned((void**)&h_flags_[i], (size_t)(4 + r_cap_) * 4, err) ||
           !pinned((void**)&h_logprob_[i], (size_t)r_cap_ * 4, err))
         return false;
       h_out_[i] = h_flags_[i] + 4;
@@ -619,7 +634,10 @@ class DeviceRunner : public StepRunner {
     int T = 0;
     for (const StepItem& it : items) T += it.n;
     if (T > t_cap_ || R > r_cap_) return *err = fmt("a step of %d tokens of %d requests exceeds the engine's sizes", T, R), false;
-    if (copied_once_) CU(cudaEventSynchronize(copied_));            // the last upload has left the pinned block
+    const int turn = turn_;
+    if (used_[turn]) CU(cudaEventSynchronize(uploaded_[turn]));     // this turn's last upload has left the pinned block
+    int* const h_ = h_blk_[turn];
+    int* const d_ = d_blk_[turn];
     int *tok = h_ + f_tokens_.off, *pos = h_ + f_positions_.off, *trq = h_ + f_token_req_.off, *wr = h_ + f_want_.off;
     int *dtk = h_ + f_decode_.off, *qs = h_ + f_q_start_.off, *kl = h_ + f_kv_len_.off, *ss = h_ + f_state_.off;
     int t0 = 0, nw = 0, n_decode = 0, max_keys = 0, max_q = 0, min_len = 1 << 30;
@@ -651,14 +669,18 @@ class DeviceRunner : public StepRunner {
     qs[R] = t0;
     if (n_decode > 1)          // single tokens in the order of their contexts, longest first
       std::stable_sort(dtk, dtk + n_decode, [&](int a, int b) { return pos[a] > pos[b]; });
-    CU(cudaMemcpyAsync(d_, h_, (size_t)total_ * 4, cudaMemcpyHostToDevice, stream_));
-    CU(cudaEventRecord(copied_, stream_));
-    copied_once_ = true;
+    // up: after the step that last read this turn's device block (two launches ago) has run
+    if (used_[turn]) CU(cudaStreamWaitEvent(up_stream_, ran_[turn], 0));
+    CU(cudaMemcpyAsync(d_, h_, (size_t)total_ * 4, cudaMemcpyHostToDevice, up_stream_));
+    if (nw > 0 && !sample_records(items, uniforms, nw, turn, err)) return false;
+    CU(cudaEventRecord(uploaded_[turn], up_stream_));
+    CU(cudaStreamWaitEvent(stream_, uploaded_[turn], 0));
+    used_[turn] = true;
 
     WalkStep s = {};
-    // (ids_on_device: what the launch before this one sampled, row for row, read where the
-    // sampler left it; this step's own sampler overwrites it after the embedding has read it)
-    s.tokens = ids_on_device ? d_out_ : d_ + f_tokens_.off; s.positions = d_ + f_positions_.off; s.token_req = d_ + f_token_req_.off;
+    // (ids_on_device: what the launch before this one sampled, row for row, read where its
+    // sampler left it: the other turn's result words)
+    s.tokens = ids_on_device ? d_res_[turn ^ 1] + 4 : d_ + f_tokens_.off; s.positions = d_ + f_positions_.off; s.token_req = d_ + f_token_req_.off;
     s.want_rows = d_ + f_want_.off; s.q_start = d_ + f_q_start_.off; s.kv_len = d_ + f_kv_len_.off;
     s.decode_tokens = d_ + f_decode_.off;
     for (int g = 0; g < n_groups_; ++g) {
@@ -670,7 +692,7 @@ class DeviceRunner : public StepRunner {
     s.bt_stride = b_cap_;
     s.workspace = ws_; s.workspace_bytes = ws_bytes_;
     s.logits = logits_;
-    s.err_flag = flags_; s.tc_err = flags_ + 1;
+    s.err_flag = d_res_[turn]; s.tc_err = d_res_[turn] + 1;
     s.tc_ws = tc_ws_; s.tc_ws_floats = TC_WS_FLOATS; s.tc_counters = tc_counters_; s.tc_n_counters = TC_COUNTERS;
     s.T = T; s.R = R; s.n_want = nw; s.max_q_len = max_q; s.max_keys = max_keys; s.n_decode = n_decode;
     s.decode_ordered = (n_decode == T && R > 1 && max_keys - min_len >= ORDER_SPREAD) ? 1 : 0;
@@ -678,17 +700,16 @@ class DeviceRunner : public StepRunner {
     s.stream_min_items = STREAM_MIN_ITEMS; s.use_tma_decode = 1;
     s.few_max_tokens = FEW_MAX_TOKENS; s.few_max_weight = FEW_MAX_WEIGHT;
     s.stream = stream_;
-    if (!forward(&s, ids_on_device, err)) return false;
-
-    // one token for every wanted row, on the device; ids (and the error words) come back in one wait
-    const int turn = turn_;
-    if (nw > 0) {
-      if (!sample(items, uniforms, nw, want_logprobs, turn, err)) return false;
-      if (want_logprobs)
-        CU(cudaMemcpyAsync(h_logprob_[turn], d_logprob_, (size_t)nw * 4, cudaMemcpyDeviceToHost, stream_));
-    }
-    CU(cudaMemcpyAsync(h_flags_[turn], flags_, (size_t)(4 + nw) * 4, cudaMemcpyDeviceToHost, stream_));
-    CU(cudaEventRecord(done_[turn], stream_));
+    // the step's kernels and, behind them in the same launch or graph, the sampler: one token for
+    // every wanted row
+    if (!forward(&s, ids_on_device, turn, want_logprobs, err)) return false;
+    CU(cudaEventRecord(ran_[turn], stream_));
+    // down: ids and the error words in one copy, beside the next step
+    CU(cudaStreamWaitEvent(down_stream_, ran_[turn], 0));
+    if (nw > 0 && want_logprobs)
+      CU(cudaMemcpyAsync(h_logprob_[turn], d_logprob_[turn], (size_t)nw * 4, cudaMemcpyDeviceToHost, down_stream_));
+    CU(cudaMemcpyAsync(h_flags_[turn], d_res_[turn], (size_t)(4 + nw) * 4, cudaMemcpyDeviceToHost, down_stream_));
+    CU(cudaEventRecord(done_[turn], down_stream_));
     n_of_[turn] = nw;
     logprobs_of_[turn] = want_logprobs;
     *ticket = turn;
@@ -701,7 +722,7 @@ class DeviceRunner : public StepRunner {
     const int* flags = h_flags_[ticket];
     if (flags[0] || flags[1]) {
       const int a = flags[0], b = flags[1];
-      cudaMemsetAsync(flags_, 0, 8, stream_);
+      cudaMemsetAsync(d_res_[ticket], 0, 8, stream_);
       if (a) return *err = "a kernel met an out-of-range token or position id", false;
       if (b & SGLC_FLAG_INDEX) return *err = "a kernel of the bounds-check build met an index outside its range", false;
       return *err = "a tensor-core kernel gave up on a bounded wait; its output is invalid", false;
@@ -742,11 +763,17 @@ class DeviceRunner : public StepRunner {
     return std::min(bound, dm_->wm.n_positions);
   }
 
-  bool walk(WalkStep* s, std::string* err) {
-    const int code = k_->forward(&dm_->wm, s);
+  bool walk(WalkStep* s, int turn, bool want_logprobs, std::string* err) {
+    int code = k_->forward(&dm_->wm, s);
     if (code != 0) {
       *err = std::string(s->where[0] ? s->where : "step walker") + ": " + k_->walker_error(code) + fmt(" (code %d)", code);
       return false;
+    }
+    if (s->n_want > 0) {
+      code = k_->sample(logits_, dm_->wm.vocab, dm_->wm.vocab, s->n_want, d_params_[turn], d_hist_tok_, d_hist_cnt_,
+                        d_res_[turn] + 4, want_logprobs ? d_logprob_[turn] : nullptr, stream_);
+      s->launches++;
+      if (code != 0) return *err = fmt("sample: launch failed (code %d)", code), false;
     }
     return true;
   }
@@ -755,16 +782,17 @@ class DeviceRunner : public StepRunner {
   // step varies in lies in device arrays at fixed addresses.  A shape runs as plain launches the
   // first time it is seen and is captured the second time; a step of single tokens, which will
   // come again, is captured the first time.
-  bool forward(WalkStep* s, bool ids_on_device, std::string* err) {
+  bool forward(WalkStep* s, bool ids_on_device, int turn, bool want_logprobs, std::string* err) {
     if (!opt_.use_graphs) {
-      if (!walk(s, err)) return false;
+      if (!walk(s, turn, want_logprobs, err)) return false;
       launches += s->launches;
       return true;
     }
     const int bound = graph_bound(*s);
     s->max_keys = bound;
     const GraphKey key{s->T, s->R, s->n_want, s->max_q_len > 1 ? (s->max_q_len + 127) / 128 : 0, bound, s->n_decode,
-                       s->decode_ordered + 2 * (ids_on_device ? 1 : 0)};      // (the token array's address is captured)
+                       // (captured with the graph: the token array's address, this turn's arrays, the sampler's form)
+                       s->decode_ordered + 2 * (ids_on_device ? 1 : 0) + 4 * turn + 8 * (want_logprobs ? 1 : 0)};
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
       const bool steady = s->n_decode == s->T && plain_steps_ > 0;
@@ -772,13 +800,13 @@ class DeviceRunner : public StepRunner {
         if (seen_.size() > 4096) seen_.clear();
         seen_[key] = true;
         ++plain_steps_;
-        if (!walk(s, err)) return false;
+        if (!walk(s, turn, want_logprobs, err)) return false;
         launches += s->launches;
         return true;
       }
       cudaGraph_t graph = nullptr;
       CU(cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal));
-      const bool ok = walk(s, err);
+      const bool ok = walk(s, turn, want_logprobs, err);
       cudaError_t e = cudaStreamEndCapture(stream_, &graph);
       if (!ok || e != cudaSuccess) {
         if (graph) cudaGraphDestroy(graph);
@@ -806,8 +834,9 @@ class DeviceRunner : public StepRunner {
     return true;
   }
 
-  bool sample(const std::vector<StepItem>& items, const std::vector<double>& uniforms, int nw, bool want_logprobs,
-              int turn, std::string* err) {
+  // the sampler's records of a step (and the histories of rows with penalties), on their way up
+  bool sample_records(const std::vector<StepItem>& items, const std::vector<double>& uniforms, int nw, int turn,
+                      std::string* err) {
     int* const h_params = h_params_[turn];
     // records of 10 words: temperature, top_p, min_p, u, top_k, the three penalties, and the
     // row's range of (token, count) pairs (csrc/sampling.cu)
@@ -816,7 +845,7 @@ class DeviceRunner : public StepRunner {
     bool plain_greedy = true;                    // every row: argmax and nothing else
     for (const StepItem& it : items)
       if (it.sampled && !(it.r->sp.greedy() && !it.r->sp.has_penalties())) plain_greedy = false;
-    const bool records_there = plain_greedy && greedy_rows_ >= nw;   // the device already holds nw such records
+    const bool records_there = plain_greedy && greedy_rows_[turn] >= nw;   // the device already holds nw such records
     for (const StepItem& it : items) {
       if (!it.sampled) continue;
       const Sampling& sp = it.r->sp;
@@ -841,6 +870,8 @@ class DeviceRunner : public StepRunner {
     const int n_pairs = (int)hist.size() / 2;
     if (n_pairs > hist_cap_) {
       CU(cudaStreamSynchronize(stream_));
+      for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);     // (they hold the old buffers' addresses)
+      graphs_.clear();
       hist_cap_ = 2 * n_pairs;
       if (!device((void**)&d_hist_tok_, (size_t)hist_cap_ * 4, err) || !device((void**)&d_hist_cnt_, (size_t)hist_cap_ * 4, err) ||
           !pinned((void**)&h_hist_, (size_t)hist_cap_ * 8, err))
@@ -851,15 +882,13 @@ class DeviceRunner : public StepRunner {
         h_hist_[i] = hist[2 * i];
         h_hist_[hist_cap_ + i] = hist[2 * i + 1];
       }
-      CU(cudaMemcpyAsync(d_hist_tok_, h_hist_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, stream_));
-      CU(cudaMemcpyAsync(d_hist_cnt_, h_hist_ + hist_cap_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, stream_));
+      // (rows with penalties are never queued ahead: the step that last read these has been collected)
+      CU(cudaMemcpyAsync(d_hist_tok_, h_hist_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, up_stream_));
+      CU(cudaMemcpyAsync(d_hist_cnt_, h_hist_ + hist_cap_, (size_t)n_pairs * 4, cudaMemcpyHostToDevice, up_stream_));
     }
-    if (!records_there) CU(cudaMemcpyAsync(d_params_, h_params, (size_t)nw * 40, cudaMemcpyHostToDevice, stream_));
-    greedy_rows_ = plain_greedy ? std::max(greedy_rows_, nw) : 0;
-    const int code = k_->sample(logits_, dm_->wm.vocab, dm_->wm.vocab, nw, d_params_, d_hist_tok_, d_hist_cnt_, d_out_,
-                                want_logprobs ? d_logprob_ : nullptr, stream_);
-    ++launches;
-    if (code != 0) return *err = fmt("sample: launch failed (code %d)", code), false;
+    if (!records_there)
+      CU(cudaMemcpyAsync(d_params_[turn], h_params, (size_t)nw * 40, cudaMemcpyHostToDevice, up_stream_));
+    greedy_rows_[turn] = plain_greedy ? std::max(greedy_rows_[turn], nw) : 0;
     return true;
   }
 
@@ -872,20 +901,20 @@ class DeviceRunner : public StepRunner {
   const CacheTables* cache_;
   const Kernels* k_;
   sglc_engine_options opt_;
-  cudaStream_t stream_ = nullptr;
-  cudaEvent_t copied_ = nullptr;
-  bool copied_once_ = false, few_ok_ = false;
+  cudaStream_t stream_ = nullptr, up_stream_ = nullptr, down_stream_ = nullptr;
+  cudaEvent_t uploaded_[2] = {nullptr, nullptr}, ran_[2] = {nullptr, nullptr};
+  bool used_[2] = {false, false}, few_ok_ = false;
   int t_cap_ = 0, r_cap_ = 0, b_cap_ = 0, n_groups_ = 0, total_ = 0, logit_rows_ = 0, hist_cap_ = 0;
   Field f_tokens_, f_positions_, f_token_req_, f_want_, f_decode_, f_q_start_, f_kv_len_, f_state_;
   std::vector<Field> f_slots_, f_bt_;
-  int *h_ = nullptr, *d_ = nullptr;
+  int *h_blk_[2] = {nullptr, nullptr}, *d_blk_[2] = {nullptr, nullptr};
   unsigned char* ws_ = nullptr;
   long long ws_bytes_ = 0;
-  float *logits_ = nullptr, *tc_ws_ = nullptr, *d_logprob_ = nullptr, *h_logprob_[2] = {nullptr, nullptr};
-  int *tc_counters_ = nullptr, *flags_ = nullptr, *h_flags_[2] = {nullptr, nullptr};
-  int *h_params_[2] = {nullptr, nullptr}, *d_params_ = nullptr, *d_out_ = nullptr, *h_out_[2] = {nullptr, nullptr};
+  float *logits_ = nullptr, *tc_ws_ = nullptr, *d_logprob_[2] = {nullptr, nullptr}, *h_logprob_[2] = {nullptr, nullptr};
+  int *tc_counters_ = nullptr, *d_res_[2] = {nullptr, nullptr}, *h_flags_[2] = {nullptr, nullptr};
+  int *h_params_[2] = {nullptr, nullptr}, *d_params_[2] = {nullptr, nullptr}, *h_out_[2] = {nullptr, nullptr};
   cudaEvent_t done_[2] = {nullptr, nullptr};
-  int turn_ = 0, n_of_[2] = {0, 0}, greedy_rows_ = 0;
+  int turn_ = 0, n_of_[2] = {0, 0}, greedy_rows_[2] = {0, 0};
   bool logprobs_of_[2] = {false, false};
   int *d_hist_tok_ = nullptr, *d_hist_cnt_ = nullptr, *h_hist_ = nullptr;
   std::vector<const int*> bts_, slots_;

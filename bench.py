@@ -7,14 +7,16 @@ n_head 12, n_inner 3072, vocab 50257, positions 1024) with random weights in
 bfloat16, a batch of 8 requests decoding at a context of 512 tokens, pages of
 16.  A "step" is one decode step of the whole batch.  One JSON line is printed:
 `value` is decoded tokens a second with the steps timed on the device (CUDA events
-around chunks of K steps, each step's sampled ids feeding the next; the median of
-five regions of at least 50 ms each; a step reads more than L2 holds, so nothing
-is flushed); `e2e` is the same through the Python entry point (scheduler, host
-token ids in and out); `prefill` is one step of 2,048 prompt tokens (2 x 1,024);
+on the stream the steps run on, around chunks of K steps of the native engine's
+scheduler, each step's sampled ids feeding the next; the median of five regions of
+at least 50 ms each; a step reads more than L2 holds, so nothing is flushed;
+`points.decode_b8_python_engine` is the same for the Python engine's loop); `e2e` is the same through the Python entry point (`sched_new(...,
+native=True)`: scheduler and step in C++, host token ids in and out every step;
+`points.e2e_python_scheduler_b8` is the Python scheduler); `prefill` is one step of 2,048 prompt tokens (2 x 1,024);
 `roofline` is the decode step's bytes (every weight once, the cache of the live
 requests) over its time, against the measured copy bandwidth; `points` has decode
-at batch 1 and 64, the true 32-bit path and the batch-8 decode through the C interface
-(`e2e_c_api_b8`); `kernels` says where a decode and a
+at batch 1 and 64, the true 32-bit path and the prefill through the C interface;
+`kernels` says where a decode and a
 prefill step's time goes, kernel by kernel.  `--full` adds medium and XL layer
 sizes and the mixed workload to `points`.
 """
@@ -202,6 +204,60 @@ def time_decode(eng, batch, context, steps, warmup):
     return statistics.median(regions), launches, regions
 
 
+def time_decode_native(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
+    """time_decode on the native engine (`sched_new(..., native=True)`): the requests are brought to
+    `context` tokens through the scheduler, then chunks of `steps` decode steps are timed on the
+    device between two marks on the stream the steps run on (sglc_engine_mark: CUDA events; the
+    stream is synchronised before the first, the second is waited for).  The steps are the
+    scheduler's own: each queued behind the one in flight, its ids taken from the sampler on the
+    device, arrays up and ids down on side streams, the sampler inside the step's graph.  After a
+    chunk the requests are rewound to their first generated token (host bookkeeping, untimed) and
+    one untimed step re-primes the queue.  Median region's ms per step, launches of a chunk,
+    the regions."""
+    import numpy as np
+    from sglang_c_b200.engine import sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    e = sched_new(model_dir, seed=0, dtype=dtype, page_size=PAGE, max_tokens=batch * (context + steps + warmup + 96),
+                  max_requests=max(batch, 1), max_step_tokens=PREFILL_TOKENS, prefill_chunk=512, native=True)
+    rng = np.random.default_rng(batch)
+    sp = SamplingParams(temperature=0.0, ignore_eos=True)
+    ids = [e.submit_ids([int(t) for t in rng.integers(0, e.vocab_size, size=context)], warmup + steps + 64, sp)
+           for _ in range(batch)]
+    while True:                                    # prompts done; every request decodes from here
+        e.step()
+        ran = e.last_step()
+        if len(ran) == batch and all(n == 1 for _, n, _ in ran):
+            break
+
+    def chunk(n):
+        e.sync()
+        for i in ids:
+            e.rewind(i, 1)
+        e.step()
+        e.step()                                   # (two: the second is queued ahead of the first's ids)
+        l0 = e.get_stats().launches
+        e.mark(sync_first=True)
+        for _ in range(n):
+            e.step()
+        e.mark()
+        return e.ms_between_marks(), e.get_stats().launches - l0
+
+    for _ in range(max(1, (warmup + steps - 1) // steps)):
+        chunk(steps)
+    regions, launches = [], 0
+    for _ in range(N_REGIONS):
+        ms, n = 0.0, 0
+        while ms < REGION_MS:
+            t, launches = chunk(steps)
+            ms += t
+            n += steps
+        regions.append(ms / n)
+    for i in ids:
+        e.abort(i)
+    e.close()
+    return statistics.median(regions), launches, regions
+
+
 def time_prefill(eng, n_prompts, prompt_len, warmup, behind_sleep=False):
     """One step of n_prompts whole prompts; the median of N_REGIONS regions of at least REGION_MS
     of device time each (a region is steps in a row, each on fresh requests).  The events stand
@@ -349,14 +405,16 @@ def time_e2e(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
 
 
 def time_e2e_c(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
-    """The same decode through the engine's C interface (csrc/sglc_engine.h, all native): token
-    ids on the host in, token ids on the host out, every step; wall clock; regions as time_e2e."""
+    """The same decode through the Python entry point on the native engine
+    (`sched_new(..., native=True)`: the engine behind the C interface csrc/sglc_engine.h): token
+    ids on the host in, token ids on the host out, every step; wall clock; regions as time_e2e.
+    Returns (tokens a second, bytes up a step, bytes down a step)."""
     import numpy as np
-    from sglang_c_b200.engine.c_api import CEngine
+    from sglang_c_b200.engine import sched_new
     from sglang_c_b200.sampling import SamplingParams
     n_timed = max(steps, 100)
-    e = CEngine(model_dir, seed=0, dtype=dtype, page_size=PAGE, max_tokens=batch * (context + n_timed + warmup + 64),
-                max_requests=max(batch, 1), max_step_tokens=PREFILL_TOKENS, prefill_chunk=512)
+    e = sched_new(model_dir, seed=0, dtype=dtype, page_size=PAGE, max_tokens=batch * (context + n_timed + warmup + 64),
+                  max_requests=max(batch, 1), max_step_tokens=PREFILL_TOKENS, prefill_chunk=512, native=True)
     V = e.vocab_size
     rng = np.random.default_rng(5)
     sp = SamplingParams(temperature=0.0, ignore_eos=True)
@@ -381,8 +439,9 @@ def time_e2e_c(model_dir, batch, context, steps, warmup, dtype="bfloat16"):
             e.abort(i)
         while e.poll() is not None:
             pass
+    up = e.get_stats().step_upload_bytes          # the packed step arrays (greedy records stay on the device)
     e.close()
-    return statistics.median(regions)
+    return statistics.median(regions), up, (4 + batch) * 4       # down: two error words (padded to four) and the ids
 
 
 def time_prefill_c(model_dir, n_prompts, prompt_len, warmup=3):
@@ -554,7 +613,8 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
                           max_tokens=64 * (CONTEXT + 256), max_requests=64, max_step_tokens=PREFILL_TOKENS)
     time_decode(eng, BATCH, 32, 2, 3)               # every path once (compiles on a fresh checkout)
     r = {}
-    ms, launches, regions = time_decode(eng, BATCH, CONTEXT, steps, warmup)
+    pms_loop, _, _ = time_decode(eng, BATCH, CONTEXT, steps, warmup)      # the Python engine's loop
+    ms, launches, regions = time_decode_native(model_dir, BATCH, CONTEXT, steps, warmup)
     r.update(ms=ms, launches=launches, regions=regions, value=BATCH / (ms / 1e3))
     r["bytes"] = model_bytes_flops(cfg_d, BATCH, CONTEXT + steps // 2)
     pms = time_prefill(eng, 2, PREFILL_TOKENS // 2, 3)
@@ -563,9 +623,9 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     r["prefill"] = {"value": PREFILL_TOKENS / (pms / 1e3), "tokens": PREFILL_TOKENS, "ms": pms,
                     "frac": pflops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), "of": pk["source"],
                     "device_ms": dms, "device_frac": pflops / (dms / 1e3) / (pk["bf16_tflops"] * 1e12)}
-    r["points"] = {}
+    r["points"] = {"decode_b8_python_engine": BATCH / (pms_loop / 1e3)}
     for b in points:
-        t, _, _ = time_decode(eng, b, CONTEXT, steps, warmup)
+        t, _, _ = time_decode_native(model_dir, b, CONTEXT, steps, warmup)
         r["points"][f"decode_b{b}"] = b / (t / 1e3)
         nb = model_bytes_flops(cfg_d, b, CONTEXT + steps // 2)
         r["points"][f"decode_b{b}_roofline_frac"] = nb / (t / 1e3) / 1e9 / pk["hbm_gbs"]
@@ -573,8 +633,10 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
         r["kernels"] = kernel_table(eng, BATCH, CONTEXT, PREFILL_TOKENS // 2)
     del eng
     torch.cuda.empty_cache()
-    r["e2e"] = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)
-    r["points"]["e2e_c_api_b8"] = time_e2e_c(model_dir, BATCH, CONTEXT, steps, warmup)
+    # end to end through the Python entry point: on the native engine (the headline), and on the
+    # Python scheduler (the general one)
+    r["e2e"] = time_e2e_c(model_dir, BATCH, CONTEXT, steps, warmup)
+    r["points"]["e2e_python_scheduler_b8"] = time_e2e(model_dir, BATCH, CONTEXT, steps, warmup)[0]
     # (a request must leave a position for the token it generates: prompts of 1,023 tokens)
     r["points"]["prefill_c_api_tok_s"] = \
         (PREFILL_TOKENS - 2) / (time_prefill_c(model_dir, 2, PREFILL_TOKENS // 2 - 1) / 1e3)

@@ -41,6 +41,8 @@ def build_parser():
     ap.add_argument("--pages", type=int, default=None, help="pages in the cache pool")
     ap.add_argument("--chunk", type=int, default=512, help="largest prompt portion per step")
     ap.add_argument("--token-budget", type=int, default=2048, help="most tokens per step")
+    ap.add_argument("--native", action="store_true",
+                    help="the engine behind the C interface (loader, scheduler and step in C++); same ids")
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="write a random model folder from --config and use it")
     ap.add_argument("--config", help="config.json for --random-weights")
@@ -90,9 +92,11 @@ def main(argv=None):
     s = sched_new(model_dir, seed=args.seed, dtype=args.dtype, device=device, page_size=args.page_size,
                   n_pages=args.pages, max_tokens=None if args.pages else max(need, 64) + args.page_size,
                   max_requests=4, max_step_tokens=args.token_budget, prefill_chunk=args.chunk,
-                  token_budget=args.token_budget)
-    log.debug(f"model loaded in {time.time() - t0:.2f}s ({s.engine.model.weight_bytes / 1e6:.1f} MB of weights, "
-              f"{s.engine.cache.n_pages} pages of {s.engine.page_size})")
+                  token_budget=args.token_budget, native=args.native)
+    st = s.get_stats()
+    mb = (st.weight_bytes if args.native else s.engine.model.weight_bytes) / 1e6
+    log.debug(f"model loaded in {time.time() - t0:.2f}s ({mb:.1f} MB of weights, {st.pool_pages} pages of "
+              f"{args.page_size})")
     sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                         min_p=args.min_p, repetition_penalty=args.repetition_penalty,
                         ignore_eos=args.ignore_eos, seed=args.seed)
@@ -103,7 +107,9 @@ def main(argv=None):
     n = len(out)
     log.info(f"generated {n} tokens in {dt:.2f}s ({n / dt if dt > 0 else 0:.1f} tok/s, "
              f"{dt * 1000 / max(n, 1):.0f} ms/tok)")
-    log.debug(f"stats: {s.get_stats()}")
+    st = s.get_stats()
+    log.debug("stats: " + ", ".join(f"{k}={getattr(st, k)}" for k in ("n_steps", "prefill_tokens", "decode_tokens",
+                                                                       "n_finished", "n_preempt", "pool_free")))
     return 0
 
 

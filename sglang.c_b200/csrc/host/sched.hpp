@@ -285,6 +285,26 @@ class Scheduler {
   }
   // a step may still be in flight when the caller asks whether anything is active
   bool in_flight() const { return flight_.active; }
+  // wait for the step in flight, if any, and append its ids; requests ended by it, or -1
+  int drain(std::string* err) {
+    if (!flight_.active) return 0;
+    return collect(&flight_, nullptr, err);
+  }
+  // Forget what a running request has generated beyond its first `keep` ids (and what the cache
+  // holds of it); it goes on from there.  For measurements that time the same steps again and
+  // again.  false: no such running request, a step in flight, or nothing to keep it running.
+  bool rewind(long long id, int keep) {
+    auto it = requests_.find(id);
+    if (it == requests_.end() || flight_.active) return false;
+    Request* r = it->second.get();
+    if (r->state != REQ_RUNNING || keep < 1 || keep > (int)r->gen.size()) return false;
+    const int n = (int)r->prompt.size() + keep - 1;           // the last kept id is not computed yet
+    if (n > r->n_computed || !cache_->truncate(r->id, n)) return false;
+    r->gen.resize((size_t)keep);
+    if (r->logprobs.size() > (size_t)keep) r->logprobs.resize((size_t)keep);
+    r->n_computed = n;
+    return true;
+  }
 
  private:
   struct FlightItem {

@@ -540,7 +540,7 @@ class DeviceRunner : public StepRunner {
     for (cudaStream_t st : {stream_, up_stream_, down_stream_})
       if (st) cudaStreamSynchronize(st);                  // a step may still be in flight
     for (int i = 0; i < 2; ++i)
-      for (cudaEvent_t ev : {done_[i], uploaded_[i], ran_[i]})
+      for (cudaEvent_t ev : {done_[i], uploaded_[i], ran_[i], marks_[i]})
         if (ev) cudaEventDestroy(ev);
     for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
     for (void* p : dev_) cudaFree(p);
@@ -549,6 +549,25 @@ class DeviceRunner : public StepRunner {
       if (st) cudaStreamDestroy(st);
   }
   long long graph_replays = 0, launches = 0;
+  long long upload_bytes() const { return (long long)total_ * 4; }
+  // a mark on the stream the steps run on (behind everything queued so far); the device time
+  // between the last two marks
+  bool mark(bool sync_first, std::string* err) {
+    if (!marks_[0]) {
+      CU(cudaEventCreate(&marks_[0]));
+      CU(cudaEventCreate(&marks_[1]));
+    }
+    if (sync_first) CU(cudaStreamSynchronize(stream_));
+    std::swap(marks_[0], marks_[1]);
+    CU(cudaEventRecord(marks_[1], stream_));
+    ++n_marks_;
+    return true;
+  }
+  double ms_between_marks() {
+    if (n_marks_ < 2 || cudaEventSynchronize(marks_[1]) != cudaSuccess) return -1.0;
+    float ms = -1.0f;
+    return cudaEventElapsedTime(&ms, marks_[0], marks_[1]) == cudaSuccess ? (double)ms : -1.0;
+  }
 
   bool init(std::string* err) {
     const WalkModel& wm = dm_->wm;
@@ -902,7 +921,8 @@ class DeviceRunner : public StepRunner {
   const Kernels* k_;
   sglc_engine_options opt_;
   cudaStream_t stream_ = nullptr, up_stream_ = nullptr, down_stream_ = nullptr;
-  cudaEvent_t uploaded_[2] = {nullptr, nullptr}, ran_[2] = {nullptr, nullptr};
+  cudaEvent_t uploaded_[2] = {nullptr, nullptr}, ran_[2] = {nullptr, nullptr}, marks_[2] = {nullptr, nullptr};
+  long long n_marks_ = 0;
   bool used_[2] = {false, false}, few_ok_ = false;
   int t_cap_ = 0, r_cap_ = 0, b_cap_ = 0, n_groups_ = 0, total_ = 0, logit_rows_ = 0, hist_cap_ = 0;
   Field f_tokens_, f_positions_, f_token_req_, f_want_, f_decode_, f_q_start_, f_kv_len_, f_state_;
@@ -1066,7 +1086,38 @@ SGLC_API int sglc_engine_poll_logprobs(sglc_engine* e, long long id, float* out,
   return n;
 }
 
+SGLC_API int sglc_engine_generated(sglc_engine* e, long long id, int* tokens, int cap) {
+  const Request* r = e->sched->find(id);
+  if (!r) return -1;
+  const int n = (int)r->gen.size();
+  if (tokens && cap > 0) memcpy(tokens, r->gen.data(), (size_t)std::min(cap, n) * sizeof(int));
+  return n;
+}
+
 SGLC_API int sglc_engine_abort(sglc_engine* e, long long id) { return e->sched->abort(id); }
+
+SGLC_API int sglc_engine_sync(sglc_engine* e) {
+  if (!e->opt.dry_run) cudaSetDevice(e->opt.device);
+  std::string err;
+  const int n = e->sched->drain(&err);
+  if (n < 0) e->last_error = err;
+  return n;
+}
+
+SGLC_API int sglc_engine_rewind(sglc_engine* e, long long id, int keep) { return e->sched->rewind(id, keep) ? 0 : -1; }
+
+SGLC_API int sglc_engine_mark(sglc_engine* e, int sync_first) {
+  if (!e->device_runner) return -1;
+  cudaSetDevice(e->opt.device);
+  std::string err;
+  if (e->device_runner->mark(sync_first != 0, &err)) return 0;
+  e->last_error = err;
+  return -1;
+}
+
+SGLC_API double sglc_engine_ms_between_marks(sglc_engine* e) {
+  return e->device_runner ? e->device_runner->ms_between_marks() : -1.0;
+}
 
 SGLC_API void sglc_engine_get_stats(sglc_engine* e, sglc_stats* out) {
   const SchedStats s = e->sched->stats();
@@ -1079,6 +1130,7 @@ SGLC_API void sglc_engine_get_stats(sglc_engine* e, sglc_stats* out) {
   if (e->device_runner) {
     out->graph_replays = e->device_runner->graph_replays;
     out->launches = e->device_runner->launches;
+    out->step_upload_bytes = e->device_runner->upload_bytes();
   }
   out->weight_bytes = e->model.weight_bytes;
   out->cache_bytes = e->model.cache_bytes;

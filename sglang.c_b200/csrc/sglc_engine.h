@@ -64,6 +64,7 @@ typedef struct sglc_stats {       /* the reference's counters (include/sgl/sched
   long long prefill_tokens, decode_tokens, n_finished, n_running, n_waiting;
   long long pool_pages, pool_free, n_preempt, prefill_chunk, n_steps, recomputed_tokens;
   long long graph_replays, launches, weight_bytes, cache_bytes, steps_ahead;
+  long long step_upload_bytes;    /* what a step copies to the device: its packed arrays (sampler records beside them) */
 } sglc_stats;
 
 enum { SGLC_FINISH_NONE = 0, SGLC_FINISH_EOS = 1, SGLC_FINISH_STOP = 2, SGLC_FINISH_LENGTH = 3,
@@ -94,11 +95,26 @@ int sglc_engine_nactive(sglc_engine* e);
  * given, nothing is taken).  Any out pointer may be null. */
 int sglc_engine_poll(sglc_engine* e, long long* id, int* tokens, int cap, int* n_tokens, int* n_prompt,
                      int* finish_reason);
+/* What a request has generated so far (running, or finished and not yet taken): up to cap ids into
+ * tokens, returns their full count; -1 if there is no such request.  With run_ahead the ids of the
+ * step in flight are not in it yet. */
+int sglc_engine_generated(sglc_engine* e, long long id, int* tokens, int cap);
 /* Log-probabilities of a finished request's tokens (want_logprobs), before it is taken. */
 int sglc_engine_poll_logprobs(sglc_engine* e, long long id, float* out, int cap);
 /* End a waiting or running request now; 0, or -1 if there is no such request. */
 int sglc_engine_abort(sglc_engine* e, long long id);
 void sglc_engine_get_stats(sglc_engine* e, sglc_stats* out);
+/* With run_ahead a step may be in flight when sglc_engine_step returns: wait for it and take its
+ * ids in.  The requests it ended, or -1. */
+int sglc_engine_sync(sglc_engine* e);
+/* For measurements: a mark on the stream the steps run on, behind everything queued so far
+ * (sync_first: after waiting for it all); the device time in milliseconds between the last two
+ * marks (waits for the second), or a negative number.  And: a running request forgets what it has
+ * generated beyond its first `keep` ids (keep >= 1; no step in flight), so that the same steps can
+ * be timed again; 0, or -1. */
+int sglc_engine_mark(sglc_engine* e, int sync_first);
+double sglc_engine_ms_between_marks(sglc_engine* e);
+int sglc_engine_rewind(sglc_engine* e, long long id, int keep);
 /* Steps until nothing is active (at most max_steps); the steps taken, or -1. */
 long long sglc_engine_run_until_done(sglc_engine* e, long long max_steps);
 /* What the last step ran, in batch order: request ids, their token counts, and whether a token was

@@ -12,10 +12,21 @@ from .scheduler import Scheduler
 
 def sched_new(model_dir, seed=0, dtype="bfloat16", device="cuda:0", page_size=16, n_pages=None,
               max_tokens=None, max_requests=64, max_step_tokens=2048, prefill_chunk=512,
-              token_budget=None, want_logprobs=False):
+              token_budget=None, want_logprobs=False, native=False):
     """Load a model folder and return a scheduler on top of a fresh engine.
     The cache holds `n_pages` pages of `page_size` positions (or room for
-    `max_tokens` positions; by default 64 full-length requests)."""
+    `max_tokens` positions; by default 64 full-length requests).
+
+    native=True: the engine behind the C interface (csrc/sglc_engine.h) with the same entry
+    points (`submit_ids / step / poll / nactive / abort / get_stats / generated /
+    run_until_done`): loader, page tables, scheduler, step arrays, graphs and sampler in C++, for
+    architectures made of the built-in parts; the same ids, a few percent faster end to end.
+    The default is the Python engine, the general one (parts registered from outside)."""
+    if native:
+        from .c_api import CEngine
+        return CEngine(model_dir, seed=seed, dtype=dtype, device=device, page_size=page_size, n_pages=n_pages,
+                       max_tokens=max_tokens, max_requests=max_requests, max_step_tokens=max_step_tokens,
+                       prefill_chunk=prefill_chunk, token_budget=token_budget, want_logprobs=want_logprobs)
     if n_pages is None and max_tokens is None:
         from ..config.registry import load_config
         arch, cfg = load_config(model_dir)
@@ -71,7 +82,7 @@ def generate(s, prompts, sp=None, max_new=16, on_token=None):
         s.step()
         if on_token is not None:
             for i, rid in enumerate(ids):
-                g = s.requests[rid].gen
+                g = s.generated(rid) or []
                 while seen[rid] < len(g):
                     on_token(i, g[seen[rid]])
                     seen[rid] += 1

@@ -28,7 +28,7 @@ class CStats(C.Structure):
     _fields_ = [(n, C.c_longlong) for n in
                 ("prefill_tokens", "decode_tokens", "n_finished", "n_running", "n_waiting", "pool_pages",
                  "pool_free", "n_preempt", "prefill_chunk", "n_steps", "recomputed_tokens", "graph_replays",
-                 "launches", "weight_bytes", "cache_bytes", "steps_ahead")]
+                 "launches", "weight_bytes", "cache_bytes", "steps_ahead", "step_upload_bytes")]
 
 
 FINISH = {0: None, 1: "eos", 2: "stop", 3: "length", 4: "context", 5: "abort"}
@@ -55,6 +55,12 @@ def _lib(dry_run):
                                          C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]
         lib.sglc_engine_poll_logprobs.argtypes = [C.c_void_p, C.c_longlong, C.POINTER(C.c_float), C.c_int]
         lib.sglc_engine_abort.argtypes = [C.c_void_p, C.c_longlong]
+        lib.sglc_engine_generated.argtypes = [C.c_void_p, C.c_longlong, C.POINTER(C.c_int), C.c_int]
+        lib.sglc_engine_sync.argtypes = [C.c_void_p]
+        lib.sglc_engine_mark.argtypes = [C.c_void_p, C.c_int]
+        lib.sglc_engine_ms_between_marks.restype = C.c_double
+        lib.sglc_engine_ms_between_marks.argtypes = [C.c_void_p]
+        lib.sglc_engine_rewind.argtypes = [C.c_void_p, C.c_longlong, C.c_int]
         lib.sglc_engine_get_stats.argtypes = [C.c_void_p, C.POINTER(CStats)]
         lib.sglc_engine_run_until_done.restype = C.c_longlong
         lib.sglc_engine_run_until_done.argtypes = [C.c_void_p, C.c_longlong]
@@ -149,6 +155,37 @@ class CEngine:
         out = (C.c_float * max(n, 1))()
         self.lib.sglc_engine_poll_logprobs(self.h, int(req_id), out, n)
         return list(out[:n])
+
+    def generated(self, req_id):
+        """What the request has generated so far (running, or finished and not yet taken), or None."""
+        n = self.lib.sglc_engine_generated(self.h, int(req_id), None, 0)
+        if n < 0:
+            return None
+        if n > len(self._buf):
+            self._buf = (C.c_int * (2 * n))()
+        n = self.lib.sglc_engine_generated(self.h, int(req_id), self._buf, len(self._buf))
+        return list(self._buf[:n])
+
+    def sync(self):
+        """Wait for the step in flight (run_ahead) and take its ids in; the requests it ended."""
+        n = self.lib.sglc_engine_sync(self.h)
+        if n < 0:
+            raise CEngineError(self.last_error())
+        return n
+
+    def mark(self, sync_first=False):
+        """A mark on the stream the steps run on, behind everything queued so far."""
+        if self.lib.sglc_engine_mark(self.h, int(sync_first)) != 0:
+            raise CEngineError(self.last_error())
+
+    def ms_between_marks(self):
+        """Device time between the last two marks (waits for the second)."""
+        return self.lib.sglc_engine_ms_between_marks(self.h)
+
+    def rewind(self, req_id, keep):
+        """A running request forgets what it generated beyond its first `keep` ids (no step in flight)."""
+        if self.lib.sglc_engine_rewind(self.h, int(req_id), int(keep)) != 0:
+            raise CEngineError(f"request {req_id} cannot be rewound to {keep} generated ids")
 
     def abort(self, req_id):
         return self.lib.sglc_engine_abort(self.h, int(req_id))

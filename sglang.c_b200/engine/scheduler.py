@@ -147,6 +147,11 @@ class Scheduler:
             self.requests.pop(self._taken.popleft(), None)
         return r.id, list(r.gen), len(r.prompt)
 
+    def generated(self, req_id):
+        """What the request has generated so far (running, or finished and kept), or None."""
+        r = self.requests.get(req_id)
+        return list(r.gen) if r is not None else None
+
     def poll_logprobs(self, req_id):
         r = self.requests.get(req_id)
         return list(r.logprobs) if r is not None else None

@@ -205,3 +205,26 @@ def test_half_and_double_precision_files_load_alike(model_dirs, tmp_path, dtype)
     got = drain(ce)
     assert [got[i] for i in ids] == want
     ce.close()
+
+
+def test_the_python_entry_points_run_on_the_native_engine(model_dirs, capsys):
+    """sched_new(native=True) gives the same entry points on the native engine: `generate` with
+    its per-token callback, and the command line's --native, give the ids of the Python engine."""
+    from sglang_c_b200 import cli
+    from sglang_c_b200.engine import generate, sched_new
+    from sglang_c_b200.sampling import SamplingParams
+    d = model_dirs("A", "bfloat16")
+    prompts = [traces.random_tokens(5, 12, TINY["A"]["vocab_size"]), traces.random_tokens(6, 3, TINY["A"]["vocab_size"])]
+    sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=3)
+    kw = dict(seed=3, dtype="bfloat16", page_size=16, max_tokens=256, max_requests=4)
+    want = generate(sched_new(d, **kw), prompts, sp, 10)
+    seen = []
+    got = generate(sched_new(d, native=True, **kw), prompts, sp, 10, on_token=lambda i, t: seen.append((i, t)))
+    assert got == want
+    assert [t for i, t in seen if i == 0] == want[0] and [t for i, t in seen if i == 1] == want[1]
+    ids = " ".join(map(str, prompts[0]))
+    outs = []
+    for extra in ([], ["--native"]):
+        assert cli.main(["--model", d, "--prompt-ids", ids, "--max-new", "10", "--seed", "3", "--verbose"] + extra) == 0
+        outs.append(capsys.readouterr().out.split())
+    assert outs[0] == outs[1] and len(outs[0]) == len(prompts[0]) + 10

@@ -654,7 +654,7 @@ def measure_model(name, base, n_layer, steps, warmup, pk, points=(1, 64), fp32=T
     return r
 
 
-def only(kind, base, n_layer, steps, warmup):
+def only(kind, base, n_layer, steps, warmup, batch=BATCH):
     """A handful of steps of one kind, each run as its launches (no graph: a profiler then sees
     the kernels in launch order), and one line of JSON with their device time."""
     import numpy as np
@@ -664,11 +664,11 @@ def only(kind, base, n_layer, steps, warmup):
     atexit.register(shutil.rmtree, tmp, True)
     model_dir = make_model(tmp, base, n_layer)
     dtype = "float32" if kind == "fp32" else "bfloat16"
-    eng = Engine.from_dir(model_dir, dtype=dtype, page_size=PAGE, max_tokens=BATCH * (CONTEXT + 256) + 4096,
-                          max_requests=BATCH, max_step_tokens=PREFILL_TOKENS, use_graphs=False)
+    eng = Engine.from_dir(model_dir, dtype=dtype, page_size=PAGE, max_tokens=batch * (CONTEXT + 256) + 4096,
+                          max_requests=batch, max_step_tokens=PREFILL_TOKENS, use_graphs=False)
     rng = np.random.default_rng(0)
     V = eng.plan.vocab_size
-    out = {"only": kind, "n_layer": n_layer, "dtype": dtype}
+    out = {"only": kind, "n_layer": n_layer, "dtype": dtype, "batch": batch}
 
     def timed(fn, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -695,12 +695,12 @@ def only(kind, base, n_layer, steps, warmup):
         timed(prefill, warmup)
         out["prefill_ms_eager"] = timed(prefill, steps)
     if kind in ("decode", "fp32"):
-        reqs = [f"d{i}" for i in range(BATCH)]
+        reqs = [f"d{i}" for i in range(batch)]
         for r in reqs:
             eng.add_request(r)
         done = 0
         while done < CONTEXT:
-            n = min(eng.max_step_tokens // BATCH, CONTEXT - done)
+            n = min(eng.max_step_tokens // batch, CONTEXT - done)
             eng.step([StepEntry(r, rng.integers(0, V, size=n).astype(np.int32), []) for r in reqs])
             done += n
 
@@ -727,6 +727,7 @@ def main():
                          "(64 requests, prompts of 16..1024 tokens, 128 generated each) under `points`")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                     help="decode: the contract's line; mixed: only the mixed workload through the scheduler")
+    ap.add_argument("--batch", type=int, default=BATCH, help="with --only decode: requests decoding together")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "fp32"],
                     help="a handful of steps of one kind and nothing else (what a profiler is pointed at): "
                          "decode steps at batch 8, prefill steps of 2 x 1,024 tokens, or both on the 32-bit path")
@@ -743,7 +744,7 @@ def main():
     base = MODELS[args.model]
     n_layer = args.layers or base["n_layer"]
     if args.only:
-        return only(args.only, base, n_layer, steps, warmup)
+        return only(args.only, base, n_layer, steps, warmup, args.batch)
     if args.workload == "mixed":
         tmp = tempfile.mkdtemp(prefix="sglc_bench_")
         atexit.register(shutil.rmtree, tmp, True)

@@ -517,6 +517,16 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (warp == 0) {
     // ---- TMA producer: one ring of stages across all of the block's tiles ----
     if (elect_one()) {
+      // the weights do not come from the kernel ahead: the first tile's weight halves of the
+      // ring's stages are asked for before the dependency wait, the token halves after it
+      const int pre = n_kb < stages ? n_kb : stages;
+      if (blockIdx.x < a.n_tiles) {
+        const int qt = blockIdx.x / a.tiles_p;
+        for (int i = 0; i < pre; i++) {
+          mbar_expect_tx(&ctl.full[i], STAGE_BYTES);
+          tma_load_2d(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, &ctl.full[i], i * BK, qt * BN);
+        }
+      }
       pdl_wait();
       int kc = 0;
       bool ok = true;
@@ -529,6 +539,10 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             break;
           }
           uint8_t* sp = smem + (size_t)s * STAGE_BYTES;
+          if (kc < pre) {
+            tma_load_2d(sp, &map_a, &ctl.full[s], i * BK, pt * BM);
+            continue;
+          }
           mbar_expect_tx(&ctl.full[s], STAGE_BYTES);
           tma_load_2d(sp, &map_a, &ctl.full[s], i * BK, pt * BM);
           tma_load_2d(sp + A_BYTES, &map_w, &ctl.full[s], i * BK, qt * BN);

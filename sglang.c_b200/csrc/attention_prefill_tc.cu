@@ -112,7 +112,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   // (the last query tile of the longest request) while most SMs have long finished.
   const int r = blockIdx.x / a.H, h = blockIdx.x % a.H, rank = blockIdx.z, cl = blockIdx.y;
   pdl_launch_dependents();
-  pdl_wait();
+  // What follows reads only the step's own arrays (request bounds, block tables), which no
+  // kernel of the step writes: the block finds its work, sets up its barriers and tensor memory
+  // and clears its stages while the kernel ahead still runs.  The loaders wait for that kernel
+  // before they touch queries or cache pages; everything else in the block follows from what
+  // they bring.
   const int t0 = a.q_start[r];
   const int q_len = a.q_start[r + 1] - t0;
   if (a.skip_single && q_len == 1) return;
@@ -215,6 +219,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     if (lt == 0) {
       const int ps = a.page_size;
       const int* bt = a.block_table + (size_t)r * a.bt_stride;
+      pdl_wait();
       mbar_expect_tx(&ctl.q_full, DB * BQ * 128);
       for (int blk = 0; blk < DB; blk++)
         tma_load_2d(sQ + blk * (BQ * 128), &map_q, &ctl.q_full, h * D + blk * 64, t0 + qt * BQ);
@@ -244,6 +249,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
   } else if (warp > MMA_WARP) {
     // ---- loaders by cp.async: Q once, then K and V tiles through the block table ----
     const int lt = threadIdx.x - (MMA_WARP + 1) * 32;
+    pdl_wait();
     {
       const __nv_bfloat16* qbase = a.q + (size_t)(t0 + qt * BQ) * a.q_stride + (size_t)h * D;
       const uint32_t dst = smem_u32(sQ);

@@ -113,6 +113,18 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int n4 = E / 4;
+  // gain and bias are weights, not produced by the kernel ahead: up to 1,024 columns they are
+  // fetched into registers before the dependency wait
+  constexpr bool PRE = NV <= 8;
+  float4 gp[PRE ? NV : 1], bp[PRE ? NV : 1];
+  if (PRE) {
+#pragma unroll
+    for (int j = 0; j < (PRE ? NV : 1); j++) {
+      const int i = lane + 32 * j;
+      gp[j] = i < n4 ? reinterpret_cast<const float4*>(gamma)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      bp[j] = i < n4 ? reinterpret_cast<const float4*>(beta)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait();
   if (r >= n_rows) return;
   const int src = rows ? rows[r] : r;
@@ -140,7 +152,8 @@ layernorm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows,
   for (int j = 0; j < NV; j++) {
     const int i = lane + 32 * j;
     if (i < n4) {
-      const float4 g = reinterpret_cast<const float4*>(gamma)[i], b = reinterpret_cast<const float4*>(beta)[i];
+      const float4 g = PRE ? gp[PRE ? j : 0] : reinterpret_cast<const float4*>(gamma)[i];
+      const float4 b = PRE ? bp[PRE ? j : 0] : reinterpret_cast<const float4*>(beta)[i];
       __nv_bfloat162 h0 = __floats2bfloat162_rn((v[j].x - mean) * inv * g.x + b.x, (v[j].y - mean) * inv * g.y + b.y);
       __nv_bfloat162 h1 = __floats2bfloat162_rn((v[j].z - mean) * inv * g.z + b.z, (v[j].w - mean) * inv * g.w + b.w);
       *reinterpret_cast<uint2*>(o + 4 * i) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));

@@ -763,6 +763,13 @@ def main():
         points["mixed_small_generated_tok_s"] = run_mixed(r["model_dir"], dict(base, n_layer=n_layer))["generated_tok_s"]
         points["mixed_small_c_api_generated_tok_s"] = \
             run_mixed_c(r["model_dir"], dict(base, n_layer=n_layer))["generated_tok_s"]
+        # other context lengths (the headline's is 512; the model has 1,024 positions)
+        for ctx in (128, 960):
+            for b in (8, 64):
+                t, _, _ = time_decode_native(r["model_dir"], b, ctx, steps, warmup)
+                points[f"decode_b{b}_ctx{ctx}"] = b / (t / 1e3)
+                nb = model_bytes_flops(dict(base, n_layer=n_layer), b, ctx + steps // 2)
+                points[f"decode_b{b}_ctx{ctx}_roofline_frac"] = nb / (t / 1e3) / 1e9 / pk["hbm_gbs"]
         for other in ("medium", "xl"):
             if other == args.model:
                 continue

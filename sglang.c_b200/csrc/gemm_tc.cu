@@ -607,40 +607,19 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
       ok = s_go[buf] != 0;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
-      if (KV && ok && qt * BN >= kv.q_cols) {
-        // a tile of keys or values: a thread has a token's row and writes it where the token's
-        // slot says, 64 bytes a chunk (a chunk of 32 columns lies within one head)
-        const int tok = pt * BM + row;
-        const int slot = tok < a.M ? kv.slots[tok] : -1;
-        const bool live = slot >= 0 && sglc_index_ok(slot / kv.page, kv.n_pages, a.err);
-        const size_t page = live ? (size_t)(slot / kv.page) : 0, off = live ? (size_t)(slot % kv.page) : 0;
-        const int kv_width = kv.heads * kv.dim;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c, r);
-          tmem_ld_wait();
-          if (c + 32 >= BN) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl.acc_empty[buf]);
-          }
-          const int cc = qt * BN + c - kv.q_cols;
-          if (!live || qt * BN + c >= a.N) continue;
-          const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / kv.dim, d = rem - head * kv.dim;
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(kv.cache) +
-                               (((page * 2 + which) * kv.heads + head) * kv.page + off) * kv.dim + d;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) {
-            __align__(16) __nv_bfloat162 hh[4];
-#pragma unroll
-            for (int x = 0; x < 4; x++)
-              hh[x] = __floats2bfloat162_rn(act_tc(__uint_as_float(r[8 * q4 + 2 * x]) + bias_s[c + 8 * q4 + 2 * x], a.act),
-                                            act_tc(__uint_as_float(r[8 * q4 + 2 * x + 1]) + bias_s[c + 8 * q4 + 2 * x + 1], a.act));
-            *reinterpret_cast<uint4*>(dst + 8 * q4) = *reinterpret_cast<uint4*>(hh);
+      if (ok && a.tma_out) {
+        // where this row's keys and values go (one of the step's own arrays names the slot)
+        size_t page = 0, off = 0;
+        bool live = false;
+        if (KV && qt * BN + BN > kv.q_cols) {
+          const int tok = pt * BM + row;
+          const int slot = tok < a.M ? kv.slots[tok] : -1;
+          live = slot >= 0 && sglc_index_ok(slot / kv.page, kv.n_pages, a.err);
+          if (live) {
+            page = (size_t)(slot / kv.page);
+            off = (size_t)(slot % kv.page);
           }
         }
-      } else if (ok && a.tma_out) {
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -655,6 +634,23 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
+          if (KV && qt * BN + c >= kv.q_cols) {
+            // 32 columns of keys or values (they lie within one head): 64 bytes of this token's
+            // row in its page, straight from the registers
+            if (!live || qt * BN + c >= a.N) continue;
+            const int kv_width = kv.heads * kv.dim, cc = qt * BN + c - kv.q_cols;
+            const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / kv.dim, d = rem - head * kv.dim;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(kv.cache) +
+                                 (((page * 2 + which) * kv.heads + head) * kv.page + off) * kv.dim + d;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(v[8 * q4 + 2 * x], v[8 * q4 + 2 * x + 1]);
+              *reinterpret_cast<uint4*>(dst + 8 * q4) = *reinterpret_cast<uint4*>(hh);
+            }
+            continue;
+          }
           const bool first_of_box = (c % box_cols) == 0;
           uint8_t* box = epi + (size_t)(boxes & 1) * BOX_BYTES;
           if (first_of_box) {
@@ -718,6 +714,259 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ---- many tokens, two SMs on one tile (cta_group::2) ------------------------------------------
+// A block of the kernel above takes in 32 KB of operands per K block of its 128 x 128 tile, and an
+// SM's way in from L2, not the tensor pipe, sets its pace.  Here a cluster of two blocks works on
+// one tile of 256 rows by BN columns: each block loads its own 128 rows of A and its half of the
+// BN rows of W, the even block issues MMAs that read both halves, and each block's 128 rows of
+// the result land in its own tensor memory.  At BN = 256 a block brings in the same 32 KB per K
+// block for twice the arithmetic; at BN = 128 24 KB for the same.  Barriers: the even block's
+// full[s] counts the bytes of both blocks' loads; empty[s] and acc_full[b] of each block get an
+// arrival from the even block's commits (the commit's multicast); the even block's acc_empty[b]
+// gets one from each epilogue warp of both blocks.  Otherwise the kernel above: one ring across
+// all of a pair's tiles, two accumulators, the same epilogues.
+template <int BN, bool KV>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, const GemmArgs a, const KvArgs kv) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int W_BYTES = (BN / 2) * BK * 2;     // this block's half of the tile's W rows
+  constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+  constexpr int BOX_BYTES = BM * 128;
+  constexpr int TMEM_COLS = 2 * BN;              // 256 or 512
+  static_assert(BN == 128 || BN == 256, "tensor memory is allocated in powers of two");
+  __shared__ StreamCtl ctl;
+  __shared__ float s_bias[2][BN];
+  __shared__ int s_go[2];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = blockIdx.x & 1;               // rank in the cluster (a cluster is two neighbours in x)
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int stages = a.stages;
+  uint8_t* epi = smem + (size_t)stages * STAGE_BYTES;       // two boxes
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; s++) {
+      mbar_init(&ctl.full[s], 1);
+      mbar_init(&ctl.empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      mbar_init(&ctl.acc_full[b], 1);
+      mbar_init(&ctl.acc_empty[b], 8);           // one arrival per epilogue warp of both blocks
+    }
+    ctl.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_w);
+    if (a.tma_out) tma_prefetch_desc(&map_out);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&ctl.tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  // both blocks' barriers exist before either signals the other's
+  cluster_arrive();
+  cluster_wait();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl.tmem_base;
+  volatile int* abort_flag = &ctl.abort_flag;
+  const int n_kb = a.kb_total;
+
+  if (warp == 0) {
+    // ---- TMA producer (both blocks): own rows of A, own half of W, bytes counted in the even block ----
+    if (elect_one()) {
+      const int pre = n_kb < stages ? n_kb : stages;
+      if (pair < a.n_tiles) {
+        const int qt = pair / a.tiles_p;
+        for (int i = 0; i < pre; i++) {
+          if (rank == 0) mbar_expect_tx(&ctl.full[i], 2 * STAGE_BYTES);
+          tma_load_2d_pair(smem + (size_t)i * STAGE_BYTES + A_BYTES, &map_w, map_to_peer(&ctl.full[i], 0), i * BK,
+                           qt * BN + rank * (BN / 2));
+        }
+      }
+      pdl_wait();
+      int kc = 0;
+      bool ok = true;
+      for (int t = pair; t < a.n_tiles && ok; t += n_pairs) {
+        const int pt = 2 * (t % a.tiles_p) + rank, qt = t / a.tiles_p;
+        for (int i = 0; i < n_kb; i++, kc++) {
+          const int s = kc % stages;
+          if (kc >= stages && !mbar_wait_cluster(&ctl.empty[s], ((kc / stages) - 1) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sp = smem + (size_t)s * STAGE_BYTES;
+          const uint32_t bar = map_to_peer(&ctl.full[s], 0);
+          if (kc < pre) {
+            tma_load_2d_pair(sp, &map_a, bar, i * BK, pt * BM);
+            continue;
+          }
+          if (rank == 0) mbar_expect_tx(&ctl.full[s], 2 * STAGE_BYTES);
+          tma_load_2d_pair(sp, &map_a, bar, i * BK, pt * BM);
+          tma_load_2d_pair(sp + A_BYTES, &map_w, bar, i * BK, qt * BN + rank * (BN / 2));
+        }
+      }
+      if (*abort_flag && rank == 0) {
+        // wait, with a limit, for both blocks' copies still in flight (they are counted here)
+        // before the pair may leave
+        for (int i = max(0, kc - stages); i < kc; i++)
+          mbar_wait_cluster(&ctl.full[i % stages], (i / stages) & 1, abort_flag);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the even block, for both ----
+    if (rank == 0 && elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16_f32(2 * BM, BN);
+      int kc = 0, n = 0;
+      bool ok = true;
+      for (int t = pair; t < a.n_tiles && ok; t += n_pairs, n++) {
+        const int buf = n & 1;
+        if (n >= 2) {
+          ok = mbar_wait_cluster(&ctl.acc_empty[buf], ((n >> 1) - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+        }
+        const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+        for (int i = 0; i < n_kb; i++, kc++) {
+          const int s = kc % stages;
+          ok = mbar_wait_cluster(&ctl.full[s], (kc / stages) & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sp = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc_k_sw128(sp);
+          const uint64_t dw = smem_desc_k_sw128(sp + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)
+            mma_bf16_pair(acc, da + 2 * k, dw + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          mma_commit_pair(&ctl.empty[s], 3);
+        }
+        if (ok) mma_commit_pair(&ctl.acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ---- epilogue (both blocks): warps 2..5 own TMEM lanes 32*(warp%4) .. +31 of their block's rows ----
+    const int e = threadIdx.x - 64;
+    const int lane_base = (warp & 3) * 32;
+    const int row = lane_base + lane;
+    const bool to_f32 = a.residual != nullptr;
+    const int box_cols = to_f32 ? 32 : 64;
+    int n = 0, boxes = 0;
+    bool ok = true;
+    for (int t = pair; t < a.n_tiles; t += n_pairs, n++) {
+      const int pt = 2 * (t % a.tiles_p) + rank, qt = t / a.tiles_p;
+      const int buf = n & 1;
+      float* bias_s = s_bias[buf];
+      for (int j = e; j < BN; j += 128) bias_s[j] = (a.bias && qt * BN + j < a.N) ? a.bias[qt * BN + j] : 0.0f;
+      if (ok) ok = mbar_wait_cluster(&ctl.acc_full[buf], (n >> 1) & 1, abort_flag);
+      tc_fence_after_sync();
+      if (threadIdx.x == 64) s_go[buf] = (ok && *abort_flag == 0) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
+      ok = s_go[buf] != 0;
+      const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
+      // the accumulator has been read: the even block's MMA warp may fill it again
+      auto release = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_peer(map_to_peer(&ctl.acc_empty[buf], 0));
+      };
+      if (ok && a.tma_out) {
+        // where this row's keys and values go (one of the step's own arrays names the slot)
+        size_t page = 0, off = 0;
+        bool live = false;
+        if (KV && qt * BN + BN > kv.q_cols) {
+          const int tok = pt * BM + row;
+          const int slot = tok < a.M ? kv.slots[tok] : -1;
+          live = slot >= 0 && sglc_index_ok(slot / kv.page, kv.n_pages, a.err);
+          if (live) {
+            page = (size_t)(slot / kv.page);
+            off = (size_t)(slot % kv.page);
+          }
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) release();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
+          if (KV && qt * BN + c >= kv.q_cols) {
+            // 32 columns of keys or values (within one head): 64 bytes of this token's row in its page
+            if (!live || qt * BN + c >= a.N) continue;
+            const int kv_width = kv.heads * kv.dim, cc = qt * BN + c - kv.q_cols;
+            const int which = cc / kv_width, rem = cc - which * kv_width, head = rem / kv.dim, d = rem - head * kv.dim;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(kv.cache) +
+                                 (((page * 2 + which) * kv.heads + head) * kv.page + off) * kv.dim + d;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(v[8 * q4 + 2 * x], v[8 * q4 + 2 * x + 1]);
+              *reinterpret_cast<uint4*>(dst + 8 * q4) = *reinterpret_cast<uint4*>(hh);
+            }
+            continue;
+          }
+          const bool first_of_box = (c % box_cols) == 0;
+          uint8_t* box = epi + (size_t)(boxes & 1) * BOX_BYTES;
+          if (first_of_box) {
+            if (threadIdx.x == 64) tma_store_wait_read_but_one();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+          if (to_f32) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++)
+              *reinterpret_cast<float4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int ch = (c % 64) / 8 + q4;
+              __align__(16) __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int x = 0; x < 4; x++) hh[x] = __floats2bfloat162_rn(v[8 * q4 + 2 * x], v[8 * q4 + 2 * x + 1]);
+              *reinterpret_cast<uint4*>(box + row * 128 + ((ch ^ (row & 7)) << 4)) = *reinterpret_cast<uint4*>(hh);
+            }
+          }
+          const bool last_of_box = ((c + 32) % box_cols) == 0;
+          if (last_of_box) {
+            fence_async_proxy();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+              const int x0 = qt * BN + (c + 32 - box_cols);
+              if (to_f32) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
+              else tma_store_2d(&map_out, box, x0, pt * BM);
+              tma_store_commit();
+            }
+            boxes++;
+          }
+        }
+      } else if (ok) {
+        release();                                   // (the host sends no such product here)
+      }
+    }
+    if (threadIdx.x == 64) tma_store_wait_read();      // shared memory must outlive the last stores' reads
+  }
+  // Neither block leaves, or frees tensor memory, while the other may still signal its barriers,
+  // have its shared memory read by an MMA, or read its own accumulators.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (threadIdx.x == 0 && ctl.abort_flag && a.err) atomicExch(a.err, 1);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -817,6 +1066,66 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   int grid = a.n_tiles < n_sm ? a.n_tiles : n_sm;
   return sglc_launch(gemm_tc_stream_kernel<BN, KV>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a, kv);
 }
+// The two-SM kernel: clusters of two blocks, as many as the device holds at once.
+template <int BN, bool KV>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a, const KvArgs& kv,
+                cudaStream_t stream) {
+  const size_t stage_bytes = (size_t)BM * BK * 2 + (size_t)(BN / 2) * BK * 2;
+  static int granted = 0, max_pairs = 0;
+  if (granted == 0) {
+    int stages = (int)(((size_t)226 * 1024 - 2 * BM * 128 - 2048) / stage_bytes);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    for (; stages >= 2; stages--) {
+      const size_t want = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
+      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)want) ==
+          cudaSuccess)
+        break;
+      cudaGetLastError();
+    }
+    if (stages < 2) return SGLC_ERR_UNSUPPORTED;
+    // how many clusters of two the device runs side by side (an SM without a free neighbour in
+    // its group stays empty): the tile walk assumes that all launched pairs are resident
+    cudaLaunchConfig_t probe = {};
+    probe.gridDim = dim3(2 * 148);
+    probe.blockDim = dim3(THREADS);
+    probe.dynamicSmemBytes = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
+    cudaLaunchAttribute pa[1];
+    pa[0].id = cudaLaunchAttributeClusterDimension;
+    pa[0].val.clusterDim.x = 2; pa[0].val.clusterDim.y = 1; pa[0].val.clusterDim.z = 1;
+    probe.attrs = pa;
+    probe.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN, KV>, &probe) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      return SGLC_ERR_UNSUPPORTED;
+    }
+    max_pairs = n;
+    granted = stages;
+  }
+  a.stages = granted;
+  const int pairs = a.n_tiles < max_pairs ? a.n_tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = (size_t)granted * stage_bytes + (size_t)2 * BM * 128 + 1024;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeClusterDimension;
+  attr[n].val.clusterDim.x = 2; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+  n++;
+  if (g_sglc_pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, KV>, ma, mw, mo, a, kv);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
+int pairs_at_once() { return 74; }
 }  // namespace
 
 // Orientation, tile width and K split for a problem size.
@@ -905,10 +1214,33 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
     else if (!out_f32) a.tma_out = get_map(&mo, out, M, N, ldo, BM) ? 1 : 0;
   }
   if (kv) {
-    // only the many-token kernel scatters, whole tiles of keys or values, 32-column chunks within a head
-    if (swap || !a.tma_out || kv->dim % 32 != 0 || kv->q_cols % bn != 0 || N != kv->q_cols + 2 * kv->heads * kv->dim ||
+    // only the many-token kernels scatter: 32-column chunks within a head, the queries' last
+    // 64-column box ending where the keys begin
+    if (swap || !a.tma_out || kv->dim % 32 != 0 || kv->q_cols % 64 != 0 || N != kv->q_cols + 2 * kv->heads * kv->dim ||
         kv->page <= 0 || ((uintptr_t)kv->cache & 15))
       return SGLC_ERR_UNSUPPORTED;
+  }
+  if (!swap && bn == 128 && a.tma_out && M >= 2 * BM) {
+    // One 128 x 128 tile a block, or 256 x 256 a pair of blocks?  The pair takes in half the bytes
+    // per flop, but a block of it has twice the epilogue to do and the pair's hand-shakes cost.
+    // Measured in replayed graphs at 2,048 tokens (one block -> pair): 6400 columns over K 1600
+    // 54.5 -> 34.9 us, 1600 columns over K 6400 65.0 -> 38.3 us, 2304 columns over K 768 12.4 ->
+    // 11.1 us, but 3072 columns with GELU over K 768 18.2 -> 19.8 us and 768 columns 8.2 -> 9.4
+    // us.  These fit: rounds of tiles x K blocks x 0.31 us + 4 us alone, x 0.38 us + 6.5 us in a
+    // pair (4 us more with an activation, whose epilogue the next tile's K loop no longer hides);
+    // the pair is taken where that says a tenth less.
+    const int rows2 = (M + 2 * BM - 1) / (2 * BM), t256 = rows2 * ((N + 255) / 256);
+    const int rounds_alone = (tp * tq + 147) / 148, rounds_pair = (t256 + pairs_at_once() - 1) / pairs_at_once();
+    const long long alone = (long long)rounds_alone * a.kb_total * 31 + 400;
+    const long long paired = (long long)rounds_pair * a.kb_total * 38 + 650 + (act != SGLC_ACT_NONE ? 400 : 0);
+    if (paired * 10 < alone * 9 && get_map(&mq, W, N, K, K, 128)) {
+      a.tiles_p = rows2;
+      a.n_tiles = t256;
+      const KvArgs none = {};
+      const int code = kv ? launch_pair<256, true>(mp, mq, mo, a, *kv, stream)
+                          : launch_pair<256, false>(mp, mq, mo, a, none, stream);
+      if (code != SGLC_ERR_UNSUPPORTED) return code;
+    }
   }
   if (!swap) {
     a.tiles_p = tp;

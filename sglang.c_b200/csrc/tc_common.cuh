@@ -340,6 +340,52 @@ static inline bool make_map_f32_2d(CUtensorMap* m, const void* base, uint64_t ro
   return r == CUDA_SUCCESS;
 }
 
+// ---- a pair of blocks (a cluster of two) on one MMA: cta_group::2 -------------------------------
+// Both blocks allocate, with the same shared-memory word for the result, and both free; the even
+// block issues the MMAs, which read each block's own rows of A and each block's half of B from
+// the same shared-memory offsets and leave each block's rows of D in its own tensor memory.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t n_cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+               "r"(n_cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t n_cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(n_cols) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// One arrival on the barrier at this offset in each block of `mask` (bit = rank in the cluster)
+// when every MMA issued so far by this thread has finished.  (A commit's multicast, not a load's.)
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+// 2-D tile load into this block's shared memory whose bytes are counted on a barrier of the
+// pair's even block (`bar_cluster`: its shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((uint64_t)m), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+
 // ---- device: tile stores ----------------------------------------------------------
 // Shared-memory tile -> global matrix through a tensor map (rows/columns outside the matrix
 // are dropped).  x*elem_size must be a multiple of 16 bytes; x, y must not be negative.

@@ -213,7 +213,12 @@ def test_attention_simt_and_kv_write(case_id, dtype):
 
 
 @pytest.mark.parametrize("M,H,Hkv,D,K,ps", [(300, 4, 4, 64, 256, 16), (1000, 8, 2, 128, 512, 16), (129, 2, 2, 32, 64, 8),
-                                            (2048, 12, 12, 64, 768, 16)])
+                                            (2048, 12, 12, 64, 768, 16),
+                                            # queries that end inside a tile (192 and 1600 columns), one block a tile
+                                            (300, 3, 3, 64, 256, 16), (300, 25, 25, 64, 1600, 16),
+                                            # sizes that take the pair of blocks on a 256 x 256 tile: queries that
+                                            # end inside a tile, and on a tile's edge
+                                            (2048, 25, 25, 64, 1600, 16), (2000, 16, 16, 128, 2048, 32)])
 def test_gemm_tc_kv_writes_what_projection_and_cache_write_would(M, H, Hkv, D, K, ps):
     """The query/key/value projection with the cache write in its epilogue: the same queries in
     `out`, the same bits in the same places of the cache as the plain product followed by
@@ -239,9 +244,9 @@ def test_gemm_tc_kv_writes_what_projection_and_cache_write_would(M, H, Hkv, D, K
 
 def test_gemm_tc_kv_declines_what_it_cannot_do():
     ops = _ops()
-    for M, H, Hkv, D, K in ((64, 4, 4, 64, 256), (300, 4, 4, 48, 256), (300, 3, 3, 64, 256)):
+    for M, H, Hkv, D, K in ((64, 4, 4, 64, 256), (300, 4, 4, 48, 256), (300, 3, 3, 32, 256)):
         # few tokens (the other orientation); heads that are no multiple of 32 wide; queries that
-        # do not end on a tile (3 x 64 columns with 128-wide tiles is fine only if tiles are 64 wide)
+        # do not end on a 64-column box (3 x 32 columns)
         N = (H + 2 * Hkv) * D
         a, w = _rand(M, K, dtype=torch.bfloat16, seed=1), _rand(N, K, dtype=torch.bfloat16, seed=2)
         out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
@@ -371,6 +376,8 @@ GEMM_TC_SHAPES = [
     (129, 768, 768), (300, 2304, 768), (2048, 768, 3072), (1000, 1000, 200), (257, 96, 320),
     (512, 50257 // 8, 96), (130, 72, 8), (2, 8, 8),
     (200, 128, 2048), (400, 200, 3000),      # few tiles and a long K; a K that ends inside a block of 64
+    # sizes that take a pair of blocks on a 256 x 256 tile; the last with ragged rows, columns and K
+    (2048, 6400, 1600), (2048, 1600, 6400), (1100, 3000, 1608),
 ]
 
 

@@ -39,6 +39,10 @@ constexpr int BK = 64;    // K per stage: 128 bytes of bfloat16, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 constexpr int MAX_STAGES = 8;
+constexpr int PAIR_THREADS = 64 + 256;   // the two-SM kernel: warp 0 TMA, warp 1 MMA, two groups of four epilogue warps
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 struct GemmArgs {
   int M, N, K;             // logical sizes
@@ -729,7 +733,7 @@ gemm_tc_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 // gets one from each epilogue warp of both blocks.  Otherwise the kernel above: one ring across
 // all of a pair's tiles, two accumulators, the same epilogues.
 template <int BN, bool KV>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, const GemmArgs a, const KvArgs kv) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -740,15 +744,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   constexpr int BOX_BYTES = BM * 128;
   constexpr int TMEM_COLS = 2 * BN;              // 256 or 512
   static_assert(BN == 128 || BN == 256, "tensor memory is allocated in powers of two");
+  // a block has 128 x BN results a tile to see off, twice the single-block kernel's: two groups
+  // of four epilogue warps (a warp reads the 32 lanes of tensor memory that its number modulo 4
+  // names), each with half of the columns, a box of its own and its own named barrier
+  constexpr int GC = BN / 2;
   __shared__ StreamCtl ctl;
-  __shared__ float s_bias[2][BN];
+  __shared__ float s_bias[BN];
   __shared__ int s_go[2];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = blockIdx.x & 1;               // rank in the cluster (a cluster is two neighbours in x)
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int stages = a.stages;
-  uint8_t* epi = smem + (size_t)stages * STAGE_BYTES;       // two boxes
+  uint8_t* epi = smem + (size_t)stages * STAGE_BYTES;       // a box for each group of epilogue warps
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -758,7 +766,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&ctl.acc_full[b], 1);
-      mbar_init(&ctl.acc_empty[b], 8);           // one arrival per epilogue warp of both blocks
+      mbar_init(&ctl.acc_empty[b], 16);          // one arrival per epilogue warp of both blocks
     }
     ctl.abort_flag = 0;
     mbar_fence_init();
@@ -854,24 +862,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // ---- epilogue (both blocks): warps 2..5 own TMEM lanes 32*(warp%4) .. +31 of their block's rows ----
-    const int e = threadIdx.x - 64;
+    // ---- epilogue (both blocks): a warp owns TMEM lanes 32*(warp%4) .. +31 of its block's rows ----
+    const int grp = (threadIdx.x - 64) >> 7, e = (threadIdx.x - 64) & 127;
+    const bool leader = e == 0;
+    const int bar_id = 1 + grp, c_lo = grp * GC;
     const int lane_base = (warp & 3) * 32;
     const int row = lane_base + lane;
     const bool to_f32 = a.residual != nullptr;
     const int box_cols = to_f32 ? 32 : 64;
-    int n = 0, boxes = 0;
+    uint8_t* box = epi + (size_t)grp * BOX_BYTES;
+    int n = 0;
     bool ok = true;
     for (int t = pair; t < a.n_tiles; t += n_pairs, n++) {
       const int pt = 2 * (t % a.tiles_p) + rank, qt = t / a.tiles_p;
       const int buf = n & 1;
-      float* bias_s = s_bias[buf];
-      for (int j = e; j < BN; j += 128) bias_s[j] = (a.bias && qt * BN + j < a.N) ? a.bias[qt * BN + j] : 0.0f;
+      float* bias_s = s_bias;
+      named_bar_sync(bar_id, 128);                              // the group is done with the last tile's bias
+      if (e < GC) bias_s[c_lo + e] = (a.bias && qt * BN + c_lo + e < a.N) ? a.bias[qt * BN + c_lo + e] : 0.0f;
       if (ok) ok = mbar_wait_cluster(&ctl.acc_full[buf], (n >> 1) & 1, abort_flag);
       tc_fence_after_sync();
-      if (threadIdx.x == 64) s_go[buf] = (ok && *abort_flag == 0) ? 1 : 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");          // the bias row is there for all
-      ok = s_go[buf] != 0;
+      if (leader) s_go[grp] = (ok && *abort_flag == 0) ? 1 : 0;
+      named_bar_sync(bar_id, 128);                              // the bias row is there for the group
+      ok = s_go[grp] != 0;
       const uint32_t taddr = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * BN);
       // the accumulator has been read: the even block's MMA warp may fill it again
       auto release = [&]() {
@@ -893,11 +905,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_lo; c < c_lo + GC; c += 32) {
           uint32_t r[32];
           tmem_ld_32x32(taddr + c, r);
           tmem_ld_wait();
-          if (c + 32 >= BN) release();
+          if (c + 32 >= c_lo + GC) release();
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = act_tc(__uint_as_float(r[j]) + bias_s[c + j], a.act);
@@ -918,10 +930,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             continue;
           }
           const bool first_of_box = (c % box_cols) == 0;
-          uint8_t* box = epi + (size_t)(boxes & 1) * BOX_BYTES;
           if (first_of_box) {
-            if (threadIdx.x == 64) tma_store_wait_read_but_one();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // the store that used the group's box before has read it (the values of this chunk
+            // were computed meanwhile)
+            if (leader) tma_store_wait_read();
+            named_bar_sync(bar_id, 128);
           }
           if (to_f32) {
 #pragma unroll
@@ -941,21 +954,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const bool last_of_box = ((c + 32) % box_cols) == 0;
           if (last_of_box) {
             fence_async_proxy();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
+            named_bar_sync(bar_id, 128);
+            if (leader) {
               const int x0 = qt * BN + (c + 32 - box_cols);
               if (to_f32) tma_reduce_add_2d(&map_out, box, x0, pt * BM);
               else tma_store_2d(&map_out, box, x0, pt * BM);
               tma_store_commit();
             }
-            boxes++;
           }
         }
       } else if (ok) {
         release();                                   // (the host sends no such product here)
       }
     }
-    if (threadIdx.x == 64) tma_store_wait_read();      // shared memory must outlive the last stores' reads
+    if (leader) tma_store_wait_read();                 // shared memory must outlive the last stores' reads
   }
   // Neither block leaves, or frees tensor memory, while the other may still signal its barriers,
   // have its shared memory read by an MMA, or read its own accumulators.
@@ -1087,7 +1099,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
     // its group stays empty): the tile walk assumes that all launched pairs are resident
     cudaLaunchConfig_t probe = {};
     probe.gridDim = dim3(2 * 148);
-    probe.blockDim = dim3(THREADS);
+    probe.blockDim = dim3(PAIR_THREADS);
     probe.dynamicSmemBytes = (size_t)stages * stage_bytes + (size_t)2 * BM * 128 + 1024;
     cudaLaunchAttribute pa[1];
     pa[0].id = cudaLaunchAttributeClusterDimension;
@@ -1106,7 +1118,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
   const int pairs = a.n_tiles < max_pairs ? a.n_tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(PAIR_THREADS);
   cfg.dynamicSmemBytes = (size_t)granted * stage_bytes + (size_t)2 * BM * 128 + 1024;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1222,18 +1234,19 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
   }
   if (!swap && bn == 128 && a.tma_out && M >= 2 * BM) {
     // One 128 x 128 tile a block, or 256 x 256 a pair of blocks?  The pair takes in half the bytes
-    // per flop, but a block of it has twice the epilogue to do and the pair's hand-shakes cost.
+    // per flop, but its hand-shakes cost and one round of its tiles leaves fewer SMs busy.
     // Measured in replayed graphs at 2,048 tokens (one block -> pair): 6400 columns over K 1600
-    // 54.5 -> 34.9 us, 1600 columns over K 6400 65.0 -> 38.3 us, 2304 columns over K 768 12.4 ->
-    // 11.1 us, but 3072 columns with GELU over K 768 18.2 -> 19.8 us and 768 columns 8.2 -> 9.4
-    // us.  These fit: rounds of tiles x K blocks x 0.31 us + 4 us alone, x 0.38 us + 6.5 us in a
-    // pair (4 us more with an activation, whose epilogue the next tile's K loop no longer hides);
-    // the pair is taken where that says a tenth less.
+    // 54.6 -> 34.7 us, 1600 columns over K 6400 64.4 -> 39.0 us, 2304 columns over K 768 12.5 ->
+    // 11.0 us, 3072 columns with GELU over K 768 18.2 -> 17.6 us, but 768 columns over K 768
+    // 8.1 -> 11.6 us and over K 3072 19.3 -> 22.0 us.  These fit: rounds of tiles x K blocks x
+    // 0.31 us + 5 us alone, x 0.38 us + 6.4 us in a pair (2 us more with an activation either
+    // way); the pair is taken where that says a twentieth less (prefill of 2,048 tokens on one
+    // GPU: GPT-2 small widths 1.060 -> 1.054 ms, medium 2.91 -> 2.72 ms, XL 11.65 -> 8.50 ms).
     const int rows2 = (M + 2 * BM - 1) / (2 * BM), t256 = rows2 * ((N + 255) / 256);
     const int rounds_alone = (tp * tq + 147) / 148, rounds_pair = (t256 + pairs_at_once() - 1) / pairs_at_once();
-    const long long alone = (long long)rounds_alone * a.kb_total * 31 + 400;
-    const long long paired = (long long)rounds_pair * a.kb_total * 38 + 650 + (act != SGLC_ACT_NONE ? 400 : 0);
-    if (paired * 10 < alone * 9 && get_map(&mq, W, N, K, K, 128)) {
+    const long long alone = (long long)rounds_alone * a.kb_total * 31 + 500 + (act != SGLC_ACT_NONE ? 200 : 0);
+    const long long paired = (long long)rounds_pair * a.kb_total * 38 + 640 + (act != SGLC_ACT_NONE ? 200 : 0);
+    if (paired * 100 < alone * 95 && get_map(&mq, W, N, K, K, 128)) {
       a.tiles_p = rows2;
       a.n_tiles = t256;
       const KvArgs none = {};

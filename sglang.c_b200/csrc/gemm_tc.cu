@@ -8,10 +8,13 @@
 // bias, GELU and the residual with separate kernels (k_fill_bias :2642, k_gelu :527,
 // k_residual :2405); its small-M products are one-block-per-output GEMVs (:333-349,412-427).
 //
-// One kernel serves both regimes through the choice of which matrix is the MMA's 128-row
-// operand ("P") and which its N operand ("Q", tile of BN rows):
-//   many tokens  (prefill): P = A (128 tokens per tile),  Q = W (BN output features per tile)
-//   few tokens   (decode):  P = W (128 features per tile), Q = A (all tokens, padded to BN),
+// Three kernels, chosen by gemm_tc_run:
+//   gemm_tc_stream_kernel   many tokens (prefill): 128 tokens x BN output features a tile, one
+//                           resident block per SM walking its tiles with two accumulators
+//   gemm_tc_pair_kernel     many tokens and enough columns: a cluster of two blocks on a tile of
+//                           256 tokens x 256 features (cta_group::2), half the operand bytes per flop
+//   gemm_tc_kernel          few tokens (decode): W on the MMA's 128-row side ("P"), the tokens as
+//                           its N operand ("Q", padded to a tile of BN),
 //                           with the K range split across the blocks of a thread-block
 //                           cluster so that many SMs stream weights.  Each block leaves its
 //                           float partial sums in its own shared memory; after a cluster

@@ -1081,7 +1081,9 @@ int launch_stream(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMa
   int grid = a.n_tiles < n_sm ? a.n_tiles : n_sm;
   return sglc_launch(gemm_tc_stream_kernel<BN, KV>, dim3(grid), dim3(THREADS), smem, stream, 1, true, ma, mw, mo, a, kv);
 }
-// The two-SM kernel: clusters of two blocks, as many as the device holds at once.
+// The two-SM kernel: clusters of two blocks, as many as the device holds at once (148 SMs: 74;
+// what the first launch learns from the occupancy query replaces the guess).
+int g_pairs_at_once = 74;
 template <int BN, bool KV>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a, const KvArgs& kv,
                 cudaStream_t stream) {
@@ -1115,6 +1117,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
       return SGLC_ERR_UNSUPPORTED;
     }
     max_pairs = n;
+    g_pairs_at_once = n;
     granted = stages;
   }
   a.stages = granted;
@@ -1140,7 +1143,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap&
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
-int pairs_at_once() { return 74; }
+int pairs_at_once() { return g_pairs_at_once; }
 }  // namespace
 
 // Orientation, tile width and K split for a problem size.

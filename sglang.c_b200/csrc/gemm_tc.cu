@@ -1193,6 +1193,26 @@ static void plan(int M, int N, int K, int* swap, int* bn, int* splits, int* kb_p
   }
 }
 
+// One 128 x 128 tile a block, or 256 x 256 a pair of blocks?  The pair takes in half the bytes
+// per flop, but its hand-shakes cost and one round of its tiles leaves fewer SMs busy.
+// Measured in replayed graphs at 2,048 tokens (one block -> pair): 6400 columns over K 1600
+// 54.6 -> 34.7 us, 1600 columns over K 6400 64.4 -> 39.0 us, 2304 columns over K 768 12.5 ->
+// 11.0 us, 3072 columns with GELU over K 768 18.2 -> 17.6 us, but 768 columns over K 768
+// 8.1 -> 11.6 us and over K 3072 19.3 -> 22.0 us.  These fit: rounds of tiles x K blocks x
+// 0.31 us + 5 us alone, x 0.38 us + 6.4 us in a pair (2 us more with an activation either
+// way); the pair is taken where that says a twentieth less (prefill of 2,048 tokens on one
+// GPU: GPT-2 small widths 1.060 -> 1.054 ms, medium 2.91 -> 2.72 ms, XL 11.65 -> 8.50 ms).
+// (tp x tq: the product's 128 x 128 tiles.)
+static bool pair_pays(int M, int N, int K, int act, int tp, int tq) {
+  if (M < 2 * BM) return false;
+  const int kb_total = (K + BK - 1) / BK;
+  const int rows2 = (M + 2 * BM - 1) / (2 * BM), t256 = rows2 * ((N + 255) / 256);
+  const int rounds_alone = (tp * tq + 147) / 148, rounds_pair = (t256 + pairs_at_once() - 1) / pairs_at_once();
+  const long long alone = (long long)rounds_alone * kb_total * 31 + 500 + (act != SGLC_ACT_NONE ? 200 : 0);
+  const long long paired = (long long)rounds_pair * kb_total * 38 + 640 + (act != SGLC_ACT_NONE ? 200 : 0);
+  return paired * 100 < alone * 95;
+}
+
 // A: bfloat16 [M,K], rows lda elements apart; W: bfloat16 [N,K] contiguous; bias float [N] or
 // null; out [M,N] rows ldo apart (bfloat16, or float if out_f32), or residual (float, in place).
 // err: device int, set to 1 if a wait ran out.
@@ -1238,21 +1258,9 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* ou
         kv->page <= 0 || ((uintptr_t)kv->cache & 15))
       return SGLC_ERR_UNSUPPORTED;
   }
-  if (!swap && bn == 128 && a.tma_out && M >= 2 * BM) {
-    // One 128 x 128 tile a block, or 256 x 256 a pair of blocks?  The pair takes in half the bytes
-    // per flop, but its hand-shakes cost and one round of its tiles leaves fewer SMs busy.
-    // Measured in replayed graphs at 2,048 tokens (one block -> pair): 6400 columns over K 1600
-    // 54.6 -> 34.7 us, 1600 columns over K 6400 64.4 -> 39.0 us, 2304 columns over K 768 12.5 ->
-    // 11.0 us, 3072 columns with GELU over K 768 18.2 -> 17.6 us, but 768 columns over K 768
-    // 8.1 -> 11.6 us and over K 3072 19.3 -> 22.0 us.  These fit: rounds of tiles x K blocks x
-    // 0.31 us + 5 us alone, x 0.38 us + 6.4 us in a pair (2 us more with an activation either
-    // way); the pair is taken where that says a twentieth less (prefill of 2,048 tokens on one
-    // GPU: GPT-2 small widths 1.060 -> 1.054 ms, medium 2.91 -> 2.72 ms, XL 11.65 -> 8.50 ms).
+  if (!swap && bn == 128 && a.tma_out && pair_pays(M, N, K, act, tp, tq)) {
     const int rows2 = (M + 2 * BM - 1) / (2 * BM), t256 = rows2 * ((N + 255) / 256);
-    const int rounds_alone = (tp * tq + 147) / 148, rounds_pair = (t256 + pairs_at_once() - 1) / pairs_at_once();
-    const long long alone = (long long)rounds_alone * a.kb_total * 31 + 500 + (act != SGLC_ACT_NONE ? 200 : 0);
-    const long long paired = (long long)rounds_pair * a.kb_total * 38 + 640 + (act != SGLC_ACT_NONE ? 200 : 0);
-    if (paired * 100 < alone * 95 && get_map(&mq, W, N, K, K, 128)) {
+    if (get_map(&mq, W, N, K, K, 128)) {
       a.tiles_p = rows2;
       a.n_tiles = t256;
       const KvArgs none = {};
@@ -1313,4 +1321,15 @@ SGLC_API int sglc_gemm_tc_kv(const void* A, const void* W, const float* bias, vo
   if (!cache || !slots || heads <= 0 || dim <= 0) return SGLC_ERR_ARGUMENT;
   const KvArgs kv{cache, slots, q_cols, heads, dim, page_size, n_pages};
   return gemm_tc_run(A, W, bias, out, nullptr, M, N, K, lda, ldo, 0, act, err, &kv, stream);
+}
+
+// Which kernel sglc_gemm_tc takes for a product whose output a tensor map can address (rows 16-byte
+// aligned; any product of few tokens): 0 the few-token kernel, 1 the many-token kernel with one
+// block a tile, 2 the many-token kernel on pairs of SMs.  (Tests ask, so that the sizes they
+// choose for a kernel do reach it.)
+SGLC_API int sglc_gemm_tc_form(int M, int N, int K, int act) {
+  int swap, bn, splits, per, tp, tq;
+  plan(M, N, K, &swap, &bn, &splits, &per, &tp, &tq);
+  if (swap) return 0;
+  return (bn == 128 && pair_pays(M, N, K, act, tp, tq)) ? 2 : 1;
 }

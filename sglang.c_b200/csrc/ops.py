@@ -341,6 +341,13 @@ def gemm_tc_kv(a, w, bias, out, cache, slots, n_heads, n_kv_heads, head_dim):
     return True
 
 
+def gemm_tc_form(M, N, K, act=None):
+    """Which of gemm_tc's kernels a product of these sizes takes: "few" (up to 128 tokens: weights on
+    the MMA's 128-row side, split-K over a cluster), "stream" (many tokens, one block a tile) or "pair"
+    (many tokens on pairs of SMs)."""
+    return ("few", "stream", "pair")[build.load("gemm_tc").sglc_gemm_tc_form(int(M), int(N), int(K), ACT[act])]
+
+
 FEW_MAX_TOKENS = 2           # products of so few tokens go to gemm_few ...
 FEW_MAX_WEIGHT = 3 << 20     # ... if the weight matrix has no more elements than this
 

@@ -381,6 +381,20 @@ GEMM_TC_SHAPES = [
 ]
 
 
+def test_gemm_tc_shapes_reach_all_three_kernels():
+    """The sizes above are chosen for a kernel each; the library says which one a size takes."""
+    ops = _ops()
+    forms = {(M, N, K): ops.gemm_tc_form(M, N, K) for M, N, K in GEMM_TC_SHAPES}
+    assert forms[(8, 2304, 768)] == "few" and forms[(64, 768, 768)] == "few" and forms[(33, 1000, 96)] == "few"
+    # (from 65 tokens on a product over a short K takes the many-token kernel)
+    assert forms[(2048, 768, 3072)] == "stream" and forms[(129, 768, 768)] == "stream" and forms[(128, 50257, 64)] == "stream"
+    for size in ((2048, 6400, 1600), (2048, 1600, 6400), (1100, 3000, 1608)):
+        assert forms[size] == "pair"
+    # and the projections of test_gemm_tc_kv_...: queries ending inside a tile, on one block and on a pair
+    assert ops.gemm_tc_form(300, 3 * 25 * 64, 1600) == "stream" and ops.gemm_tc_form(2048, 3 * 25 * 64, 1600) == "pair"
+    assert ops.gemm_tc_form(2000, 3 * 16 * 128, 2048) == "pair" and ops.gemm_tc_form(2048, 2304, 768) == "pair"
+
+
 @pytest.mark.parametrize("M,N,K", GEMM_TC_SHAPES)
 def test_gemm_tc(M, N, K):
     """The tcgen05 GEMM against a float64 product of the same bfloat16 operands."""

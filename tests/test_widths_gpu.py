@@ -67,6 +67,33 @@ def test_real_widths_whole_and_cut(width_dirs, tmp_path, name, dtype):
         eng.check_device_errors()
 
 
+def test_xl_widths_two_thousand_tokens_a_step(width_dirs, tmp_path):
+    """Four prompts of 500 tokens in one step at XL widths: the products are large enough for the
+    kernel on pairs of SMs (all four of a layer), and the queries' 1,600 columns end inside one of
+    its tiles, beside which keys and values go into the cache from the same epilogue.  The same
+    requests cut into portions of changing size stay on the one-block kernel; both against the
+    plain implementation."""
+    from sglang_c_b200.csrc import ops
+    from sglang_c_b200.engine import Engine
+    from sglang_c_b200.engine.replay import replay
+    for N, K, act in ((4800, 1600, None), (1600, 1600, None), (6400, 1600, "gelu_tanh"), (1600, 6400, None)):
+        assert ops.gemm_tc_form(2000, N, K, act) == "pair"
+    d = width_dirs("xl", "bfloat16")
+    reqs = {rid: traces.random_tokens(10 + i, 500, 1031) for i, rid in enumerate("abcd")}
+    ref = {rid: plain(d, toks, "bfloat16") for rid, toks in reqs.items()}
+    together = [{"step": 0, "entries": [{"id": rid, "tokens": toks, "want": list(range(len(toks)))}
+                                        for rid, toks in reqs.items()], "end": list(reqs)}]
+    for mode, steps in (("together", together), ("portions", traces.portions(reqs))):
+        eng = Engine.from_dir(d, dtype="bfloat16", page_size=16, n_pages=traces.peak_tokens(steps) // 16,
+                              max_requests=4, max_step_tokens=2048)
+        out = str(tmp_path / mode)
+        replay(eng, traces.to_lines(steps), out)
+        got = traces.collect(steps, out, 1031)
+        err, where = traces.max_error(got, ref)
+        assert err < TOL["bfloat16"], f"xl {mode}: max error {err} at {where}"
+        eng.check_device_errors()
+
+
 def test_many_single_tokens_of_unequal_contexts(width_dirs, tmp_path):
     """Sixteen requests of 12 heads decode together: enough (token, head) items for the streaming
     decode attention, with contexts from 20 to 330 tokens, so that the step lists its tokens
